@@ -1,0 +1,142 @@
+/* munet_b200 — C ABI of the B200 (sm_100a) forward-inference kernels.
+ *
+ * This is the thin boundary a MuNet device backend binds to: plain pointers and
+ * sizes, no C++ or torch types.  Every function returns an int status
+ * (MU_OK == 0), never throws and never exits; mu_last_error(ctx) gives the text
+ * of the last failure on that context.  All compute entry points are
+ * asynchronous on the `stream` argument (a cudaStream_t passed as void*, NULL =
+ * the legacy default stream).  Device-side faults that cannot be known at
+ * launch time (a bounded wait that ran out, an out-of-range embedding id) are
+ * latched in a per-context status word and reported by mu_check().
+ *
+ * Citations name the interface of the reference (bryan-pakulski/MuNet, paths
+ * relative to its checkout) that each entry point stands in for.
+ *
+ * dtype codes follow the reference DataType enum order (src/types.hpp:16).
+ */
+#ifndef MUNET_B200_H
+#define MUNET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MU_ABI_VERSION 1
+
+enum mu_status {
+  MU_OK = 0,
+  MU_ERR_INVALID = 1,     /* bad argument (null pointer, negative size, …) */
+  MU_ERR_UNSUPPORTED = 2, /* dtype / mode this build does not implement */
+  MU_ERR_CUDA = 3,        /* a CUDA runtime / driver call failed */
+  MU_ERR_TIMEOUT = 4,     /* a bounded device-side wait ran out */
+  MU_ERR_INDEX = 5,       /* embedding id out of range */
+  MU_ERR_NOMEM = 6,
+  MU_ERR_SIZE = 7         /* size beyond a documented maximum */
+};
+
+enum mu_dtype { MU_F32 = 0, MU_F16 = 1, MU_BF16 = 2, MU_I32 = 3 };
+
+/* Activation modules (src/nn/activations.hpp): GELU is x*sigmoid(1.702x),
+ * Tanh is sigmoid(2x)*2-1, exactly as the reference composes them. */
+enum mu_act { MU_ACT_NONE = 0, MU_ACT_RELU = 1, MU_ACT_GELU = 2, MU_ACT_SIGMOID = 3, MU_ACT_TANH = 4 };
+
+/* How attention scores address K (src/nn/attention.hpp:64).
+ * MU_K_LITERAL reproduces the reference bit-for-bit in structure: its
+ * `k.transpose(0,1)` is a stride-only view and its matmul ignores strides, so
+ * scores are sum_d Q[i,d] * Kbuf[d*N + j] with N = B*H*T.
+ * MU_K_MATH is the textbook Q·K^T. */
+enum mu_kmode { MU_K_LITERAL = 0, MU_K_MATH = 1 };
+
+enum mu_copy_kind { MU_COPY_H2D = 1, MU_COPY_D2H = 2, MU_COPY_D2D = 3 };
+
+typedef struct mu_ctx mu_ctx;
+
+/* ---- context, memory, synchronisation -------------------------------------
+ * Replaces Backend construction per (type,index) (src/backend/backend_manager.cpp:102-123)
+ * and Backend::allocate / deallocate / copy / synchronize
+ * (src/core/backend.hpp:207-232; CUDA reference src/backend/cuda_backend.cu:842-961). */
+int mu_abi_version(void);
+int mu_ctx_create(int device, mu_ctx **out);
+void mu_ctx_destroy(mu_ctx *ctx);
+const char *mu_last_error(const mu_ctx *ctx);
+int mu_ctx_num_sms(const mu_ctx *ctx);
+/* force every matmul onto the CUDA-core kernel (debug / A-B checks); 0 restores */
+int mu_ctx_force_simt(mu_ctx *ctx, int on);
+int mu_alloc(mu_ctx *ctx, size_t bytes, void **ptr);
+int mu_free(mu_ctx *ctx, void *ptr);
+int mu_copy(mu_ctx *ctx, void *dst, const void *src, size_t bytes, int kind, void *stream);
+int mu_synchronize(mu_ctx *ctx);
+/* Synchronise `stream`, then report and clear the latched device status. */
+int mu_check(mu_ctx *ctx, void *stream);
+
+/* ---- BLAS capability -------------------------------------------------------
+ * BackendBlasCapability::matmul / batched_matmul (src/core/backend.hpp:250-260):
+ * C[M,N] = op(A)·op(B), row-major. transA is a training-only path
+ * (autograd) and returns MU_ERR_UNSUPPORTED. stride_b == 0 broadcasts B. */
+int mu_matmul(mu_ctx *ctx, const void *a, const void *b, void *c, int M, int K, int N,
+              int transA, int transB, int dtype, void *stream);
+int mu_batched_matmul(mu_ctx *ctx, const void *a, const void *b, void *c, int batch, int M, int K,
+                      int N, int transA, int transB, long long stride_a, long long stride_b,
+                      long long stride_out, int dtype, void *stream);
+
+/* ---- fused Linear ----------------------------------------------------------
+ * nn::Linear::forward_impl (src/nn/linear.hpp:28-34) = matmul + broadcast add,
+ * fused with the activation module that follows it in a Sequential and with the
+ * residual add of a decoder block (demos/multigpu/gpt3_multi_gpu_demo.py:106-113):
+ *   y[M,N] = act(x[M,K]·w[K,N] + bias[N]) + residual[M,N]
+ * bias and residual may be NULL. w is [in_features, out_features] row-major. */
+int mu_linear(mu_ctx *ctx, const void *x, const void *w, const void *bias, const void *residual,
+              void *y, int M, int K, int N, int act, int dtype, void *stream);
+
+/* Fused q/k/v projections of nn::MultiHeadAttention (src/nn/attention.hpp:46-62):
+ * x[B*T,E]·w[E,3E] + bias[3E] with w = [q_proj.weight | k_proj.weight | v_proj.weight]
+ * concatenated on the output axis; the result is written head-major, i.e. what
+ * reshape[B,T,H,D].permute(0,2,1,3).contiguous() produces: q,k,v each [B*H*T, D]. */
+int mu_linear_qkv(mu_ctx *ctx, const void *x, const void *w_qkv, const void *bias_qkv, void *q,
+                  void *k, void *v, int B, int T, int E, int H, int dtype, void *stream);
+
+/* ---- attention core --------------------------------------------------------
+ * The scale / mask / softmax / P·V part of MultiHeadAttention::forward_impl
+ * (src/nn/attention.hpp:64-99) on head-major q,k,v [B*H*T, D]; `out` is the merged
+ * token-major context [B*T, H*D] that feeds out_proj. Block-diagonal masking is
+ * implicit (each head attends to itself only). workspace: mu_attention_workspace_bytes. */
+size_t mu_attention_workspace_bytes(int B, int H, int T, int D, int dtype);
+int mu_attention(mu_ctx *ctx, const void *q, const void *k, const void *v, void *out, int B, int H,
+                 int T, int D, int causal, int kmode, int dtype, void *workspace,
+                 size_t workspace_bytes, void *stream);
+
+/* ---- normalisation / softmax ----------------------------------------------
+ * ops::layer_norm (src/core/ops/normalization.cpp:125-224; host-only in the
+ * reference) and Backend::softmax over the last dim (src/core/backend.hpp:243). */
+int mu_layer_norm(mu_ctx *ctx, const void *x, const void *gamma, const void *beta, void *y,
+                  long long rows, int cols, float eps, int dtype, void *stream);
+int mu_softmax(mu_ctx *ctx, const void *x, void *y, long long rows, int cols, int dtype,
+               void *stream);
+
+/* ---- embedding -------------------------------------------------------------
+ * nn::Embedding index path (src/nn/linear.hpp:92-131): out[b,t,:] = table[ids[b,t],:]
+ * (+ pos[t,:] when pos != NULL — the token + position sum of the decoder).
+ * An id outside [0,V) latches MU_ERR_INDEX (the reference throws). */
+int mu_embedding(mu_ctx *ctx, const int32_t *ids, const void *table, const void *pos, void *out,
+                 int B, int T, int V, int D, int dtype, void *stream);
+
+/* ---- elementwise chain -----------------------------------------------------
+ * Backend::add / relu / sigmoid and the activation modules built from them
+ * (src/core/backend.hpp:233-242, src/nn/activations.hpp):
+ *   y = act(x + bias[i % cols]) + residual ; bias / residual may be NULL. */
+int mu_eltwise(mu_ctx *ctx, const void *x, const void *bias, const void *residual, void *y,
+               long long n, int cols, int act, int dtype, void *stream);
+
+/* ---- argmax ---------------------------------------------------------------
+ * The reference has no argmax op; its demos take np.argmax of the logits
+ * (demos/transformers/decoder_block_demo.py:112). First maximum wins. */
+int mu_argmax(mu_ctx *ctx, const void *x, int32_t *idx, long long rows, int cols, int dtype,
+              void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MUNET_B200_H */

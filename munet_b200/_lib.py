@@ -1,0 +1,187 @@
+"""ctypes binding of the C ABI in include/munet_b200.h.
+
+``Context`` wraps one ``mu_ctx`` (one device).  Its methods take any object with
+a ``data_ptr()`` (torch tensors) or raw integer device addresses; torch is used
+only by callers for device memory and streams, never for compute.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+F32, F16, BF16, I32 = 0, 1, 2, 3
+ACT = {"none": 0, "relu": 1, "gelu": 2, "sigmoid": 3, "tanh": 4, None: 0}
+K_LITERAL, K_MATH = 0, 1
+COPY_H2D, COPY_D2H, COPY_D2D = 1, 2, 3
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+class MuNetError(RuntimeError):
+    """A non-zero status from the native library (message = mu_last_error)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[munet_b200 status {code}] {message}")
+        self.code = code
+
+
+def lib_path() -> str:
+    return os.path.join(_HERE, "lib", "libmunet_b200.so")
+
+
+_lib = None
+
+_vp, _i, _ll, _sz, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t, C.c_float
+
+# name -> (restype, argtypes); mirrors include/munet_b200.h one to one
+SIGNATURES = {
+    "mu_abi_version": (_i, []),
+    "mu_ctx_create": (_i, [_i, C.POINTER(_vp)]),
+    "mu_ctx_destroy": (None, [_vp]),
+    "mu_last_error": (C.c_char_p, [_vp]),
+    "mu_ctx_num_sms": (_i, [_vp]),
+    "mu_ctx_force_simt": (_i, [_vp, _i]),
+    "mu_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
+    "mu_free": (_i, [_vp, _vp]),
+    "mu_copy": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
+    "mu_synchronize": (_i, [_vp]),
+    "mu_check": (_i, [_vp, _vp]),
+    "mu_matmul": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "mu_batched_matmul": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _vp]),
+    "mu_linear": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "mu_linear_qkv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "mu_attention_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "mu_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "mu_layer_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _i, _f, _i, _vp]),
+    "mu_softmax": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
+    "mu_embedding": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "mu_eltwise": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp]),
+    "mu_argmax": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
+}
+
+
+def lib() -> C.CDLL:
+    """Load libmunet_b200.so (built in-tree by ``python -m munet_b200.build``)."""
+    global _lib
+    if _lib is None:
+        path = lib_path()
+        if not os.path.exists(path):
+            raise ImportError(
+                f"{path} is missing: build the CUDA extension first "
+                "(python -m munet_b200.build). There is no fallback implementation.")
+        handle = C.CDLL(path)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError here = ABI mismatch, fail loudly
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+def _stream(stream):
+    if stream is None:
+        try:
+            import torch
+            return torch.cuda.current_stream().cuda_stream
+        except Exception:
+            return None
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+class Context:
+    """One device context of the native backend."""
+
+    def __init__(self, device: int = 0):
+        self._lib = lib()
+        h = _vp()
+        rc = self._lib.mu_ctx_create(device, C.byref(h))
+        if rc != 0:
+            raise MuNetError(rc, f"mu_ctx_create(device={device}) failed")
+        self._h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.mu_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _rc(self, rc: int):
+        if rc != 0:
+            raise MuNetError(rc, self._lib.mu_last_error(self._h).decode())
+
+    @property
+    def num_sms(self) -> int:
+        return self._lib.mu_ctx_num_sms(self._h)
+
+    def force_simt(self, on: bool):
+        self._rc(self._lib.mu_ctx_force_simt(self._h, int(on)))
+
+    def check(self, stream=None):
+        """Synchronise the stream and raise if a kernel latched a device-side error."""
+        self._rc(self._lib.mu_check(self._h, _stream(stream)))
+
+    def synchronize(self):
+        self._rc(self._lib.mu_synchronize(self._h))
+
+    # -- BLAS ----------------------------------------------------------------
+    def matmul(self, a, b, c, M, K, N, dtype, transA=False, transB=False, stream=None):
+        self._rc(self._lib.mu_matmul(self._h, _ptr(a), _ptr(b), _ptr(c), M, K, N, int(transA),
+                                     int(transB), dtype, _stream(stream)))
+
+    def batched_matmul(self, a, b, c, batch, M, K, N, stride_a, stride_b, stride_out, dtype,
+                       transA=False, transB=False, stream=None):
+        self._rc(self._lib.mu_batched_matmul(self._h, _ptr(a), _ptr(b), _ptr(c), batch, M, K, N,
+                                             int(transA), int(transB), stride_a, stride_b,
+                                             stride_out, dtype, _stream(stream)))
+
+    def linear(self, x, w, bias, y, M, K, N, dtype, act="none", residual=None, stream=None):
+        self._rc(self._lib.mu_linear(self._h, _ptr(x), _ptr(w), _ptr(bias), _ptr(residual), _ptr(y),
+                                     M, K, N, ACT[act], dtype, _stream(stream)))
+
+    def linear_qkv(self, x, w_qkv, bias_qkv, q, k, v, B, T, E, H, dtype, stream=None):
+        self._rc(self._lib.mu_linear_qkv(self._h, _ptr(x), _ptr(w_qkv), _ptr(bias_qkv), _ptr(q),
+                                         _ptr(k), _ptr(v), B, T, E, H, dtype, _stream(stream)))
+
+    def attention_workspace_bytes(self, B, H, T, D, dtype) -> int:
+        return int(self._lib.mu_attention_workspace_bytes(B, H, T, D, dtype))
+
+    def attention(self, q, k, v, out, B, H, T, D, causal, kmode, dtype, workspace, workspace_bytes,
+                  stream=None):
+        self._rc(self._lib.mu_attention(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H, T, D,
+                                        int(causal), kmode, dtype, _ptr(workspace),
+                                        workspace_bytes, _stream(stream)))
+
+    # -- rows / elementwise ----------------------------------------------------
+    def layer_norm(self, x, gamma, beta, y, rows, cols, dtype, eps=1e-5, stream=None):
+        self._rc(self._lib.mu_layer_norm(self._h, _ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), rows,
+                                         cols, eps, dtype, _stream(stream)))
+
+    def softmax(self, x, y, rows, cols, dtype, stream=None):
+        self._rc(self._lib.mu_softmax(self._h, _ptr(x), _ptr(y), rows, cols, dtype, _stream(stream)))
+
+    def embedding(self, ids, table, pos, out, B, T, V, D, dtype, stream=None):
+        self._rc(self._lib.mu_embedding(self._h, _ptr(ids), _ptr(table), _ptr(pos), _ptr(out), B, T,
+                                        V, D, dtype, _stream(stream)))
+
+    def eltwise(self, x, y, n, dtype, act="none", bias=None, cols=1, residual=None, stream=None):
+        self._rc(self._lib.mu_eltwise(self._h, _ptr(x), _ptr(bias), _ptr(residual), _ptr(y), n, cols,
+                                      ACT[act], dtype, _stream(stream)))
+
+    def argmax(self, x, idx, rows, cols, dtype, stream=None):
+        self._rc(self._lib.mu_argmax(self._h, _ptr(x), _ptr(idx), rows, cols, dtype, _stream(stream)))

@@ -1,0 +1,495 @@
+// extern "C" boundary of libmunet_b200.so (declared in include/munet_b200.h).
+// Validates arguments, picks the kernel for each call and turns every failure
+// into a status code + message; nothing here throws or exits.
+#include "../../include/munet_b200.h"
+#include "common.h"
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+namespace mu {
+int launch_gemm_bf16_tcgen05(const GemmOperands &, const GemmShape &, const Epilogue &, int *status,
+                             int num_sms, cudaStream_t);
+int launch_gemm_simt(const SimtArgs &, cudaStream_t);
+int launch_layer_norm(const void *, const void *, const void *, void *, long long, int, float, int,
+                      cudaStream_t);
+int launch_softmax(const void *, void *, long long, int, float, int, int, int, cudaStream_t);
+int launch_embedding(const int *, const void *, const void *, void *, long long, int, int, int, int,
+                     int *, cudaStream_t);
+int launch_eltwise(const void *, const void *, const void *, void *, long long, int, int, int, int,
+                   cudaStream_t);
+int launch_argmax(const void *, int *, long long, int, int, cudaStream_t);
+} // namespace mu
+
+struct mu_ctx {
+  int device = 0;
+  int num_sms = 0;
+  int force_simt = 0;
+  int *d_status = nullptr;
+  char err[512] = {0};
+};
+
+namespace {
+
+int fail(mu_ctx *ctx, int code, const char *fmt, ...) {
+  if (ctx) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+    va_end(ap);
+  }
+  return code;
+}
+
+int cuda_fail(mu_ctx *ctx, const char *what, cudaError_t e) {
+  return fail(ctx, MU_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool set_device(mu_ctx *ctx) {
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess)
+    return false;
+  if (cur != ctx->device && cudaSetDevice(ctx->device) != cudaSuccess)
+    return false;
+  return true;
+}
+
+size_t esize(int dtype) { return dtype == MU_F32 || dtype == MU_I32 ? 4 : 2; }
+bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool epilogue_vec_ok(const mu::Epilogue &ep) {
+  if (!al16(ep.c) || (ep.bias && !al16(ep.bias)) || (ep.residual && !al16(ep.residual)))
+    return false;
+  if (ep.split_T > 0)
+    return ep.split_D % 32 == 0 && ep.split_which_stride % 8 == 0;
+  return ep.ldc % 8 == 0 && ep.batch_hi % 8 == 0 && ep.batch_lo % 8 == 0;
+}
+
+// One GEMM: tcgen05 when dtype/alignment allow it, CUDA-core kernel otherwise.
+int run_gemm(mu_ctx *ctx, const mu::GemmOperands &op, const mu::GemmShape &sh, mu::Epilogue ep,
+             int dtype, cudaStream_t st, const char *who) {
+  if (dtype != MU_F32 && dtype != MU_BF16)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "%s: dtype %d not implemented (float32, bfloat16)", who,
+                dtype);
+  if (sh.M == 0 || sh.N == 0 || sh.batch == 0)
+    return MU_OK;
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "%s: cannot select device %d", who, ctx->device);
+  if (dtype == MU_BF16 && !ctx->force_simt && sh.K > 0) {
+    ep.vec_ok = epilogue_vec_ok(ep) ? 1 : 0;
+    int rc = mu::launch_gemm_bf16_tcgen05(op, sh, ep, ctx->d_status, ctx->num_sms, st);
+    if (rc == 0)
+      return MU_OK;
+    if (rc == 2)
+      return cuda_fail(ctx, who, cudaGetLastError());
+    // rc == 1: shape or alignment outside the TMA kernel's envelope
+  }
+  mu::SimtArgs g;
+  g.a = op.a, g.b = op.b, g.lda = op.lda, g.ldb = op.ldb;
+  g.a_batch = op.a_batch, g.b_batch = op.b_batch, g.b_kmajor = op.b_kmajor;
+  g.is_bf16 = dtype == MU_BF16;
+  g.sh = sh, g.ep = ep;
+  int rc = mu::launch_gemm_simt(g, st);
+  if (rc == 1)
+    return fail(ctx, MU_ERR_INVALID, "%s: shape M=%d N=%d K=%d batch=%d out of range", who, sh.M,
+                sh.N, sh.K, sh.batch);
+  if (rc != 0)
+    return cuda_fail(ctx, who, cudaGetLastError());
+  return MU_OK;
+}
+
+#define MU_REQUIRE(cond, ...)                                                                    \
+  do {                                                                                           \
+    if (!(cond))                                                                                 \
+      return fail(ctx, MU_ERR_INVALID, __VA_ARGS__);                                             \
+  } while (0)
+
+} // namespace
+
+extern "C" {
+
+int mu_abi_version(void) { return MU_ABI_VERSION; }
+
+int mu_ctx_create(int device, mu_ctx **out) {
+  if (!out)
+    return MU_ERR_INVALID;
+  *out = nullptr;
+  mu_ctx *ctx = new (std::nothrow) mu_ctx();
+  if (!ctx)
+    return MU_ERR_NOMEM;
+  ctx->device = device;
+  cudaError_t e = cudaSetDevice(device);
+  cudaDeviceProp prop;
+  if (e == cudaSuccess)
+    e = cudaGetDeviceProperties(&prop, device);
+  if (e == cudaSuccess && prop.major != 10) {
+    // Built for sm_100a only; there is no other code path.
+    fprintf(stderr, "munet_b200: device %d is sm_%d%d, this library only runs on sm_100\n", device,
+            prop.major, prop.minor);
+    delete ctx;
+    return MU_ERR_UNSUPPORTED;
+  }
+  if (e == cudaSuccess)
+    e = cudaMalloc(&ctx->d_status, sizeof(int));
+  if (e == cudaSuccess)
+    e = cudaMemset(ctx->d_status, 0, sizeof(int));
+  if (e != cudaSuccess) {
+    fprintf(stderr, "munet_b200: context creation failed: %s\n", cudaGetErrorString(e));
+    delete ctx;
+    return MU_ERR_CUDA;
+  }
+  ctx->num_sms = prop.multiProcessorCount;
+  *out = ctx;
+  return MU_OK;
+}
+
+void mu_ctx_destroy(mu_ctx *ctx) {
+  if (!ctx)
+    return;
+  if (ctx->d_status)
+    cudaFree(ctx->d_status);
+  delete ctx;
+}
+
+const char *mu_last_error(const mu_ctx *ctx) { return ctx ? ctx->err : "null context"; }
+int mu_ctx_num_sms(const mu_ctx *ctx) { return ctx ? ctx->num_sms : 0; }
+int mu_ctx_force_simt(mu_ctx *ctx, int on) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  ctx->force_simt = on;
+  return MU_OK;
+}
+
+int mu_alloc(mu_ctx *ctx, size_t bytes, void **ptr) {
+  if (!ctx || !ptr)
+    return MU_ERR_INVALID;
+  *ptr = nullptr;
+  if (bytes == 0)
+    return MU_OK;
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "mu_alloc: cannot select device");
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    return fail(ctx, MU_ERR_NOMEM, "mu_alloc: out of device memory (%zu bytes)", bytes);
+  }
+  if (e != cudaSuccess)
+    return cuda_fail(ctx, "mu_alloc", e);
+  return MU_OK;
+}
+
+int mu_free(mu_ctx *ctx, void *ptr) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  if (!ptr)
+    return MU_OK;
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? MU_OK : cuda_fail(ctx, "mu_free", e);
+}
+
+int mu_copy(mu_ctx *ctx, void *dst, const void *src, size_t bytes, int kind, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  if (bytes == 0)
+    return MU_OK;
+  MU_REQUIRE(dst && src, "mu_copy: null pointer");
+  cudaMemcpyKind k;
+  if (kind == MU_COPY_H2D)
+    k = cudaMemcpyHostToDevice;
+  else if (kind == MU_COPY_D2H)
+    k = cudaMemcpyDeviceToHost;
+  else if (kind == MU_COPY_D2D)
+    k = cudaMemcpyDeviceToDevice;
+  else
+    return fail(ctx, MU_ERR_INVALID, "mu_copy: unknown kind %d", kind);
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "mu_copy: cannot select device");
+  cudaError_t e = cudaMemcpyAsync(dst, src, bytes, k, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MU_OK : cuda_fail(ctx, "mu_copy", e);
+}
+
+int mu_synchronize(mu_ctx *ctx) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "mu_synchronize: cannot select device");
+  cudaError_t e = cudaDeviceSynchronize();
+  return e == cudaSuccess ? MU_OK : cuda_fail(ctx, "mu_synchronize", e);
+}
+
+int mu_check(mu_ctx *ctx, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "mu_check: cannot select device");
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess)
+    return cuda_fail(ctx, "mu_check", e);
+  int st = 0;
+  e = cudaMemcpy(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess)
+    return cuda_fail(ctx, "mu_check", e);
+  if (st == 0)
+    return MU_OK;
+  cudaMemset(ctx->d_status, 0, sizeof(int));
+  if (st == 110)
+    return fail(ctx, MU_ERR_INDEX, "Embedding index out of range");
+  return fail(ctx, MU_ERR_TIMEOUT, "device-side bounded wait ran out (code %d)", st);
+}
+
+int mu_matmul(mu_ctx *ctx, const void *a, const void *b, void *c, int M, int K, int N, int transA,
+              int transB, int dtype, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(M >= 0 && K >= 0 && N >= 0, "matmul: negative dimension");
+  if (transA)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "matmul: transA is a training-only path");
+  if (M == 0 || N == 0)
+    return MU_OK;
+  MU_REQUIRE(a && b && c, "matmul: null pointer");
+  mu::GemmOperands op;
+  op.a = a, op.lda = K, op.b = b, op.ldb = transB ? K : N, op.b_kmajor = transB ? 1 : 0;
+  mu::GemmShape sh{M, N, K, 1};
+  mu::Epilogue ep;
+  ep.c = c, ep.ldc = N, ep.round_each = 1;
+  return run_gemm(ctx, op, sh, ep, dtype, static_cast<cudaStream_t>(stream), "matmul");
+}
+
+int mu_batched_matmul(mu_ctx *ctx, const void *a, const void *b, void *c, int batch, int M, int K,
+                      int N, int transA, int transB, long long stride_a, long long stride_b,
+                      long long stride_out, int dtype, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(batch >= 0 && M >= 0 && K >= 0 && N >= 0, "batched_matmul: negative dimension");
+  if (transA)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "batched_matmul: transA is a training-only path");
+  if (batch == 0 || M == 0 || N == 0)
+    return MU_OK;
+  MU_REQUIRE(a && b && c, "batched_matmul: null pointer");
+  mu::Epilogue ep;
+  ep.c = c, ep.ldc = N, ep.round_each = 1;
+  if (stride_b == 0 && stride_a == 1ll * M * K && stride_out == 1ll * M * N &&
+      1ll * batch * M < 2147483647ll) {
+    // broadcast weights over a dense batch (how a 3-D Linear input arrives,
+    // src/core/ops/matmul.cpp:300-326): fold the batch into M.
+    mu::GemmOperands op;
+  op.a = a, op.lda = K, op.b = b, op.ldb = transB ? K : N, op.b_kmajor = transB ? 1 : 0;
+    mu::GemmShape sh{batch * M, N, K, 1};
+    return run_gemm(ctx, op, sh, ep, dtype, static_cast<cudaStream_t>(stream), "batched_matmul");
+  }
+  mu::GemmOperands op;
+  op.a = a, op.lda = K, op.a_batch = stride_a, op.b = b, op.ldb = transB ? K : N;
+  op.b_batch = stride_b, op.b_kmajor = transB ? 1 : 0;
+  mu::GemmShape sh{M, N, K, batch};
+  ep.batch_hi = stride_out, ep.batch_div = 1;
+  return run_gemm(ctx, op, sh, ep, dtype, static_cast<cudaStream_t>(stream), "batched_matmul");
+}
+
+int mu_linear(mu_ctx *ctx, const void *x, const void *w, const void *bias, const void *residual,
+              void *y, int M, int K, int N, int act, int dtype, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(M >= 0 && K >= 0 && N >= 0, "linear: negative dimension");
+  MU_REQUIRE(act >= MU_ACT_NONE && act <= MU_ACT_TANH, "linear: unknown activation %d", act);
+  if (M == 0 || N == 0)
+    return MU_OK;
+  MU_REQUIRE(x && w && y, "linear: null pointer");
+  mu::GemmOperands op;
+  op.a = x, op.lda = K, op.b = w, op.ldb = N;
+  mu::GemmShape sh{M, N, K, 1};
+  mu::Epilogue ep;
+  ep.c = y, ep.bias = bias, ep.residual = residual, ep.act = act, ep.ldc = N, ep.round_each = 1;
+  return run_gemm(ctx, op, sh, ep, dtype, static_cast<cudaStream_t>(stream), "linear");
+}
+
+int mu_linear_qkv(mu_ctx *ctx, const void *x, const void *w_qkv, const void *bias_qkv, void *q,
+                  void *k, void *v, int B, int T, int E, int H, int dtype, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(B >= 0 && T >= 0 && E > 0 && H > 0 && E % H == 0, "linear_qkv: bad dimensions");
+  if (B == 0 || T == 0)
+    return MU_OK;
+  MU_REQUIRE(x && w_qkv && q && k && v, "linear_qkv: null pointer");
+  const long long per = 1ll * B * T * E;
+  const size_t es = esize(dtype);
+  // q, k, v are addressed from q with one stride; they may be separate buffers
+  const long long dk = (static_cast<const char *>(k) - static_cast<const char *>(q));
+  const long long dv = (static_cast<const char *>(v) - static_cast<const char *>(q));
+  mu::GemmOperands op;
+  op.a = x, op.lda = E, op.b = w_qkv, op.ldb = 3ll * E;
+  mu::Epilogue ep;
+  ep.bias = bias_qkv, ep.round_each = 1;
+  ep.split_T = T, ep.split_H = H, ep.split_D = E / H;
+  if (dk == static_cast<long long>(per * es) && dv == 2 * dk) {
+    mu::GemmShape sh{B * T, 3 * E, E, 1};
+    ep.c = q, ep.split_which_stride = per;
+    return run_gemm(ctx, op, sh, ep, dtype, static_cast<cudaStream_t>(stream), "linear_qkv");
+  }
+  // separate destinations: three GEMMs over column slices of the fused weight
+  void *outs[3] = {q, k, v};
+  for (int i = 0; i < 3; ++i) {
+    mu::GemmOperands opi = op;
+    opi.b = static_cast<const char *>(w_qkv) + 1ll * i * E * es;
+    mu::Epilogue epi = ep;
+    epi.c = outs[i];
+    epi.bias = bias_qkv ? static_cast<const char *>(bias_qkv) + 1ll * i * E * es : nullptr;
+    epi.split_which_stride = 0;
+    mu::GemmShape sh{B * T, E, E, 1};
+    int rc = run_gemm(ctx, opi, sh, epi, dtype, static_cast<cudaStream_t>(stream), "linear_qkv");
+    if (rc)
+      return rc;
+  }
+  return MU_OK;
+}
+
+size_t mu_attention_workspace_bytes(int B, int H, int T, int D, int dtype) {
+  (void)D;
+  if (B <= 0 || H <= 0 || T <= 0)
+    return 0;
+  // one [B*H, T, T] score/probability buffer (softmax runs in place)
+  return static_cast<size_t>(B) * H * T * T * esize(dtype);
+}
+
+int mu_attention(mu_ctx *ctx, const void *q, const void *k, const void *v, void *out, int B, int H,
+                 int T, int D, int causal, int kmode, int dtype, void *workspace,
+                 size_t workspace_bytes, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(B >= 0 && H > 0 && T >= 0 && D > 0, "attention: bad dimensions");
+  MU_REQUIRE(kmode == MU_K_LITERAL || kmode == MU_K_MATH, "attention: unknown kmode %d", kmode);
+  if (dtype != MU_F32 && dtype != MU_BF16)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "attention: dtype %d not implemented", dtype);
+  if (B == 0 || T == 0)
+    return MU_OK;
+  MU_REQUIRE(q && k && v && out, "attention: null pointer");
+  MU_REQUIRE(workspace && workspace_bytes >= mu_attention_workspace_bytes(B, H, T, D, dtype),
+             "attention: workspace too small (%zu < %zu bytes)", workspace_bytes,
+             mu_attention_workspace_bytes(B, H, T, D, dtype));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int BH = B * H;
+  const long long Ntot = 1ll * BH * T;
+  const int E = H * D;
+  // S = scale * Q·K'   (scale is a separately rounded multiply in the reference)
+  {
+    mu::GemmOperands op;
+    op.a = q, op.lda = D, op.a_batch = 1ll * T * D;
+    op.b = k;
+    if (kmode == MU_K_LITERAL) {
+      // K's [N,D] buffer read as row-major [D,N]; head block bh = columns bh*T..
+      op.b_kmajor = 0, op.ldb = Ntot, op.b_batch = T, op.b_col_per_batch = T;
+    } else {
+      op.b_kmajor = 1, op.ldb = D, op.b_batch = 1ll * T * D;
+    }
+    mu::GemmShape sh{T, T, D, BH};
+    mu::Epilogue ep;
+    ep.c = workspace, ep.ldc = T, ep.batch_hi = 1ll * T * T, ep.batch_div = 1;
+    ep.alpha = 1.0f / sqrtf(static_cast<float>(D));
+    ep.round_each = 1;
+    int rc = run_gemm(ctx, op, sh, ep, dtype, st, "attention(scores)");
+    if (rc)
+      return rc;
+  }
+  int rc = mu::launch_softmax(workspace, workspace, Ntot, T, 1.0f, causal ? T : 0, 0, dtype, st);
+  if (rc)
+    return cuda_fail(ctx, "attention(softmax)", cudaGetLastError());
+  {
+    mu::GemmOperands op;
+    op.a = workspace, op.lda = T, op.a_batch = 1ll * T * T;
+    op.b = v, op.b_kmajor = 0, op.ldb = D, op.b_batch = 1ll * T * D;
+    mu::GemmShape sh{T, D, T, BH};
+    mu::Epilogue ep;
+    ep.c = out, ep.ldc = E, ep.batch_div = H, ep.batch_hi = 1ll * T * E, ep.batch_lo = D;
+    ep.round_each = 1;
+    return run_gemm(ctx, op, sh, ep, dtype, st, "attention(context)");
+  }
+}
+
+int mu_layer_norm(mu_ctx *ctx, const void *x, const void *gamma, const void *beta, void *y,
+                  long long rows, int cols, float eps, int dtype, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(rows >= 0 && cols > 0, "LayerNorm: input must have at least 1 dim");
+  if (rows == 0)
+    return MU_OK;
+  MU_REQUIRE(x && gamma && beta && y, "LayerNorm: null pointer");
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "LayerNorm: cannot select device");
+  int rc = mu::launch_layer_norm(x, gamma, beta, y, rows, cols, eps, dtype,
+                                 static_cast<cudaStream_t>(stream));
+  if (rc == 1)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "LayerNorm: dtype %d not implemented", dtype);
+  return rc ? cuda_fail(ctx, "LayerNorm", cudaGetLastError()) : MU_OK;
+}
+
+int mu_softmax(mu_ctx *ctx, const void *x, void *y, long long rows, int cols, int dtype,
+               void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(rows >= 0 && cols > 0, "Softmax expects non-empty shape");
+  if (rows == 0)
+    return MU_OK;
+  MU_REQUIRE(x && y, "Softmax: null pointer");
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "Softmax: cannot select device");
+  int rc = mu::launch_softmax(x, y, rows, cols, 1.0f, 0, 0, dtype, static_cast<cudaStream_t>(stream));
+  if (rc == 1)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "Softmax: dtype %d not implemented", dtype);
+  return rc ? cuda_fail(ctx, "Softmax", cudaGetLastError()) : MU_OK;
+}
+
+int mu_embedding(mu_ctx *ctx, const int32_t *ids, const void *table, const void *pos, void *out,
+                 int B, int T, int V, int D, int dtype, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(V > 0 && D > 0, "Embedding expects positive num_embeddings and embedding_dim");
+  MU_REQUIRE(B >= 0 && T >= 0, "Embedding: negative dimension");
+  if (B == 0 || T == 0)
+    return MU_OK;
+  MU_REQUIRE(ids && table && out, "Embedding: null pointer");
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "Embedding: cannot select device");
+  int rc = mu::launch_embedding(ids, table, pos, out, 1ll * B * T, T, V, D, dtype, ctx->d_status,
+                                static_cast<cudaStream_t>(stream));
+  if (rc == 1)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "Embedding: dtype %d not implemented", dtype);
+  return rc ? cuda_fail(ctx, "Embedding", cudaGetLastError()) : MU_OK;
+}
+
+int mu_eltwise(mu_ctx *ctx, const void *x, const void *bias, const void *residual, void *y,
+               long long n, int cols, int act, int dtype, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(n >= 0, "eltwise: negative size");
+  MU_REQUIRE(act >= MU_ACT_NONE && act <= MU_ACT_TANH, "eltwise: unknown activation %d", act);
+  if (n == 0)
+    return MU_OK;
+  MU_REQUIRE(x && y, "eltwise: null pointer");
+  MU_REQUIRE(!bias || cols > 0, "eltwise: bias needs cols > 0");
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "eltwise: cannot select device");
+  int rc = mu::launch_eltwise(x, bias, residual, y, n, cols, act, dtype, ctx->num_sms,
+                              static_cast<cudaStream_t>(stream));
+  if (rc == 1)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "eltwise: dtype %d not implemented", dtype);
+  return rc ? cuda_fail(ctx, "eltwise", cudaGetLastError()) : MU_OK;
+}
+
+int mu_argmax(mu_ctx *ctx, const void *x, int32_t *idx, long long rows, int cols, int dtype,
+              void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(rows >= 0 && cols > 0, "argmax: bad shape");
+  if (rows == 0)
+    return MU_OK;
+  MU_REQUIRE(x && idx, "argmax: null pointer");
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "argmax: cannot select device");
+  int rc = mu::launch_argmax(x, idx, rows, cols, dtype, static_cast<cudaStream_t>(stream));
+  if (rc == 1)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "argmax: dtype %d not implemented", dtype);
+  return rc ? cuda_fail(ctx, "argmax", cudaGetLastError()) : MU_OK;
+}
+
+} // extern "C"

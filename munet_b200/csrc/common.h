@@ -1,0 +1,64 @@
+// Internal shared definitions for the kernels and their host launchers.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace mu {
+
+// dtype codes follow the MuNet DataType enum order (src/types.hpp:16).
+enum DType : int { F32 = 0, F16 = 1, BF16 = 2, I32 = 3 };
+enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_SIGMOID = 3, ACT_TANH = 4 };
+
+// Where an output element (batch, m, n) of a GEMM goes, and what happens to
+// the accumulator on the way. The same addressing is used for the residual.
+struct Epilogue {
+  void *c = nullptr;              // output base
+  const void *bias = nullptr;     // [N], same dtype as c, or null
+  const void *residual = nullptr; // same addressing as c, or null
+  float alpha = 1.0f;             // accumulator scale (1 = none)
+  int act = ACT_NONE;
+  int round_each = 1; // bf16 only: round to bf16 after every op like the reference's
+                      // per-op typed loops (src/core/ops/common.hpp:46-85)
+  long long ldc = 0;  // row stride in elements
+  // batch b lives at (b / batch_div) * batch_hi + (b % batch_div) * batch_lo
+  long long batch_hi = 0, batch_lo = 0;
+  int batch_div = 1;
+  // Head-split store (QKV projection → head-major [which][B·H][T][D]):
+  // enabled when split_T > 0. Row m = b·T + t, column n = which·(H·D) + h·D + d.
+  int split_T = 0, split_H = 0, split_D = 0;
+  long long split_which_stride = 0;
+  int vec_ok = 0; // host-verified: 16-byte aligned rows/pointers → 128-bit stores allowed
+};
+
+struct GemmShape {
+  int M = 0, N = 0, K = 0, batch = 1;
+  // tcgen05 kernel only: how the batch index reaches the operands' tensor maps.
+  int a_batched = 1;        // third TMA coordinate of A = batch index (else 0)
+  int b_batched = 1;        // third TMA coordinate of B = batch index (else 0)
+  int b_col_per_batch = 0;  // added to B's N coordinate per batch (B = column slab of a wide matrix)
+};
+
+// Operand addressing in elements. A is row-major [M,K]. B is row-major [K,N]
+// (b_kmajor = 0, how MuNet stores Linear weights) or row-major [N,K]
+// (b_kmajor = 1, "B transposed"). A batch stride of 0 shares the operand.
+struct GemmOperands {
+  const void *a = nullptr;
+  long long lda = 0, a_batch = 0;
+  const void *b = nullptr;
+  long long ldb = 0, b_batch = 0;
+  int b_kmajor = 0;
+  // B of batch i is the column slab [i*b_col_per_batch, ...) of one wide row-major
+  // [K, ldb] matrix (b_kmajor = 0 only). Used for the reference's literal K addressing.
+  long long b_col_per_batch = 0;
+};
+
+struct SimtArgs {
+  const void *a, *b;
+  long long lda, ldb, a_batch, b_batch;
+  int b_kmajor;
+  int is_bf16;
+  GemmShape sh;
+  Epilogue ep;
+};
+
+} // namespace mu

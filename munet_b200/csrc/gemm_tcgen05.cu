@@ -1,0 +1,464 @@
+// bf16 GEMM for sm_100a: C = epilogue(A · B), fp32 accumulation in TMEM.
+//
+// The B200 replacement for the reference's `BackendBlasCapability::matmul` /
+// `batched_matmul` (src/core/backend.hpp:250-260) fused with the broadcast bias
+// add of nn::Linear (src/nn/linear.hpp:28-34), the activation module that
+// follows it and the residual add of the decoder block.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0   TMA producer: A [128 x 64] and B [64 x BN] tiles, 128-byte swizzle,
+//            STAGES-deep mbarrier ring. No cluster multicast anywhere.
+//   warp 1   allocates TMEM and issues tcgen05.mma (kind::f16, M=128, N=BN, K=16)
+//            from one thread; accumulators are double-buffered in TMEM so the
+//            epilogue of tile i overlaps the main loop of tile i+1.
+//   warps 2-5 epilogue: tcgen05.ld 32 lanes x 32 columns, scale / bias /
+//            activation / residual in registers, 128-bit stores.
+// A is row-major [M,K] (K-major operand). B is either row-major [K,N] as MuNet
+// stores Linear weights (MN-major operand) or row-major [N,K] (K-major, "B
+// transposed"). All operands may be batched through a third tensor-map dim.
+// Tails in M, N and K are handled by TMA zero fill and guarded stores.
+#include "common.h"
+#include "ptx.cuh"
+#include <cuda.h>
+
+namespace mu {
+
+constexpr int BM = 128;
+constexpr int BK = 64; // 64 bf16 = 128 bytes = one swizzle row
+constexpr int GEMM_THREADS = 192;
+
+template <int BN> struct GemmCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float epi_math(float x, float bias, float res, bool has_bias,
+                                          bool has_res, float alpha, int act, bool rnd) {
+  if (rnd)
+    x = bf16_round(x);
+  if (alpha != 1.0f) {
+    x = x * alpha;
+    if (rnd)
+      x = bf16_round(x);
+  }
+  if (has_bias) {
+    x = x + bias;
+    if (rnd)
+      x = bf16_round(x);
+  }
+  if (act == ACT_RELU) {
+    x = fmaxf(x, 0.0f);
+  } else if (act == ACT_GELU) {
+    // x * sigmoid(1.702 x): the reference's GELU (src/nn/activations.hpp:31-38)
+    const float c = rnd ? bf16_round(1.702f) : 1.702f;
+    float t = x * c;
+    if (rnd)
+      t = bf16_round(t);
+    float s = 1.0f / (1.0f + __expf(-t));
+    if (rnd)
+      s = bf16_round(s);
+    x = x * s;
+    if (rnd)
+      x = bf16_round(x);
+  } else if (act == ACT_SIGMOID) {
+    x = 1.0f / (1.0f + __expf(-x));
+    if (rnd)
+      x = bf16_round(x);
+  } else if (act == ACT_TANH) {
+    // sigmoid(2x)*2 - 1 (src/nn/activations.hpp:20-29)
+    float t = x * 2.0f;
+    float s = 1.0f / (1.0f + __expf(-t));
+    if (rnd)
+      s = bf16_round(s);
+    x = s * 2.0f;
+    x = x - 1.0f;
+    if (rnd)
+      x = bf16_round(x);
+  }
+  if (has_res) {
+    x = x + res;
+    if (rnd)
+      x = bf16_round(x);
+  }
+  return x;
+}
+
+template <int BN, bool B_KMAJOR>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmB, GemmShape sh, Epilogue ep,
+                         int *status) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128-byte swizzle atoms.
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t *bar_base = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(bar_base);
+  uint64_t *empty_bar = full_bar + STAGES;
+  uint64_t *tfull_bar = empty_bar + STAGES;
+  uint64_t *tempty_bar = tfull_bar + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty_bar + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (sh.M + BM - 1) / BM;
+  const int tiles_n = (sh.N + BN - 1) / BN;
+  const int num_kb = (sh.K + BK - 1) / BK;
+  const long long total_tiles = 1ll * tiles_m * tiles_n * sh.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 4);
+    }
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int nt = static_cast<int>(tile % tiles_n);
+        const int mt = static_cast<int>((tile / tiles_n) % tiles_m);
+        const int bt = static_cast<int>(tile / (1ll * tiles_n * tiles_m));
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t *sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t *sb = sa + Cfg::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          const int bta = sh.a_batched ? bt : 0, btb = sh.b_batched ? bt : 0;
+          tma_load_3d(sa, &tmA, &full_bar[stage], kb * BK, mt * BM, bta);
+          if (B_KMAJOR) {
+            tma_load_3d(sb, &tmB, &full_bar[stage], kb * BK, nt * BN, btb);
+          } else {
+            const int c0 = nt * BN + bt * sh.b_col_per_batch;
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sb + j * 8192, &tmB, &full_bar[stage], c0 + j * 64, kb * BK, btb);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // let copies already in flight land before the CTA's memory is released
+        for (int i = 0; i < 64; ++i)
+          __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(1u, 0u, B_KMAJOR ? 0u : 1u, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t use = static_cast<uint32_t>(it >> 1);
+        if (!mbar_wait(&tempty_bar[buf], (use & 1) ^ 1)) {
+          atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = B_KMAJOR ? make_smem_desc(sb + k * 32, 16, 1024)
+                                            : make_smem_desc(sb + k * 2048, 8192, 1024);
+            umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]); // smem slot reusable once these MMAs retire
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok)
+          umma_commit(&tfull_bar[buf]); // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int q = warp & 3; // TMEM lane quarter this warp may read
+    const bool rnd = ep.round_each != 0;
+    const float alpha = (rnd && ep.alpha != 1.0f) ? bf16_round(ep.alpha) : ep.alpha;
+    const __nv_bfloat16 *bias = static_cast<const __nv_bfloat16 *>(ep.bias);
+    const __nv_bfloat16 *resid = static_cast<const __nv_bfloat16 *>(ep.residual);
+    __nv_bfloat16 *cout = static_cast<__nv_bfloat16 *>(ep.c);
+    const bool split = ep.split_T > 0;
+    const int HD = ep.split_H * ep.split_D;
+    int it = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      const int nt = static_cast<int>(tile % tiles_n);
+      const int mt = static_cast<int>((tile / tiles_n) % tiles_m);
+      const int bt = static_cast<int>(tile / (1ll * tiles_n * tiles_m));
+      const int buf = it & 1;
+      const uint32_t use = static_cast<uint32_t>(it >> 1);
+      if (!mbar_wait(&tfull_bar[buf], use & 1)) {
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int m = mt * BM + q * 32 + lane;
+      const bool row_ok = m < sh.M;
+      const long long batch_off =
+          1ll * (bt / ep.batch_div) * ep.batch_hi + 1ll * (bt % ep.batch_div) * ep.batch_lo;
+      long long row_off;
+      if (split) {
+        const int b = m / ep.split_T, t = m % ep.split_T;
+        row_off = (1ll * b * ep.split_H * ep.split_T + t) * ep.split_D;
+      } else {
+        row_off = batch_off + 1ll * m * ep.ldc;
+      }
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        const int n0 = nt * BN + chunk * 32;
+        if (n0 >= sh.N)
+          break; // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                          static_cast<uint32_t>(buf * BN + chunk * 32),
+                      r);
+        tmem_ld_wait();
+        const bool full = (n0 + 32 <= sh.N) && ep.vec_ok;
+        if (full) {
+          long long off;
+          if (split) {
+            const int which = n0 / HD, rem = n0 % HD;
+            const int h = rem / ep.split_D, d = rem % ep.split_D;
+            off = which * ep.split_which_stride + row_off + 1ll * h * ep.split_T * ep.split_D + d;
+          } else {
+            off = row_off + n0;
+          }
+          uint32_t bw[16], rw[16];
+          if (bias) {
+            const uint4 *bp = reinterpret_cast<const uint4 *>(bias + n0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 t = __ldg(bp + j);
+              bw[4 * j] = t.x, bw[4 * j + 1] = t.y, bw[4 * j + 2] = t.z, bw[4 * j + 3] = t.w;
+            }
+          }
+          if (resid && row_ok) {
+            const uint4 *rp = reinterpret_cast<const uint4 *>(resid + off);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 t = rp[j];
+              rw[4 * j] = t.x, rw[4 * j + 1] = t.y, rw[4 * j + 2] = t.z, rw[4 * j + 3] = t.w;
+            }
+          }
+          uint32_t ow[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float b0 = bias ? bf16_lo(bw[j]) : 0.f, b1 = bias ? bf16_hi(bw[j]) : 0.f;
+            const float r0 = (resid && row_ok) ? bf16_lo(rw[j]) : 0.f;
+            const float r1 = (resid && row_ok) ? bf16_hi(rw[j]) : 0.f;
+            const float v0 = epi_math(__uint_as_float(r[2 * j]), b0, r0, bias != nullptr,
+                                      resid != nullptr, alpha, ep.act, rnd);
+            const float v1 = epi_math(__uint_as_float(r[2 * j + 1]), b1, r1, bias != nullptr,
+                                      resid != nullptr, alpha, ep.act, rnd);
+            ow[j] = pack_bf16x2(v0, v1);
+          }
+          if (row_ok) {
+            uint4 *op = reinterpret_cast<uint4 *>(cout + off);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              op[j] = make_uint4(ow[4 * j], ow[4 * j + 1], ow[4 * j + 2], ow[4 * j + 3]);
+          }
+        } else if (row_ok) {
+          for (int j = 0; j < 32; ++j) {
+            const int n = n0 + j;
+            if (n >= sh.N)
+              break;
+            long long off;
+            if (split) {
+              const int which = n / HD, rem = n % HD;
+              const int h = rem / ep.split_D, d = rem % ep.split_D;
+              off = which * ep.split_which_stride + row_off + 1ll * h * ep.split_T * ep.split_D + d;
+            } else {
+              off = row_off + n;
+            }
+            const float b = bias ? __bfloat162float(bias[n]) : 0.f;
+            const float rs = resid ? __bfloat162float(resid[off]) : 0.f;
+            // r[] must be indexed with a compile-time constant to stay in registers
+            float acc = 0.f;
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+              acc = (jj == j) ? __uint_as_float(r[jj]) : acc;
+            cout[off] = __float2bfloat16_rn(
+                epi_math(acc, b, rs, bias != nullptr, resid != nullptr, alpha, ep.act, rnd));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&tempty_bar[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1)
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault,
+                                         &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// rank-3 bf16 map, 128-byte swizzle. dims/strides in elements, inner stride 1.
+static bool encode_map3(CUtensorMap *map, const void *base, unsigned long long d0,
+                        unsigned long long d1, unsigned long long d2, unsigned long long s1,
+                        unsigned long long s2, unsigned b0, unsigned b1) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn)
+    return false;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {s1 * 2ull, s2 * 2ull};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Returns 0 ok, 1 shape/alignment not supported by this kernel, 2 launch/encode failure.
+int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const Epilogue &ep,
+                             int *status, int num_sms, cudaStream_t stream) {
+  if (sh.M <= 0 || sh.N <= 0 || sh.K <= 0 || sh.batch <= 0)
+    return 1;
+  if (!aligned16(op.a) || !aligned16(op.b) || (op.lda % 8) || (op.ldb % 8) ||
+      (op.a_batch % 8) || (op.b_batch % 8))
+    return 1;
+  GemmShape s2 = sh;
+  // An operand shared by every batch (stride 0) or addressed as a column slab is
+  // encoded with a single batch entry; its natural extent serves as the stride.
+  const bool b_slab = op.b_col_per_batch > 0;
+  if (b_slab && (op.b_kmajor || (op.b_col_per_batch % 8) || op.b_col_per_batch > 0x7fffffffll / sh.batch))
+    return 1;
+  s2.a_batched = (op.a_batch > 0 && sh.batch > 1) ? 1 : 0;
+  s2.b_batched = (op.b_batch > 0 && sh.batch > 1 && !b_slab) ? 1 : 0;
+  s2.b_col_per_batch = b_slab ? static_cast<int>(op.b_col_per_batch) : 0;
+  const unsigned long long a_nb = s2.a_batched ? sh.batch : 1;
+  const unsigned long long b_nb = s2.b_batched ? sh.batch : 1;
+  const unsigned long long a_bs = s2.a_batched ? op.a_batch : 1ull * op.lda * sh.M;
+  const int BN = sh.N > 128 ? 256 : (sh.N > 64 ? 128 : 64);
+  CUtensorMap tmA, tmB;
+  if (!encode_map3(&tmA, op.a, sh.K, sh.M, a_nb, op.lda, a_bs, BK, BM))
+    return 2;
+  bool okb;
+  if (op.b_kmajor) {
+    const unsigned long long b_bs = s2.b_batched ? op.b_batch : 1ull * op.ldb * sh.N;
+    okb = encode_map3(&tmB, op.b, sh.K, sh.N, b_nb, op.ldb, b_bs, BK, BN);
+  } else {
+    const unsigned long long cols = b_slab ? 1ull * op.b_col_per_batch * sh.batch : sh.N;
+    const unsigned long long b_bs = s2.b_batched ? op.b_batch : 1ull * op.ldb * sh.K;
+    okb = encode_map3(&tmB, op.b, cols, sh.K, b_nb, op.ldb, b_bs, 64, BK);
+  }
+  if (!okb)
+    return 2;
+  const long long tiles = 1ll * ((sh.M + BM - 1) / BM) * ((sh.N + BN - 1) / BN) * sh.batch;
+  const int grid = static_cast<int>(tiles < num_sms ? tiles : num_sms);
+
+#define MU_LAUNCH(BN_, KM_)                                                                      \
+  do {                                                                                           \
+    auto kern = gemm_bf16_tcgen05_kernel<BN_, KM_>;                                              \
+    static bool attr_set = false;                                                                \
+    if (!attr_set) {                                                                             \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
+                               GemmCfg<BN_>::SMEM_BYTES) != cudaSuccess)                         \
+        return 2;                                                                                \
+      attr_set = true;                                                                           \
+    }                                                                                            \
+    kern<<<grid, GEMM_THREADS, GemmCfg<BN_>::SMEM_BYTES, stream>>>(tmA, tmB, s2, ep, status);    \
+  } while (0)
+
+  if (op.b_kmajor) {
+    if (BN == 256)
+      MU_LAUNCH(256, true);
+    else if (BN == 128)
+      MU_LAUNCH(128, true);
+    else
+      MU_LAUNCH(64, true);
+  } else {
+    if (BN == 256)
+      MU_LAUNCH(256, false);
+    else if (BN == 128)
+      MU_LAUNCH(128, false);
+    else
+      MU_LAUNCH(64, false);
+  }
+#undef MU_LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+} // namespace mu

@@ -1,0 +1,249 @@
+"""GPU parity: every C-ABI entry point against the CPU checker (oracle/) on the
+same seeded inputs.  float32 tolerance 1e-4, bfloat16 2e-2, relative as defined
+in tests/util.close; float32 matmul/linear (none, relu) and argmax are bit-exact."""
+import numpy as np
+import pytest
+
+import oracle
+from oracle import BF16, F32, I32
+from tests.util import assert_close, empty_dev, rnd, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import munet_b200 as mb
+    c = mb.Context(0)
+    yield c
+    c.close()
+
+
+def dev_linear(ctx, x, w, b, dtype, act="none", res=None, simt=False):
+    M, K = x.shape
+    N = w.shape[1]
+    y = empty_dev((M, N), dtype)
+    ctx.force_simt(simt)
+    ctx.linear(to_dev(x, dtype), to_dev(w, dtype), None if b is None else to_dev(b, dtype), y,
+               M, K, N, dtype, act=act, residual=None if res is None else to_dev(res, dtype))
+    ctx.check()
+    ctx.force_simt(False)
+    return to_host(y)
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 64, 64), (128, 64, 256), (256, 512, 384), (1000, 328, 520),
+                                   (77, 40, 24), (2048, 1024, 1024)])
+@pytest.mark.parametrize("act", ["none", "gelu"])
+def test_linear_bf16_tcgen05(ctx, M, K, N, act):
+    rng = np.random.default_rng(M + K + N)
+    x = rnd(rng, (M, K), BF16)
+    w = rnd(rng, (K, N), BF16, 1.0 / np.sqrt(K))
+    b = rnd(rng, (N,), BF16, 0.02)
+    want = oracle.port().linear(x, w, b, BF16, act)
+    got = dev_linear(ctx, x, w, b, BF16, act)
+    assert_close(got, want, BF16, what="linear bf16")
+    got_simt = dev_linear(ctx, x, w, b, BF16, act, simt=True)
+    assert_close(got_simt, want, BF16, what="linear bf16 (cuda-core kernel)")
+
+
+@pytest.mark.parametrize("act", ["none", "relu", "gelu", "sigmoid", "tanh"])
+def test_linear_bf16_acts_residual(ctx, act):
+    rng = np.random.default_rng(5)
+    M, K, N = 300, 256, 512
+    x, w = rnd(rng, (M, K), BF16), rnd(rng, (K, N), BF16, 1.0 / 16)
+    b, r = rnd(rng, (N,), BF16, 0.1), rnd(rng, (M, N), BF16)
+    want = oracle.port().add(oracle.port().linear(x, w, b, BF16, act), r, BF16)
+    assert_close(dev_linear(ctx, x, w, b, BF16, act, res=r), want, BF16, what=f"linear+{act}+res")
+    want_nb = oracle.port().linear(x, w, None, BF16, act)
+    assert_close(dev_linear(ctx, x, w, None, BF16, act), want_nb, BF16, what="linear no bias")
+
+
+@pytest.mark.parametrize("M,K,N", [(256, 784, 512), (256, 512, 10), (33, 17, 5), (1, 64, 3)])
+@pytest.mark.parametrize("act", ["none", "relu"])
+def test_linear_f32_bit_exact(ctx, M, K, N, act):
+    rng = np.random.default_rng(M * 3 + N)
+    x = rng.random((M, K), dtype=np.float32)
+    w = rnd(rng, (K, N), F32, np.sqrt(2.0 / K))
+    b = rnd(rng, (N,), F32, 0.1)
+    want = oracle.port().linear(x, w, b, F32, act)
+    got = dev_linear(ctx, x, w, b, F32, act)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), \
+        f"max diff {np.abs(got - want).max()}"
+
+
+@pytest.mark.parametrize("act", ["gelu", "sigmoid", "tanh"])
+def test_linear_f32_acts(ctx, act):
+    rng = np.random.default_rng(9)
+    x, w, b = rnd(rng, (64, 96), F32), rnd(rng, (96, 80), F32, 0.1), rnd(rng, (80,), F32, 0.1)
+    assert_close(dev_linear(ctx, x, w, b, F32, act), oracle.port().linear(x, w, b, F32, act), F32)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("transB", [False, True])
+def test_matmul_and_batched(ctx, dtype, transB):
+    rng = np.random.default_rng(11)
+    M, K, N, batch = 96, 128, 64, 5
+    a = rnd(rng, (batch, M, K), dtype)
+    b = rnd(rng, (batch, K, N), dtype, 1.0 / np.sqrt(K))
+    want = np.stack([oracle.port().matmul(a[i], b[i], dtype) for i in range(batch)])
+    bd = np.ascontiguousarray(np.swapaxes(b, 1, 2)) if transB else b
+    c = empty_dev((batch, M, N), dtype)
+    ctx.batched_matmul(to_dev(a, dtype), to_dev(bd, dtype), c, batch, M, K, N, M * K, K * N, M * N,
+                       dtype, transB=transB)
+    ctx.check()
+    assert_close(to_host(c), want, dtype, what="batched_matmul")
+    # broadcast weights (stride_b = 0): how a 3-D Linear input reaches the backend
+    want0 = np.stack([oracle.port().matmul(a[i], b[0], dtype) for i in range(batch)])
+    ctx.batched_matmul(to_dev(a, dtype), to_dev(bd[0], dtype), c, batch, M, K, N, M * K, 0, M * N,
+                       dtype, transB=transB)
+    ctx.check()
+    assert_close(to_host(c), want0, dtype, what="batched_matmul broadcast")
+    c2 = empty_dev((M, N), dtype)
+    ctx.matmul(to_dev(a[1], dtype), to_dev(bd[1], dtype), c2, M, K, N, dtype, transB=transB)
+    ctx.check()
+    assert_close(to_host(c2), want[1], dtype, what="matmul")
+
+
+def test_matmul_transA_is_rejected(ctx):
+    import munet_b200 as mb
+    t = empty_dev((4, 4), F32)
+    with pytest.raises(mb.MuNetError):
+        ctx.matmul(t, t, t, 4, 4, 4, F32, transA=True)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("rows,cols", [(64, 512), (1000, 2048), (7, 200), (5, 33), (3, 4096)])
+def test_layer_norm(ctx, dtype, rows, cols):
+    rng = np.random.default_rng(rows + cols)
+    x = rnd(rng, (rows, cols), dtype, 2.0)
+    g, b = rnd(rng, (cols,), dtype), rnd(rng, (cols,), dtype)
+    y = empty_dev((rows, cols), dtype)
+    ctx.layer_norm(to_dev(x, dtype), to_dev(g, dtype), to_dev(b, dtype), y, rows, cols, dtype)
+    ctx.check()
+    assert_close(to_host(y), oracle.port().layer_norm(x, g, b, dtype), dtype, what="layer_norm")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("rows,cols", [(64, 256), (100, 1024), (9, 33), (4, 5000)])
+def test_softmax(ctx, dtype, rows, cols):
+    rng = np.random.default_rng(rows * cols)
+    x = rnd(rng, (rows, cols), dtype, 3.0)
+    y = empty_dev((rows, cols), dtype)
+    ctx.softmax(to_dev(x, dtype), y, rows, cols, dtype)
+    ctx.check()
+    got, want = to_host(y), oracle.port().softmax(x, dtype)
+    assert_close(got, want, dtype, what="softmax")
+    assert np.allclose(oracle.as_float(got, dtype).sum(-1), 1.0, atol=2e-2 if dtype == BF16 else 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_embedding(ctx, dtype):
+    import munet_b200 as mb
+    rng = np.random.default_rng(3)
+    B, T, V, D = 3, 17, 100, 64
+    table, pos = rnd(rng, (V, D), dtype), rnd(rng, (T, D), dtype)
+    ids = rng.integers(0, V, (B, T)).astype(np.int32)
+    out = empty_dev((B, T, D), dtype)
+    ctx.embedding(to_dev(ids, I32), to_dev(table, dtype), None, out, B, T, V, D, dtype)
+    ctx.check()
+    want = oracle.port().embedding(ids, table, dtype)
+    assert np.array_equal(to_host(out), want)
+    ctx.embedding(to_dev(ids, I32), to_dev(table, dtype), to_dev(pos, dtype), out, B, T, V, D, dtype)
+    ctx.check()
+    want_pos = np.stack([oracle.port().add(want[b], pos, dtype) for b in range(B)])
+    assert np.array_equal(to_host(out), want_pos)
+    bad = ids.copy()
+    bad[1, 2] = V  # the reference throws "Embedding index out of range"
+    ctx.embedding(to_dev(bad, I32), to_dev(table, dtype), None, out, B, T, V, D, dtype)
+    with pytest.raises(mb.MuNetError, match="out of range"):
+        ctx.check()
+    ctx.check()  # status is cleared after being reported
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("act", ["relu", "gelu", "sigmoid", "tanh"])
+def test_eltwise(ctx, dtype, act):
+    rng = np.random.default_rng(4)
+    for n in (4096, 1001):
+        x = rnd(rng, (n,), dtype, 2.0)
+        y = empty_dev((n,), dtype)
+        ctx.eltwise(to_dev(x, dtype), y, n, dtype, act=act)
+        ctx.check()
+        assert_close(to_host(y), oracle.port().activation(x, dtype, act), dtype, what=act)
+    a, b = rnd(rng, (64, 48), dtype), rnd(rng, (64, 48), dtype)
+    y = empty_dev((64, 48), dtype)
+    ctx.eltwise(to_dev(a, dtype), y, a.size, dtype, residual=to_dev(b, dtype))
+    ctx.check()
+    want = oracle.port().add(a, b, dtype)
+    if dtype == F32:
+        assert np.array_equal(to_host(y), want)
+    else:
+        assert_close(to_host(y), want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_argmax_first_max(ctx, dtype):
+    rng = np.random.default_rng(6)
+    x = rnd(rng, (50, 1000), dtype)
+    xf = oracle.as_float(x, dtype).copy()
+    xf[3, 10] = xf[3, 500] = 100.0  # tie: the first index wins
+    x = xf if dtype == F32 else oracle.to_bf16(xf)
+    idx = empty_dev((50,), I32)
+    ctx.argmax(to_dev(x, dtype), idx, 50, 1000, dtype)
+    ctx.check()
+    want = oracle.port().argmax(x, dtype)
+    assert np.array_equal(to_host(idx), want) and want[3] == 10
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("kmode", [oracle.K_LITERAL, oracle.K_MATH])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("B,H,T,D", [(2, 4, 64, 64), (1, 2, 256, 128), (2, 2, 24, 16), (1, 3, 10, 8)])
+def test_attention_core(ctx, dtype, kmode, causal, B, H, T, D):
+    rng = np.random.default_rng(B * 1000 + T + D)
+    n = B * H * T
+    q, k, v = (rnd(rng, (n, D), dtype) for _ in range(3))
+    want_hm = oracle.port().attention_core(q, k, v, B * H, T, D, causal, dtype, kmode)
+    # merge heads: [B,H,T,D] -> [B,T,H*D]
+    want = np.ascontiguousarray(want_hm.reshape(B, H, T, D).transpose(0, 2, 1, 3)).reshape(B * T, H * D)
+    out = empty_dev((B * T, H * D), dtype)
+    nbytes = ctx.attention_workspace_bytes(B, H, T, D, dtype)
+    import torch
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    ctx.attention(to_dev(q, dtype), to_dev(k, dtype), to_dev(v, dtype), out, B, H, T, D, causal,
+                  kmode, dtype, ws, nbytes)
+    ctx.check()
+    assert_close(to_host(out), want, dtype, what="attention")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("B,T,E,H", [(2, 64, 256, 4), (1, 24, 48, 3)])
+def test_linear_qkv_head_major(ctx, dtype, B, T, E, H):
+    rng = np.random.default_rng(E)
+    x = rnd(rng, (B * T, E), dtype)
+    ws = [rnd(rng, (E, E), dtype, 1 / np.sqrt(E)) for _ in range(3)]
+    bs = [rnd(rng, (E,), dtype, 0.1) for _ in range(3)]
+    wqkv = np.ascontiguousarray(np.concatenate(ws, axis=1))
+    bqkv = np.concatenate(bs)
+    D = E // H
+    qkv = empty_dev((3, B * H * T, D), dtype)
+    ctx.linear_qkv(to_dev(x, dtype), to_dev(wqkv, dtype), to_dev(bqkv, dtype), qkv[0], qkv[1], qkv[2],
+                   B, T, E, H, dtype)
+    ctx.check()
+    got = to_host(qkv)
+    for i in range(3):
+        y = oracle.port().linear(x, ws[i], bs[i], dtype)
+        hm = np.ascontiguousarray(y.reshape(B, T, H, D).transpose(0, 2, 1, 3)).reshape(B * H * T, D)
+        if dtype == F32:
+            assert np.array_equal(got[i], hm)
+        else:
+            assert_close(got[i], hm, dtype, what="qkv")
+
+
+def test_empty_inputs(ctx):
+    t = empty_dev((8,), F32)
+    ctx.linear(t, t, None, t, 0, 4, 4, F32)
+    ctx.layer_norm(t, t, t, t, 0, 8, F32)
+    ctx.softmax(t, t, 0, 8, F32)
+    ctx.eltwise(t, t, 0, F32, act="relu")
+    ctx.check()
