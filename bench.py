@@ -1,0 +1,347 @@
+#!/usr/bin/env python
+"""Forward-inference throughput of the GPT-style decoder config
+(24 layers, d_model 2048, 16 heads, vocab 32000, seq 1024, batch 64 per GPU, bf16)
+through the munet_b200 compiled executor — tokens/s, roofline fraction of the
+dominant kernel, and the reference CPU path timed on the same host.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One process per GPU (launched under torch.distributed.run for N > 1). The batch is
+sharded over ranks with no data-path collective: every rank holds a full weight
+replica and runs its own 64 sequences ("weak" scaling; whole-job value = all
+ranks' tokens / max-over-ranks device time). Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # BASELINE config 5: the one the headline metric is quoted on
+    "gpt_l": dict(n_layers=24, d_model=2048, n_heads=16, vocab=32000, seq=1024, batch=64),
+    # BASELINE config 4 (parity-test size; selectable for quick runs)
+    "gpt_s": dict(n_layers=6, d_model=512, n_heads=8, vocab=8192, seq=256, batch=32),
+}
+METRIC = "tokens/s, GPT-style decoder forward (24L d2048 16h, seq 1024, bf16)"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) during the timed region."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag = index, [], set(), False
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksEventReasonSwPowerCap: "sw_power_cap",
+            nv.nvmlClocksEventReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksEventReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksEventReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksEventReasonHwPowerBrakeSlowdown: "hw_power_brake",
+        }
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def result(self):
+        self.stop_flag = True
+        if self.nv is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml unavailable"]}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+def cpu_reference_sample(cfg, steps=1, warmup=0):
+    """Times the reference's own CPU implementation (oracle/_ref, the unmodified MuNet CPU core;
+    the C restatement when that library is absent) on a bounded sample of the workload and
+    extrapolates to tokens/s of the full model. The reference materialises a [B*H*T]^2 score
+    matrix and runs bf16 through scalar double loops, so the full config would take days."""
+    import oracle
+    use_ref = oracle.have_ref()
+    lib = oracle.ref() if use_ref else oracle.port()
+    d, H, V = cfg["d_model"], cfg["n_heads"], cfg["vocab"]
+    T_s, T_head = 16, 4  # tokens of the sample: one layer on [1,T_s], head on T_head tokens
+    rng = np.random.default_rng(1005)
+
+    def w(*s):
+        return oracle.to_bf16((rng.standard_normal(s) * 0.02).astype(np.float32))
+    one, zero = oracle.to_bf16(np.ones(d, np.float32)), oracle.to_bf16(np.zeros(d, np.float32))
+    layer = [one, zero]
+    for _ in range(4):
+        layer += [w(d, d), w(d)]
+    layer += [one, zero, w(d, 4 * d), w(4 * d), w(4 * d, d), w(d)]
+    # a 1-layer model with a tiny vocabulary isolates the per-layer cost
+    v_small = 8
+    ps = [w(v_small, d), w(T_s, d)] + layer + [one, zero, w(d, v_small), w(v_small)]
+    ids = rng.integers(0, v_small, (1, T_s)).astype(np.int32)
+    head_w, head_b = w(d, V), w(V)
+    xh = w(T_head, d)
+    t_layer, t_head = [], []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        lib.gpt_forward(ids, ps, v_small, d, H, 1, oracle.BF16, stop_after_layers=1)
+        t1 = time.perf_counter()
+        lib.linear(xh, head_w, head_b, oracle.BF16)
+        t2 = time.perf_counter()
+        if i >= warmup:
+            t_layer.append(t1 - t0)
+            t_head.append(t2 - t1)
+    per_token = cfg["n_layers"] * float(np.mean(t_layer)) / T_s + float(np.mean(t_head)) / T_head
+    cores = lib.hardware_concurrency() if use_ref else (os.cpu_count() or 1)
+    return {
+        "value": 1.0 / per_token, "unit": "tokens/s", "cores": cores,
+        "kind": "reference" if use_ref else "port",
+        "sample": (f"extrapolated: 1 of {cfg['n_layers']} layers on 1x{T_s} tokens + LM head on "
+                   f"{T_head} tokens, bf16, literal attention; reference bf16 matmul/LayerNorm/"
+                   "attention loops are single-threaded (thread pool of `cores` only serves fp32); "
+                   "attention cost at seq 1024 is under-counted (sample uses seq 16)"),
+        "seconds": float(np.sum(t_layer) + np.sum(t_head)),
+    }
+
+
+def run_reference(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    base = cpu_reference_sample(cfg, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    wall = time.perf_counter() - t0
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * base["seconds"] / max(1, args.steps), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(cfg, args.gpus),
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": wall,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(cfg, n_gpus):
+    return {
+        "workload": (f"GPT decoder forward: {cfg['n_layers']}L d{cfg['d_model']} h{cfg['n_heads']} "
+                     f"vocab {cfg['vocab']} seq {cfg['seq']} batch {cfg['batch']}/GPU, pre-LN, "
+                     "causal, 4x GELU MLP, weights N(0,0.02), uniform random ids"),
+        "global_batch": cfg["batch"] * n_gpus, "seq_len": cfg["seq"],
+        "parallelism": f"batch-sharded x{n_gpus}, full replica per GPU, no collective",
+        "attention_k_addressing": "literal (reference semantics)",
+        "l2": "no flush needed: per-step working set (2.7 GB weights + >6 GB activations) >> 126 MB L2",
+        "e2e_result": "argmax token ids [batch, seq] int32 read back to the host",
+    }
+
+
+def run_ours(args, cfg):
+    import torch
+    import torch.distributed as dist
+    import munet_b200 as mb
+    from munet_b200.inference import Engine, gpt_decoder_config, gpt_param_shapes
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    L, d, H, V, T, B = (cfg[k] for k in ("n_layers", "d_model", "n_heads", "vocab", "seq", "batch"))
+    dev = torch.device("cuda", local)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1005)  # identical replica on every rank
+
+    def w(*shape):
+        return (torch.randn(*shape, device=dev, generator=gen, dtype=torch.float32) * 0.02).bfloat16()
+    tensors = {}
+    for name, shape in gpt_param_shapes(V, T, d, L).items():
+        if ".ln" in name or name.startswith("ln_f"):
+            fill = torch.ones if name.endswith("weight") else torch.zeros
+            tensors[name] = fill(*shape, device=dev).bfloat16()
+        elif name.endswith("bias"):
+            tensors[name] = torch.zeros(*shape, device=dev).bfloat16()
+        else:
+            tensors[name] = w(*shape)
+
+    ctx = mb.Context(local)
+    eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_LITERAL, argmax=True)
+    eng.load(gpt_decoder_config(V, T, d, H, L), tensors)
+    eng.compile((B, T), mb.I32)
+    del tensors
+    torch.cuda.empty_cache()
+    stats = eng.stats()
+
+    ids_gen = torch.Generator(device="cpu")
+    ids_gen.manual_seed(2005 + rank)  # each rank owns its shard of the global batch
+    ids_host = torch.randint(0, V, (B, T), generator=ids_gen, dtype=torch.int32).pin_memory()
+    ids_dev = ids_host.to(dev)
+    am_host = torch.empty((B, T), dtype=torch.int32).pin_memory()
+    stream = torch.cuda.current_stream()
+    lib = mb.lib()
+
+    def step_device():
+        rc = lib.mu_engine_run(eng._h, ids_dev.data_ptr(), 0, None, 0, None, 0, stream.cuda_stream)
+        if rc:
+            raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
+
+    def step_e2e():
+        rc = lib.mu_engine_run(eng._h, ids_host.data_ptr(), 1, None, 0, am_host.data_ptr(), 1,
+                               stream.cuda_stream)
+        if rc:
+            raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    ctx.check()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms_total = timed(step_device, args.steps)
+    clocks = sampler.result()
+    ctx.check()
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    ctx.check()
+
+    tokens_step = B * T * world
+    value = tokens_step * args.steps / (ms_total / 1e3)
+    e2e_value = tokens_step * args.steps / (ms_e2e / 1e3)
+
+    # dominant kernel: the tcgen05 GEMM behind every linear. Timed live with CUDA events
+    # around each op of an eager forward on the same stream and buffers.
+    prof = eng.profile(reps=2)
+    pk = peaks()
+    by_kind = {}
+    for p in prof:
+        k = by_kind.setdefault(p["kind"], {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "n": 0})
+        k["ms"] += p["ms"]
+        k["flops"] += p["flops"]
+        k["bytes"] += p["bytes"]
+        k["n"] += 1
+    gemm_ms = by_kind.get("linear", {"ms": 0})["ms"] + by_kind.get("qkv_linear", {"ms": 0})["ms"]
+    gemm_fl = by_kind.get("linear", {"flops": 0})["flops"] + by_kind.get("qkv_linear", {"flops": 0})["flops"]
+    achieved = gemm_fl / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
+    roofline = {
+        "bound": "tensor", "kernel": "gemm_bf16_tcgen05_kernel (all Linear layers of one forward)",
+        "achieved": achieved, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+        "frac": achieved / pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (sustained)",
+        "traffic": None,
+        "launches_per_step": by_kind.get("linear", {"n": 0})["n"] + by_kind.get("qkv_linear", {"n": 0})["n"],
+        "avg_launch_ms": gemm_ms / max(1, by_kind.get("linear", {"n": 0})["n"] + by_kind.get("qkv_linear", {"n": 0})["n"]),
+        "per_kind_ms": {k: round(v["ms"], 3) for k, v in by_kind.items()},
+        "hbm_bound_ops": {
+            k: {"achieved_gbs": v["bytes"] / (v["ms"] / 1e3) / 1e9, "frac_of_measured_hbm":
+                v["bytes"] / (v["ms"] / 1e3) / 1e9 / pk["hbm_gbs"]}
+            for k, v in by_kind.items() if k in ("layer_norm", "embed", "argmax") and v["ms"] > 0},
+    }
+
+    line = None
+    if rank == 0:
+        base = cpu_reference_sample(cfg) if world == 1 and not args.no_cpu_baseline else None
+        flops_step = sum(p["flops"] for p in prof) * world
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(cfg, world),
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": B * T * 4 * world,
+                    "d2h_bytes_per_step": B * T * 4 * world, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": stats["n_launches"] * args.steps,
+            "roofline": roofline, "clocks": clocks,
+            "model_tflops_per_s": flops_step * args.steps / (ms_total / 1e3) / 1e12,
+            "engine": stats,
+        }
+        if base is not None:
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line))
+    eng.close()
+    ctx.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="gpt_l", choices=sorted(CONFIGS))
+    ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = dict(CONFIGS[args.config])
+    if args.batch:
+        cfg["batch"] = args.batch
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

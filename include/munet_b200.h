@@ -136,6 +136,50 @@ int mu_eltwise(mu_ctx *ctx, const void *x, const void *bias, const void *residua
 int mu_argmax(mu_ctx *ctx, const void *x, int32_t *idx, long long rows, int cols, int dtype,
               void *stream);
 
+/* ---- compiled inference executor -------------------------------------------
+ * Stands in for munet::inference::Engine (src/inference.hpp:292-801) and
+ * load_serialized (src/inference_serialization.cpp:1086-1089).
+ *   mu_engine_load         Engine::load(path): parse + validate a deploy artifact
+ *                          (.npz of .npy members, JSON module tree in __config__).
+ *   mu_engine_load_memory  Engine::load(module): same module tree given as JSON text
+ *                          plus named tensors already in memory (host or device).
+ *   mu_engine_compile      Engine::compile(example): fixes the input shape contract,
+ *                          lowers the module tree to a fused op list, plans one arena,
+ *                          uploads weights and captures a CUDA graph.
+ *   mu_engine_run          Engine::run(input): strict shape contract, one graph launch.
+ * Module types: the reference's Sequential, Linear, ReLU, Sigmoid, Tanh, GELU, Dropout,
+ * Flatten, LayerNorm, Embedding, MultiHeadAttention, plus the extension containers
+ * TransformerBlock{d_model,n_heads} and GPTDecoder{vocab,ctx_len,d_model,n_heads,n_layers}
+ * (the reference format has no residual container, so it cannot express a decoder).
+ * compute_dtype: MU_F32 or MU_BF16; float32 tensors are converted on load like
+ * Module::to(DataType) (src/core/module.hpp:177-194). */
+typedef struct mu_engine mu_engine;
+int mu_engine_create(mu_ctx *ctx, mu_engine **out);
+void mu_engine_destroy(mu_engine *engine);
+const char *mu_engine_last_error(const mu_engine *engine);
+/* options: "kmode" (mu_kmode), "use_graph" (0/1), "argmax" (0/1: also produce int32 argmax) */
+int mu_engine_set_option(mu_engine *engine, const char *name, int value);
+int mu_engine_load(mu_engine *engine, const char *artifact_path, int compute_dtype);
+/* shapes: all tensors' dims concatenated, ndims[i] of them per tensor */
+int mu_engine_load_memory(mu_engine *engine, const char *config_json, int n_tensors,
+                          const char *const *names, const void *const *data, const int *dtypes,
+                          const int *ndims, const long long *shapes, int on_device,
+                          int compute_dtype);
+int mu_engine_compile(mu_engine *engine, const int *input_shape, int ndim, int input_dtype);
+int mu_engine_output_shape(const mu_engine *engine, int *shape, int *ndim, int *dtype);
+int mu_engine_stats(const mu_engine *engine, long long *arena_bytes, long long *weight_bytes,
+                    long long *n_ops, long long *n_launches, long long *unplanned_bytes);
+int mu_engine_run(mu_engine *engine, const void *input, int input_on_host, void *output,
+                  int output_on_host, int32_t *argmax_out, int argmax_on_host, void *stream);
+/* Per-op timing of an eager forward (CUDA events around every op, mean of `reps`),
+ * with each op's algorithmic FLOPs / bytes: the engine-level counterpart of the
+ * reference's Profiler rows (src/core/util/profiler.hpp:31-185).
+ * kinds: 0 embed, 1 layer_norm, 2 linear, 3 qkv linear, 4 attention, 5 eltwise, 6 argmax. */
+int mu_engine_profile(mu_engine *engine, int reps, int capacity, int *n_ops, int *kinds, float *ms,
+                      double *flops, double *bytes, void *stream);
+void *mu_engine_output_ptr(const mu_engine *engine);
+void *mu_engine_argmax_ptr(const mu_engine *engine);
+
 #ifdef __cplusplus
 }
 #endif

@@ -57,6 +57,21 @@ SIGNATURES = {
     "mu_embedding": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "mu_eltwise": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp]),
     "mu_argmax": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
+    "mu_engine_create": (_i, [_vp, C.POINTER(_vp)]),
+    "mu_engine_destroy": (None, [_vp]),
+    "mu_engine_last_error": (C.c_char_p, [_vp]),
+    "mu_engine_set_option": (_i, [_vp, C.c_char_p, _i]),
+    "mu_engine_load": (_i, [_vp, C.c_char_p, _i]),
+    "mu_engine_load_memory": (_i, [_vp, C.c_char_p, _i, C.POINTER(C.c_char_p), C.POINTER(_vp),
+                                   C.POINTER(_i), C.POINTER(_i), C.POINTER(_ll), _i, _i]),
+    "mu_engine_compile": (_i, [_vp, C.POINTER(_i), _i, _i]),
+    "mu_engine_output_shape": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
+    "mu_engine_stats": (_i, [_vp] + [C.POINTER(_ll)] * 5),
+    "mu_engine_run": (_i, [_vp, _vp, _i, _vp, _i, _vp, _i, _vp]),
+    "mu_engine_profile": (_i, [_vp, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_f),
+                               C.POINTER(C.c_double), C.POINTER(C.c_double), _vp]),
+    "mu_engine_output_ptr": (_vp, [_vp]),
+    "mu_engine_argmax_ptr": (_vp, [_vp]),
 }
 
 

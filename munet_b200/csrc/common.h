@@ -28,6 +28,8 @@ struct Epilogue {
   int split_T = 0, split_H = 0, split_D = 0;
   long long split_which_stride = 0;
   int vec_ok = 0; // host-verified: 16-byte aligned rows/pointers → 128-bit stores allowed
+  int tma_out = 0; // tcgen05 kernel: output (and residual) go through staged TMA boxes
+  int tma_mode = 0; // coordinate scheme of the output tensor map: 0 plain, 1 merge-heads, 2 split-heads
 };
 
 struct GemmShape {

@@ -1,0 +1,907 @@
+// Compiled inference executor (host C++ over the C ABI of the kernels).
+//
+// Stands in for munet::inference::Engine (src/inference.hpp:292-801) running a
+// module tree (src/core/module.hpp, src/nn/*.hpp). Where the reference's
+// compile() only records a shape contract and run() re-walks the modules
+// eagerly, allocating every intermediate (src/inference.hpp:446-610), this
+// engine lowers the module tree ONCE per input shape into a flat op list with
+//   * a fusion pass: Linear+bias+activation(+residual) → one GEMM epilogue,
+//     q/k/v projections → one GEMM that writes head-major, residual adds and
+//     head split/merge permutes folded into GEMM epilogues, token+position
+//     embedding → one gather;
+//   * a buffer plan: liveness intervals over the op list → one device arena
+//     (no allocation at run time, vs. one Backend::allocate per op,
+//     src/storage.hpp:10-21);
+//   * a CUDA graph of the whole forward, replayed by run().
+// Module semantics (parameter names, layouts, eval-mode behaviour) follow the
+// reference's nn:: classes; citations sit next to each lowering rule.
+#include "../../include/munet_b200.h"
+#include "engine_io.h"
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <cuda_runtime.h>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+using mu::Json;
+using mu::NamedTensor;
+
+namespace {
+
+enum OpKind {
+  OP_EMBED, OP_LN, OP_LINEAR, OP_QKV, OP_ATTN, OP_ELTWISE, OP_ARGMAX, OP_ALLREDUCE
+};
+
+struct Tensor {
+  size_t bytes = 0;
+  int first = -1, last = -1; // op indices of definition and last use
+  size_t offset = 0;
+  int alias_of = -1;
+  bool external = false; // engine input: lives in its own buffer
+};
+
+struct Op {
+  OpKind kind;
+  int in = -1, res = -1, out = -1, out2 = -1, out3 = -1, ws = -1;
+  int w = -1, b = -1, w2 = -1, b2 = -1;
+  int M = 0, K = 0, N = 0, act = 0;
+  int B = 0, T = 0, H = 0, D = 0, V = 0, causal = 0;
+  float eps = 1e-5f;
+  long long n = 0;
+  size_t ws_bytes = 0;
+};
+
+struct Weight {
+  size_t offset = 0, bytes = 0;
+};
+
+struct Val {
+  int tid = -1;
+  std::vector<int> shape;
+  int dtype = MU_F32;
+  long long numel() const {
+    long long n = 1;
+    for (int s : shape)
+      n *= s;
+    return n;
+  }
+};
+
+size_t esize(int dt) { return (dt == MU_F32 || dt == MU_I32) ? 4 : 2; }
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+uint16_t f2bf(float v) { // RNE exactly like the reference (src/types.hpp:311-317)
+  uint32_t bits;
+  memcpy(&bits, &v, 4);
+  bits += 0x7fffu + ((bits >> 16) & 1u);
+  return static_cast<uint16_t>(bits >> 16);
+}
+
+} // namespace
+
+struct mu_engine {
+  mu_ctx *ctx = nullptr;
+  int dtype = MU_F32; // compute dtype of floating tensors
+  int kmode = MU_K_LITERAL;
+  int use_graph = 1;
+  int want_argmax = 0;
+  Json config;
+  std::map<std::string, NamedTensor> params;
+  bool loaded = false, compiled = false;
+
+  std::vector<Tensor> tensors;
+  std::vector<Op> ops;
+  std::vector<Weight> weights;
+  std::map<std::string, int> weight_ids;
+  std::vector<uint8_t> weight_stage; // host staging of converted weights
+  struct DevCopy { size_t dst, dst_pitch; const void *src; size_t width, rows; };
+  std::vector<DevCopy> dev_copies;   // weights whose source already lives on the device
+  std::vector<bool> dev_weight;      // per weight: filled by device copies
+  void *weight_slab = nullptr;
+  void *arena = nullptr;
+  void *input_buf = nullptr;
+  size_t arena_bytes = 0, weight_bytes = 0, input_bytes = 0;
+  std::vector<int> in_shape, out_shape;
+  int in_dtype = MU_F32, out_dtype = MU_F32;
+  int out_tid = -1, argmax_tid = -1;
+  cudaGraphExec_t gexec = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaStream_t cap_stream = nullptr;
+  long long n_launches = 0;
+  char err[768] = {0};
+
+  int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(err, sizeof(err), fmt, ap);
+    va_end(ap);
+    return code;
+  }
+
+  void release_compiled() {
+    if (gexec) cudaGraphExecDestroy(gexec), gexec = nullptr;
+    if (graph) cudaGraphDestroy(graph), graph = nullptr;
+    if (cap_stream) cudaStreamDestroy(cap_stream), cap_stream = nullptr;
+    if (weight_slab) mu_free(ctx, weight_slab), weight_slab = nullptr;
+    if (arena) mu_free(ctx, arena), arena = nullptr;
+    if (input_buf) mu_free(ctx, input_buf), input_buf = nullptr;
+    tensors.clear(), ops.clear(), weights.clear(), weight_ids.clear();
+    weight_stage.clear(), dev_copies.clear(), dev_weight.clear();
+    compiled = false;
+  }
+
+  // ---- lowering helpers ----------------------------------------------------
+  int new_tensor(size_t bytes) {
+    Tensor t;
+    t.bytes = bytes;
+    tensors.push_back(t);
+    return static_cast<int>(tensors.size()) - 1;
+  }
+  int root(int tid) const {
+    while (tensors[tid].alias_of >= 0)
+      tid = tensors[tid].alias_of;
+    return tid;
+  }
+  void touch(int tid, int op_index) {
+    if (tid < 0) return;
+    Tensor &t = tensors[root(tid)];
+    if (t.first < 0) t.first = op_index;
+    t.last = std::max(t.last, op_index);
+  }
+  int push(const Op &op) {
+    const int idx = static_cast<int>(ops.size());
+    ops.push_back(op);
+    for (int t : {op.in, op.res, op.out, op.out2, op.out3, op.ws})
+      touch(t, idx);
+    return idx;
+  }
+
+  const NamedTensor *find_param(const std::string &name) const {
+    auto it = params.find(name);
+    return it == params.end() ? nullptr : &it->second;
+  }
+
+  // Stage a parameter (converted to the compute dtype) into the weight slab.
+  // `parts` are concatenated along the last axis (fused q/k/v weights).
+  int stage_weight(const std::vector<std::string> &parts, std::string *why) {
+    std::string key;
+    for (auto &p : parts) key += p + "|";
+    auto it = weight_ids.find(key);
+    if (it != weight_ids.end()) return it->second;
+    std::vector<const NamedTensor *> ts;
+    long long rows = -1, cols_total = 0;
+    for (auto &p : parts) {
+      const NamedTensor *t = find_param(p);
+      if (!t) { *why = "missing tensor '" + p + "'"; return -1; }
+      if (t->dtype != MU_F32 && t->dtype != dtype) {
+        *why = "tensor '" + p + "' has dtype " + std::to_string(t->dtype) +
+               ", expected float32 or the compute dtype";
+        return -1;
+      }
+      long long r = 1;
+      for (size_t i = 0; i + 1 < t->shape.size(); ++i) r *= t->shape[i];
+      long long c = t->shape.empty() ? 1 : t->shape.back();
+      if (parts.size() == 1) { r = 1; c = t->numel(); }
+      if (rows >= 0 && r != rows) { *why = "concat shape mismatch at '" + p + "'"; return -1; }
+      rows = r;
+      cols_total += c;
+      ts.push_back(t);
+    }
+    const size_t es = esize(dtype);
+    Weight w;
+    w.bytes = static_cast<size_t>(rows) * cols_total * es;
+    w.offset = align_up(weight_bytes, 256);
+    weight_bytes = w.offset + w.bytes;
+    bool any_dev = false;
+    for (auto *t : ts) any_dev = any_dev || t->on_device;
+    if (any_dev) {
+      // device-resident sources: strided device-to-device copies into the slab
+      long long col0 = 0;
+      for (auto *t : ts) {
+        if (!t->on_device || t->dtype != dtype) {
+          *why = "device-resident tensors must all be on the device and already have the compute dtype";
+          return -1;
+        }
+        const long long c = parts.size() == 1 ? t->numel() : t->shape.back();
+        dev_copies.push_back({w.offset + static_cast<size_t>(col0) * es,
+                              static_cast<size_t>(cols_total) * es, t->data,
+                              static_cast<size_t>(c) * es, static_cast<size_t>(rows)});
+        col0 += c;
+      }
+      dev_weight.push_back(true);
+    } else {
+      dev_weight.push_back(false);
+      if (weight_stage.size() < weight_bytes) weight_stage.resize(weight_bytes);
+      uint8_t *dst = weight_stage.data() + w.offset;
+      long long col0 = 0;
+      for (auto *t : ts) {
+        const long long c = parts.size() == 1 ? t->numel() : t->shape.back();
+        for (long long r = 0; r < rows; ++r) {
+          uint8_t *d = dst + (static_cast<size_t>(r) * cols_total + col0) * es;
+          if (t->dtype == dtype) {
+            memcpy(d, static_cast<const uint8_t *>(t->data) + static_cast<size_t>(r) * c * es, c * es);
+          } else { // float32 → bfloat16, Tensor::to(DataType) semantics (src/tensor.cpp:249-284)
+            const float *s = static_cast<const float *>(t->data) + r * c;
+            uint16_t *o = reinterpret_cast<uint16_t *>(d);
+            for (long long i = 0; i < c; ++i) o[i] = f2bf(s[i]);
+          }
+        }
+        col0 += c;
+      }
+    }
+    weights.push_back(w);
+    const int id = static_cast<int>(weights.size()) - 1;
+    weight_ids[key] = id;
+    return id;
+  }
+
+  int lower(const Json &node, const std::string &prefix, Val &v, const Json *next, bool *fused_next);
+  int lower_linear(const std::string &prefix, int K, int N, bool bias, int act, int res_tid, Val &v);
+  int lower_mha(const std::string &prefix, int E, int H, bool causal, int res_tid, Val &v);
+  int lower_block(const std::string &prefix, int d, int H, Val &v);
+  int plan_and_allocate();
+  int launch_all(cudaStream_t st);
+  int launch_op(const Op &op, cudaStream_t st);
+  void op_work(const Op &op, double *flops, double *bytes) const;
+  void *tptr(int tid) const {
+    if (tid < 0) return nullptr;
+    const Tensor &t = tensors[root(tid)];
+    return t.external ? input_buf : static_cast<char *>(arena) + t.offset;
+  }
+  void *wptr(int wid) const {
+    return wid < 0 ? nullptr : static_cast<char *>(weight_slab) + weights[wid].offset;
+  }
+};
+
+namespace {
+
+int act_code(const std::string &type) {
+  if (type == "ReLU") return MU_ACT_RELU;
+  if (type == "GELU") return MU_ACT_GELU;
+  if (type == "Sigmoid") return MU_ACT_SIGMOID;
+  if (type == "Tanh") return MU_ACT_TANH;
+  return -1;
+}
+
+} // namespace
+
+// nn::Linear (src/nn/linear.hpp:9-37): weight [in,out], optional bias [out];
+// the following activation module and a residual add ride in the GEMM epilogue.
+int mu_engine::lower_linear(const std::string &prefix, int K, int N, bool bias, int act,
+                            int res_tid, Val &v) {
+  if (v.shape.empty() || v.shape.back() != K)
+    return fail(MU_ERR_INVALID, "Linear '%s': input last dim %d != in_features %d", prefix.c_str(),
+                v.shape.empty() ? -1 : v.shape.back(), K);
+  std::string why;
+  Op op;
+  op.kind = OP_LINEAR;
+  op.w = stage_weight({prefix + "weight"}, &why);
+  if (op.w < 0) return fail(MU_ERR_INVALID, "Linear '%s': %s", prefix.c_str(), why.c_str());
+  if (bias) {
+    op.b = stage_weight({prefix + "bias"}, &why);
+    if (op.b < 0) return fail(MU_ERR_INVALID, "Linear '%s': %s", prefix.c_str(), why.c_str());
+  }
+  op.M = static_cast<int>(v.numel() / K), op.K = K, op.N = N, op.act = act;
+  op.in = v.tid, op.res = res_tid;
+  if (res_tid >= 0) {
+    // x + f(x): the epilogue reads and writes the same element, so the residual
+    // stream is updated in place.
+    op.out = new_tensor(0);
+    tensors[op.out].alias_of = root(res_tid);
+  } else {
+    op.out = new_tensor(static_cast<size_t>(op.M) * N * esize(dtype));
+  }
+  push(op);
+  v.tid = op.out;
+  v.shape.back() = N;
+  return MU_OK;
+}
+
+// nn::MultiHeadAttention::forward_impl (src/nn/attention.hpp:34-103).
+int mu_engine::lower_mha(const std::string &prefix, int E, int H, bool causal, int res_tid, Val &v) {
+  if (v.shape.size() != 3)
+    return fail(MU_ERR_INVALID, "MultiHeadAttention expects input shape [B,T,E]");
+  if (v.shape[2] != E)
+    return fail(MU_ERR_INVALID, "MultiHeadAttention expects last dim == embed_dim");
+  if (H <= 0 || E % H)
+    return fail(MU_ERR_INVALID, "MultiHeadAttention: embed_dim must be divisible by num_heads");
+  const int B = v.shape[0], T = v.shape[1], D = E / H;
+  const size_t per = static_cast<size_t>(B) * T * E * esize(dtype);
+  std::string why;
+  Op q;
+  q.kind = OP_QKV;
+  q.w = stage_weight({prefix + "q_proj.weight", prefix + "k_proj.weight", prefix + "v_proj.weight"}, &why);
+  if (q.w >= 0)
+    q.b = stage_weight({prefix + "q_proj.bias", prefix + "k_proj.bias", prefix + "v_proj.bias"}, &why);
+  if (q.w < 0 || q.b < 0)
+    return fail(MU_ERR_INVALID, "MultiHeadAttention '%s': %s", prefix.c_str(), why.c_str());
+  q.B = B, q.T = T, q.K = E, q.H = H;
+  q.in = v.tid;
+  q.out = new_tensor(3 * per); // q | k | v, head-major, contiguous
+  push(q);
+  Op a;
+  a.kind = OP_ATTN;
+  a.in = q.out;
+  a.B = B, a.T = T, a.H = H, a.D = D, a.causal = causal;
+  a.ws_bytes = mu_attention_workspace_bytes(B, H, T, D, dtype);
+  a.ws = new_tensor(a.ws_bytes);
+  a.out = new_tensor(per);
+  push(a);
+  v.tid = a.out;
+  v.shape = {B * T, E};
+  int rc = lower_linear(prefix + "out_proj.", E, E, true, MU_ACT_NONE, res_tid, v);
+  v.shape = {B, T, E};
+  return rc;
+}
+
+// Pre-norm decoder block (demos/multigpu/gpt3_multi_gpu_demo.py:89-113):
+//   x = x + attn(ln1(x)); x = x + ff(ln2(x)), ff = Linear(d,4d) → GELU → Linear(4d,d)
+int mu_engine::lower_block(const std::string &prefix, int d, int H, Val &v) {
+  std::string why;
+  for (int half = 0; half < 2; ++half) {
+    const std::string ln = prefix + (half ? "ln2." : "ln1.");
+    Op n;
+    n.kind = OP_LN;
+    n.w = stage_weight({ln + "weight"}, &why);
+    if (n.w >= 0) n.b = stage_weight({ln + "bias"}, &why);
+    if (n.w < 0 || n.b < 0) return fail(MU_ERR_INVALID, "LayerNorm '%s': %s", ln.c_str(), why.c_str());
+    n.M = static_cast<int>(v.numel() / d), n.N = d;
+    n.in = v.tid;
+    n.out = new_tensor(static_cast<size_t>(v.numel()) * esize(dtype));
+    push(n);
+    Val h = v;
+    h.tid = n.out;
+    int rc;
+    if (half == 0) {
+      rc = lower_mha(prefix + "attn.", d, H, true, v.tid, h);
+    } else {
+      rc = lower_linear(prefix + "ff.0.", d, 4 * d, true, MU_ACT_GELU, -1, h);
+      if (rc == MU_OK) rc = lower_linear(prefix + "ff.2.", 4 * d, d, true, MU_ACT_NONE, v.tid, h);
+    }
+    if (rc) return rc;
+    v.tid = h.tid;
+  }
+  return MU_OK;
+}
+
+int mu_engine::lower(const Json &node, const std::string &prefix, Val &v, const Json *next,
+                     bool *fused_next) {
+  if (fused_next) *fused_next = false;
+  if (!node.is_object()) return fail(MU_ERR_INVALID, "Serialized module config root must be a JSON object");
+  const Json *ty = node.get("type");
+  if (!ty || !ty->is_string()) return fail(MU_ERR_INVALID, "module config is missing 'type'");
+  const std::string &type = ty->str;
+  auto req_int = [&](const char *k, int *out) {
+    const Json *j = node.get(k);
+    if (!j || !j->is_number()) return false;
+    *out = static_cast<int>(j->num);
+    return true;
+  };
+  auto req_bool = [&](const char *k, bool *out) {
+    const Json *j = node.get(k);
+    if (!j || j->kind != Json::BOOL) return false;
+    *out = j->b;
+    return true;
+  };
+  std::string why;
+
+  if (type == "Sequential") { // src/nn/sequential.hpp:8-28, children named by index
+    const Json *layers = node.get("layers");
+    if (!layers || !layers->is_array()) return fail(MU_ERR_INVALID, "Sequential: missing 'layers'");
+    for (size_t i = 0; i < layers->arr.size(); ++i) {
+      const Json *nx = i + 1 < layers->arr.size() ? &layers->arr[i + 1] : nullptr;
+      bool fused = false;
+      int rc = lower(layers->arr[i], prefix + std::to_string(i) + ".", v, nx, &fused);
+      if (rc) return rc;
+      if (fused) ++i;
+    }
+    return MU_OK;
+  }
+  if (type == "Linear") {
+    int K, N;
+    bool bias;
+    if (!req_int("in_features", &K) || !req_int("out_features", &N) || !req_bool("bias", &bias))
+      return fail(MU_ERR_INVALID, "Linear: missing in_features/out_features/bias");
+    int act = MU_ACT_NONE;
+    if (next && next->is_object() && next->get("type") && next->get("type")->is_string()) {
+      const int a = act_code(next->get("type")->str);
+      if (a > 0) { act = a; if (fused_next) *fused_next = true; }
+    }
+    return lower_linear(prefix, K, N, bias, act, -1, v);
+  }
+  if (act_code(type) > 0) {
+    Op op;
+    op.kind = OP_ELTWISE, op.act = act_code(type), op.n = v.numel();
+    op.in = v.tid, op.out = new_tensor(static_cast<size_t>(op.n) * esize(dtype));
+    push(op);
+    v.tid = op.out;
+    return MU_OK;
+  }
+  if (type == "Dropout") return MU_OK; // eval mode: identity (src/nn/activations.hpp:47-50)
+  if (type == "Flatten") {             // src/nn/linear.hpp:66-73
+    if (v.shape.empty()) return fail(MU_ERR_INVALID, "Flatten: empty shape");
+    const int b0 = v.shape[0];
+    v.shape = {b0, static_cast<int>(v.numel() / std::max(b0, 1))};
+    return MU_OK;
+  }
+  if (type == "LayerNorm") { // src/nn/normalization.hpp:8-37
+    int d;
+    const Json *eps = node.get("eps");
+    if (!req_int("normalized_shape", &d) || !eps || !eps->is_number())
+      return fail(MU_ERR_INVALID, "LayerNorm: missing normalized_shape/eps");
+    if (v.shape.empty() || v.shape.back() != d)
+      return fail(MU_ERR_INVALID, "LayerNorm expects last dim to match normalized_shape");
+    Op n;
+    n.kind = OP_LN, n.eps = static_cast<float>(eps->num);
+    n.w = stage_weight({prefix + "weight"}, &why);
+    if (n.w >= 0) n.b = stage_weight({prefix + "bias"}, &why);
+    if (n.w < 0 || n.b < 0) return fail(MU_ERR_INVALID, "LayerNorm: %s", why.c_str());
+    n.M = static_cast<int>(v.numel() / d), n.N = d, n.in = v.tid;
+    n.out = new_tensor(static_cast<size_t>(v.numel()) * esize(dtype));
+    push(n);
+    v.tid = n.out;
+    return MU_OK;
+  }
+  if (type == "Embedding") { // index path, src/nn/linear.hpp:92-131
+    int V, D;
+    if (!req_int("num_embeddings", &V) || !req_int("embedding_dim", &D))
+      return fail(MU_ERR_INVALID, "Embedding: missing num_embeddings/embedding_dim");
+    if (V <= 0 || D <= 0)
+      return fail(MU_ERR_INVALID, "Embedding expects positive num_embeddings and embedding_dim");
+    if (v.shape.size() != 2 || v.dtype != MU_I32)
+      return fail(MU_ERR_INVALID, "Embedding expects [B,T] int32 indices");
+    Op e;
+    e.kind = OP_EMBED, e.B = v.shape[0], e.T = v.shape[1], e.V = V, e.D = D;
+    e.w = stage_weight({prefix + "weight"}, &why);
+    if (e.w < 0) return fail(MU_ERR_INVALID, "Embedding: %s", why.c_str());
+    e.in = v.tid;
+    e.out = new_tensor(static_cast<size_t>(e.B) * e.T * D * esize(dtype));
+    push(e);
+    v.tid = e.out, v.shape = {e.B, e.T, D}, v.dtype = dtype;
+    return MU_OK;
+  }
+  if (type == "MultiHeadAttention") {
+    int E, H;
+    bool causal;
+    if (!req_int("embed_dim", &E) || !req_int("num_heads", &H) || !req_bool("causal", &causal))
+      return fail(MU_ERR_INVALID, "MultiHeadAttention: missing embed_dim/num_heads/causal");
+    return lower_mha(prefix, E, H, causal, -1, v);
+  }
+  // ---- extension node types (a superset of the reference's deploy format, which has
+  // no residual container and therefore cannot express a decoder) ----
+  if (type == "TransformerBlock") {
+    int d, H;
+    if (!req_int("d_model", &d) || !req_int("n_heads", &H))
+      return fail(MU_ERR_INVALID, "TransformerBlock: missing d_model/n_heads");
+    if (v.shape.size() != 3 || v.shape[2] != d)
+      return fail(MU_ERR_INVALID, "TransformerBlock expects [B,T,d_model]");
+    return lower_block(prefix, d, H, v);
+  }
+  if (type == "GPTDecoder") { // SimpleGPT, demos/multigpu/gpt3_multi_gpu_demo.py:116-172
+    int V, C, d, H, L;
+    if (!req_int("vocab", &V) || !req_int("ctx_len", &C) || !req_int("d_model", &d) ||
+        !req_int("n_heads", &H) || !req_int("n_layers", &L))
+      return fail(MU_ERR_INVALID, "GPTDecoder: missing vocab/ctx_len/d_model/n_heads/n_layers");
+    if (v.shape.size() != 2 || v.dtype != MU_I32)
+      return fail(MU_ERR_INVALID, "GPTDecoder expects [B,T] int32 token ids");
+    const int B = v.shape[0], T = v.shape[1];
+    if (T > C) return fail(MU_ERR_INVALID, "GPTDecoder: sequence length %d exceeds ctx_len %d", T, C);
+    Op e;
+    e.kind = OP_EMBED, e.B = B, e.T = T, e.V = V, e.D = d;
+    e.w = stage_weight({prefix + "token_embed.weight"}, &why);
+    if (e.w >= 0) e.w2 = stage_weight({prefix + "pos_embed.weight"}, &why);
+    if (e.w < 0 || e.w2 < 0) return fail(MU_ERR_INVALID, "GPTDecoder: %s", why.c_str());
+    e.in = v.tid;
+    e.out = new_tensor(static_cast<size_t>(B) * T * d * esize(dtype));
+    push(e);
+    v.tid = e.out, v.shape = {B, T, d}, v.dtype = dtype;
+    for (int l = 0; l < L; ++l) {
+      int rc = lower_block(prefix + "blocks." + std::to_string(l) + ".", d, H, v);
+      if (rc) return rc;
+    }
+    Op n;
+    n.kind = OP_LN;
+    n.w = stage_weight({prefix + "ln_f.weight"}, &why);
+    if (n.w >= 0) n.b = stage_weight({prefix + "ln_f.bias"}, &why);
+    if (n.w < 0 || n.b < 0) return fail(MU_ERR_INVALID, "GPTDecoder: %s", why.c_str());
+    n.M = B * T, n.N = d, n.in = v.tid;
+    n.out = new_tensor(static_cast<size_t>(B) * T * d * esize(dtype));
+    push(n);
+    v.tid = n.out;
+    return lower_linear(prefix + "head.", d, V, true, MU_ACT_NONE, -1, v);
+  }
+  return fail(MU_ERR_UNSUPPORTED, "Unsupported serialized module type for C++ reconstruction: %s",
+              type.c_str());
+}
+
+// Liveness-based arena plan: tensors that are never live at the same op may
+// share bytes. Largest-first first-fit over the already placed tensors.
+int mu_engine::plan_and_allocate() {
+  std::vector<int> order;
+  for (size_t i = 0; i < tensors.size(); ++i)
+    if (tensors[i].alias_of < 0 && !tensors[i].external && tensors[i].bytes > 0) order.push_back(static_cast<int>(i));
+  std::sort(order.begin(), order.end(), [&](int a, int b) { return tensors[a].bytes > tensors[b].bytes; });
+  std::vector<int> placed;
+  arena_bytes = 0;
+  for (int id : order) {
+    Tensor &t = tensors[id];
+    std::vector<std::pair<size_t, size_t>> busy;
+    for (int p : placed) {
+      const Tensor &o = tensors[p];
+      if (o.first <= t.last && t.first <= o.last) busy.push_back({o.offset, o.offset + o.bytes});
+    }
+    std::sort(busy.begin(), busy.end());
+    size_t off = 0;
+    for (auto &iv : busy) {
+      if (off + t.bytes <= iv.first) break;
+      off = std::max(off, align_up(iv.second, 1024));
+    }
+    t.offset = off;
+    arena_bytes = std::max(arena_bytes, off + t.bytes);
+    placed.push_back(id);
+  }
+  int rc = mu_alloc(ctx, std::max<size_t>(arena_bytes, 16), &arena);
+  if (rc) return fail(rc, "arena allocation of %zu bytes failed: %s", arena_bytes, mu_last_error(ctx));
+  rc = mu_alloc(ctx, std::max<size_t>(weight_bytes, 16), &weight_slab);
+  if (rc) return fail(rc, "weight slab allocation of %zu bytes failed: %s", weight_bytes, mu_last_error(ctx));
+  rc = mu_alloc(ctx, std::max<size_t>(input_bytes, 16), &input_buf);
+  if (rc) return fail(rc, "input buffer allocation failed: %s", mu_last_error(ctx));
+  // the warm-up forward of compile() reads this buffer before any run(): all-zero
+  // ids / activations are valid inputs for every op
+  if (cudaMemset(input_buf, 0, std::max<size_t>(input_bytes, 16)) != cudaSuccess)
+    return fail(MU_ERR_CUDA, "input buffer clear failed");
+  // upload weights: host-staged ones in one copy per contiguous run, device ones D2D
+  for (size_t i = 0; i < weights.size(); ++i) {
+    const Weight &w = weights[i];
+    if (dev_weight[i] || w.bytes == 0) continue;
+    if (cudaMemcpy(static_cast<char *>(weight_slab) + w.offset, weight_stage.data() + w.offset,
+                   w.bytes, cudaMemcpyHostToDevice) != cudaSuccess)
+      return fail(MU_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(cudaGetLastError()));
+  }
+  for (auto &d : dev_copies)
+    if (cudaMemcpy2D(static_cast<char *>(weight_slab) + d.dst, d.dst_pitch, d.src, d.width, d.width,
+                     d.rows, cudaMemcpyDeviceToDevice) != cudaSuccess)
+      return fail(MU_ERR_CUDA, "weight copy failed: %s", cudaGetErrorString(cudaGetLastError()));
+  std::vector<uint8_t>().swap(weight_stage);
+  return MU_OK;
+}
+
+int mu_engine::launch_all(cudaStream_t st) {
+  n_launches = 0;
+  for (const Op &op : ops) {
+    int rc = launch_op(op, st);
+    if (rc) return rc;
+  }
+  return MU_OK;
+}
+
+int mu_engine::launch_op(const Op &op, cudaStream_t st) {
+  {
+    int rc = MU_OK;
+    switch (op.kind) {
+    case OP_EMBED:
+      rc = mu_embedding(ctx, static_cast<const int32_t *>(tptr(op.in)), wptr(op.w), wptr(op.w2),
+                        tptr(op.out), op.B, op.T, op.V, op.D, dtype, st);
+      n_launches += 1;
+      break;
+    case OP_LN:
+      rc = mu_layer_norm(ctx, tptr(op.in), wptr(op.w), wptr(op.b), tptr(op.out), op.M, op.N, op.eps,
+                         dtype, st);
+      n_launches += 1;
+      break;
+    case OP_LINEAR:
+      rc = mu_linear(ctx, tptr(op.in), wptr(op.w), wptr(op.b), tptr(op.res), tptr(op.out), op.M, op.K,
+                     op.N, op.act, dtype, st);
+      n_launches += 1;
+      break;
+    case OP_QKV: {
+      char *base = static_cast<char *>(tptr(op.out));
+      const size_t per = static_cast<size_t>(op.B) * op.T * op.K * esize(dtype);
+      rc = mu_linear_qkv(ctx, tptr(op.in), wptr(op.w), wptr(op.b), base, base + per, base + 2 * per,
+                         op.B, op.T, op.K, op.H, dtype, st);
+      n_launches += 1;
+      break;
+    }
+    case OP_ATTN: {
+      char *base = static_cast<char *>(tptr(op.in));
+      const size_t per = static_cast<size_t>(op.B) * op.T * op.H * op.D * esize(dtype);
+      rc = mu_attention(ctx, base, base + per, base + 2 * per, tptr(op.out), op.B, op.H, op.T, op.D,
+                        op.causal, kmode, dtype, tptr(op.ws), op.ws_bytes, st);
+      n_launches += 3;
+      break;
+    }
+    case OP_ELTWISE:
+      rc = mu_eltwise(ctx, tptr(op.in), nullptr, tptr(op.res), tptr(op.out), op.n, 1, op.act, dtype, st);
+      n_launches += 1;
+      break;
+    case OP_ARGMAX:
+      rc = mu_argmax(ctx, tptr(op.in), static_cast<int32_t *>(tptr(op.out)), op.M, op.N, dtype, st);
+      n_launches += 1;
+      break;
+    default:
+      rc = MU_ERR_UNSUPPORTED;
+    }
+    if (rc) return fail(rc, "op launch failed: %s", mu_last_error(ctx));
+  }
+  return MU_OK;
+}
+
+// Algorithmic work of one op: FLOPs for contractions (attention counted
+// causal-useful: only the unmasked half of the score square), bytes that must
+// be read plus bytes that must be written once for the HBM-bound ops.
+void mu_engine::op_work(const Op &op, double *flops, double *bytes) const {
+  const double es = static_cast<double>(esize(dtype));
+  *flops = 0, *bytes = 0;
+  switch (op.kind) {
+  case OP_LINEAR:
+    *flops = 2.0 * op.M * op.K * op.N;
+    *bytes = es * (1.0 * op.M * op.K + 1.0 * op.K * op.N + 1.0 * op.M * op.N * (op.res >= 0 ? 2 : 1));
+    break;
+  case OP_QKV:
+    *flops = 2.0 * op.B * op.T * op.K * 3.0 * op.K;
+    *bytes = es * (1.0 * op.B * op.T * op.K * 4 + 3.0 * op.K * op.K);
+    break;
+  case OP_ATTN: {
+    const double sq = 1.0 * op.B * op.H * op.T * op.T * op.D;
+    *flops = op.causal ? 2.0 * sq : 4.0 * sq; // QK' + PV, halved when causal
+    *bytes = es * 4.0 * op.B * op.H * op.T * op.D;
+    break;
+  }
+  case OP_LN:
+    *bytes = es * 2.0 * op.M * op.N;
+    break;
+  case OP_EMBED:
+    *bytes = es * 2.0 * op.B * op.T * op.D + 4.0 * op.B * op.T;
+    break;
+  case OP_ELTWISE:
+    *bytes = es * op.n * (op.res >= 0 ? 3 : 2);
+    break;
+  case OP_ARGMAX:
+    *bytes = es * op.M * op.N + 4.0 * op.M;
+    break;
+  default:
+    break;
+  }
+}
+
+extern "C" {
+
+// Eager (graph-free) forward with a CUDA-event pair around every op, `reps`
+// times; reports per-op mean milliseconds, kind and algorithmic work.
+// kinds: 0 embed, 1 layer_norm, 2 linear, 3 qkv linear, 4 attention, 5 eltwise, 6 argmax.
+int mu_engine_profile(mu_engine *e, int reps, int capacity, int *n_ops, int *kinds, float *ms,
+                      double *flops, double *bytes, void *stream) {
+  if (!e || !e->compiled || reps <= 0) return MU_ERR_INVALID;
+  const int n = static_cast<int>(e->ops.size());
+  if (n_ops) *n_ops = n;
+  if (capacity < n) return e->fail(MU_ERR_SIZE, "profile: capacity %d < %d ops", capacity, n);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  std::vector<cudaEvent_t> ev(2 * static_cast<size_t>(n));
+  for (auto &x : ev)
+    if (cudaEventCreate(&x) != cudaSuccess) return e->fail(MU_ERR_CUDA, "event creation failed");
+  std::vector<double> acc(n, 0.0);
+  int rc = MU_OK;
+  for (int r = 0; r < reps && rc == MU_OK; ++r) {
+    for (int i = 0; i < n && rc == MU_OK; ++i) {
+      cudaEventRecord(ev[2 * i], st);
+      rc = e->launch_op(e->ops[i], st);
+      cudaEventRecord(ev[2 * i + 1], st);
+    }
+    if (rc == MU_OK) rc = mu_check(e->ctx, st);
+    if (rc) break;
+    for (int i = 0; i < n; ++i) {
+      float t = 0;
+      cudaEventElapsedTime(&t, ev[2 * i], ev[2 * i + 1]);
+      acc[i] += t;
+    }
+  }
+  for (auto &x : ev) cudaEventDestroy(x);
+  if (rc) return rc;
+  for (int i = 0; i < n; ++i) {
+    kinds[i] = static_cast<int>(e->ops[i].kind);
+    ms[i] = static_cast<float>(acc[i] / reps);
+    e->op_work(e->ops[i], &flops[i], &bytes[i]);
+  }
+  return MU_OK;
+}
+
+int mu_engine_create(mu_ctx *ctx, mu_engine **out) {
+  if (!ctx || !out) return MU_ERR_INVALID;
+  mu_engine *e = new (std::nothrow) mu_engine();
+  if (!e) return MU_ERR_NOMEM;
+  e->ctx = ctx;
+  *out = e;
+  return MU_OK;
+}
+
+void mu_engine_destroy(mu_engine *e) {
+  if (!e) return;
+  e->release_compiled();
+  delete e;
+}
+
+const char *mu_engine_last_error(const mu_engine *e) { return e ? e->err : "null engine"; }
+
+int mu_engine_set_option(mu_engine *e, const char *name, int value) {
+  if (!e || !name) return MU_ERR_INVALID;
+  const std::string n(name);
+  if (n == "kmode") {
+    if (value != MU_K_LITERAL && value != MU_K_MATH) return e->fail(MU_ERR_INVALID, "kmode must be 0 or 1");
+    e->kmode = value;
+  } else if (n == "use_graph") e->use_graph = value;
+  else if (n == "argmax") e->want_argmax = value;
+  else return e->fail(MU_ERR_INVALID, "unknown option '%s'", name);
+  return MU_OK;
+}
+
+static int finish_load(mu_engine *e, int compute_dtype) {
+  if (compute_dtype != MU_F32 && compute_dtype != MU_BF16)
+    return e->fail(MU_ERR_UNSUPPORTED, "compute dtype %d not implemented (float32, bfloat16)", compute_dtype);
+  e->dtype = compute_dtype;
+  e->loaded = true;
+  return MU_OK;
+}
+
+int mu_engine_load(mu_engine *e, const char *path, int compute_dtype) {
+  if (!e || !path) return MU_ERR_INVALID;
+  e->release_compiled();
+  e->params.clear();
+  e->loaded = false;
+  std::string why;
+  if (!mu::load_artifact(path, &e->config, &e->params, &why))
+    return e->fail(MU_ERR_INVALID, "%s", why.c_str());
+  return finish_load(e, compute_dtype);
+}
+
+int mu_engine_load_memory(mu_engine *e, const char *config_json, int n_tensors,
+                          const char *const *names, const void *const *data, const int *dtypes,
+                          const int *ndims, const long long *shapes, int on_device,
+                          int compute_dtype) {
+  if (!e || !config_json || n_tensors < 0) return MU_ERR_INVALID;
+  e->release_compiled();
+  e->params.clear();
+  e->loaded = false;
+  std::string why;
+  if (!mu::parse_json(config_json, &e->config, &why))
+    return e->fail(MU_ERR_INVALID, "config JSON: %s", why.c_str());
+  size_t s = 0;
+  for (int i = 0; i < n_tensors; ++i) {
+    NamedTensor t;
+    t.dtype = dtypes[i];
+    for (int d = 0; d < ndims[i]; ++d) t.shape.push_back(shapes[s++]);
+    t.data = data[i];
+    t.on_device = on_device != 0;
+    e->params[names[i]] = std::move(t);
+  }
+  return finish_load(e, compute_dtype);
+}
+
+int mu_engine_compile(mu_engine *e, const int *input_shape, int ndim, int input_dtype) {
+  if (!e || !input_shape || ndim <= 0) return MU_ERR_INVALID;
+  if (!e->loaded) return e->fail(MU_ERR_INVALID, "Engine: no module loaded");
+  e->release_compiled();
+  e->weight_bytes = 0;
+  Val v;
+  v.shape.assign(input_shape, input_shape + ndim);
+  v.dtype = input_dtype;
+  for (int s : v.shape)
+    if (s <= 0) return e->fail(MU_ERR_INVALID, "Engine: compile needs a concrete positive input shape");
+  if (input_dtype != MU_I32 && input_dtype != e->dtype)
+    return e->fail(MU_ERR_INVALID, "Engine: input dtype %d does not match compute dtype %d", input_dtype, e->dtype);
+  e->in_shape = v.shape, e->in_dtype = input_dtype;
+  e->input_bytes = static_cast<size_t>(v.numel()) * esize(input_dtype);
+  v.tid = e->new_tensor(e->input_bytes);
+  e->tensors[v.tid].external = true;
+  int rc = e->lower(e->config, "", v, nullptr, nullptr);
+  if (rc) return rc;
+  e->out_tid = v.tid, e->out_shape = v.shape, e->out_dtype = v.dtype;
+  if (e->want_argmax) {
+    Op a;
+    a.kind = OP_ARGMAX, a.N = v.shape.back(), a.M = static_cast<int>(v.numel() / a.N);
+    a.in = v.tid, a.out = e->new_tensor(static_cast<size_t>(a.M) * 4);
+    e->push(a);
+    e->argmax_tid = a.out;
+  }
+  // the outputs stay live to the end of the plan
+  const int last = static_cast<int>(e->ops.size());
+  e->touch(e->out_tid, last);
+  if (e->argmax_tid >= 0) e->touch(e->argmax_tid, last);
+  rc = e->plan_and_allocate();
+  if (rc) return rc;
+  if (e->use_graph) {
+    if (cudaStreamCreateWithFlags(&e->cap_stream, cudaStreamNonBlocking) != cudaSuccess)
+      return e->fail(MU_ERR_CUDA, "stream creation failed");
+    // warm-up launch outside capture (sets per-kernel attributes), then capture
+    rc = e->launch_all(e->cap_stream);
+    if (rc) return rc;
+    rc = mu_check(e->ctx, e->cap_stream);
+    if (rc) return e->fail(rc, "warm-up forward failed: %s", mu_last_error(e->ctx));
+    if (cudaStreamBeginCapture(e->cap_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
+      return e->fail(MU_ERR_CUDA, "graph capture could not start");
+    rc = e->launch_all(e->cap_stream);
+    cudaError_t ce = cudaStreamEndCapture(e->cap_stream, &e->graph);
+    if (rc) return rc;
+    if (ce != cudaSuccess) return e->fail(MU_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
+    ce = cudaGraphInstantiate(&e->gexec, e->graph, 0);
+    if (ce != cudaSuccess) return e->fail(MU_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(ce));
+  }
+  e->compiled = true;
+  return MU_OK;
+}
+
+int mu_engine_output_shape(const mu_engine *e, int *shape, int *ndim, int *dtype) {
+  if (!e || !e->compiled || !shape || !ndim) return MU_ERR_INVALID;
+  *ndim = static_cast<int>(e->out_shape.size());
+  for (size_t i = 0; i < e->out_shape.size() && i < 8; ++i) shape[i] = e->out_shape[i];
+  if (dtype) *dtype = e->out_dtype;
+  return MU_OK;
+}
+
+int mu_engine_stats(const mu_engine *e, long long *arena_bytes, long long *weight_bytes,
+                    long long *n_ops, long long *n_launches, long long *unplanned_bytes) {
+  if (!e || !e->compiled) return MU_ERR_INVALID;
+  if (arena_bytes) *arena_bytes = static_cast<long long>(e->arena_bytes);
+  if (weight_bytes) *weight_bytes = static_cast<long long>(e->weight_bytes);
+  if (n_ops) *n_ops = static_cast<long long>(e->ops.size());
+  if (n_launches) *n_launches = e->n_launches;
+  if (unplanned_bytes) {
+    long long s = 0;
+    for (auto &t : e->tensors)
+      if (t.alias_of < 0 && !t.external) s += static_cast<long long>(t.bytes);
+    *unplanned_bytes = s;
+  }
+  return MU_OK;
+}
+
+// Engine::run (src/inference.hpp:541-610): strict input contract, forward, output.
+// input/output may be host or device pointers; argmax_out (optional) receives
+// int32 indices over the last dim when the "argmax" option is set.
+int mu_engine_run(mu_engine *e, const void *input, int input_on_host, void *output,
+                  int output_on_host, int32_t *argmax_out, int argmax_on_host, void *stream) {
+  if (!e) return MU_ERR_INVALID;
+  if (!e->compiled) return e->fail(MU_ERR_INVALID, "Engine: run() called before compile()");
+  if (!input) return e->fail(MU_ERR_INVALID, "Engine: null input");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = mu_copy(e->ctx, e->input_buf, input, e->input_bytes,
+                   input_on_host ? MU_COPY_H2D : MU_COPY_D2D, st);
+  if (rc) return e->fail(rc, "input copy failed: %s", mu_last_error(e->ctx));
+  if (e->gexec) {
+    cudaError_t ce = cudaGraphLaunch(e->gexec, st);
+    if (ce != cudaSuccess) return e->fail(MU_ERR_CUDA, "graph launch failed: %s", cudaGetErrorString(ce));
+  } else {
+    rc = e->launch_all(st);
+    if (rc) return rc;
+  }
+  if (output) {
+    size_t bytes = esize(e->out_dtype);
+    for (int s : e->out_shape) bytes *= s;
+    rc = mu_copy(e->ctx, output, e->tptr(e->out_tid), bytes, output_on_host ? MU_COPY_D2H : MU_COPY_D2D, st);
+    if (rc) return e->fail(rc, "output copy failed: %s", mu_last_error(e->ctx));
+  }
+  if (argmax_out && e->argmax_tid >= 0) {
+    size_t rows = 1;
+    for (size_t i = 0; i + 1 < e->out_shape.size(); ++i) rows *= e->out_shape[i];
+    rc = mu_copy(e->ctx, argmax_out, e->tptr(e->argmax_tid), rows * 4,
+                 argmax_on_host ? MU_COPY_D2H : MU_COPY_D2D, st);
+    if (rc) return e->fail(rc, "argmax copy failed: %s", mu_last_error(e->ctx));
+  }
+  if (output_on_host || (argmax_out && argmax_on_host)) {
+    rc = mu_check(e->ctx, st);
+    if (rc) return e->fail(rc, "%s", mu_last_error(e->ctx));
+  }
+  return MU_OK;
+}
+
+// Device address of the planned output (valid until the next compile); lets a
+// caller consume logits in place instead of copying 4 GB around.
+void *mu_engine_output_ptr(const mu_engine *e) { return (e && e->compiled) ? e->tptr(e->out_tid) : nullptr; }
+void *mu_engine_argmax_ptr(const mu_engine *e) {
+  return (e && e->compiled && e->argmax_tid >= 0) ? e->tptr(e->argmax_tid) : nullptr;
+}
+
+} // extern "C"

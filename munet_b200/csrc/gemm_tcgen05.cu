@@ -33,7 +33,11 @@ template <int BN> struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  // epilogue staging: per epilogue warp two [32 rows x 64 cols] bf16 boxes (128-byte rows)
+  static constexpr int OUT_BOX_BYTES = 32 * 128;
+  static constexpr int OUT_BYTES = 4 * 2 * OUT_BOX_BYTES;
+  static constexpr int SMEM_BYTES =
+      STAGES * STAGE_BYTES + OUT_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ float epi_math(float x, float bias, float res, bool has_bias,
@@ -87,22 +91,97 @@ __device__ __forceinline__ float epi_math(float x, float bias, float res, bool h
   return x;
 }
 
+// Same chain with the activation fixed at compile time (hot path).
+template <int ACT>
+__device__ __forceinline__ float epi_math_t(float x, float bias, float res, float alpha,
+                                            bool has_alpha, bool rnd) {
+  if (rnd) {
+    x = bf16_round(x);
+    if (has_alpha)
+      x = bf16_round(x * alpha);
+    x = bf16_round(x + bias); // bias == 0 when absent: value-preserving
+    if (ACT == ACT_RELU) {
+      x = fmaxf(x, 0.0f);
+    } else if (ACT == ACT_GELU) {
+      const float t = bf16_round(x * 1.703125f); // bf16(1.702)
+      const float s = bf16_round(__fdividef(1.0f, 1.0f + __expf(-t)));
+      x = bf16_round(x * s);
+    } else if (ACT == ACT_SIGMOID) {
+      x = bf16_round(__fdividef(1.0f, 1.0f + __expf(-x)));
+    } else if (ACT == ACT_TANH) {
+      const float t = bf16_round(x * 2.0f);
+      const float s = bf16_round(__fdividef(1.0f, 1.0f + __expf(-t)));
+      x = bf16_round(s * 2.0f - 1.0f);
+    }
+    x = bf16_round(x + res);
+  } else {
+    if (has_alpha)
+      x = x * alpha;
+    x = x + bias;
+    if (ACT == ACT_RELU) {
+      x = fmaxf(x, 0.0f);
+    } else if (ACT == ACT_GELU) {
+      x = x * __fdividef(1.0f, 1.0f + __expf(-1.702f * x));
+    } else if (ACT == ACT_SIGMOID) {
+      x = __fdividef(1.0f, 1.0f + __expf(-x));
+    } else if (ACT == ACT_TANH) {
+      x = 2.0f * __fdividef(1.0f, 1.0f + __expf(-2.0f * x)) - 1.0f;
+    }
+    x = x + res;
+  }
+  return x;
+}
+
+// One half (32 accumulator columns = four 16-byte chunks) of a staged 64-column
+// group: optional residual is read from the staging row (where a TMA load put
+// it), the result is written back to the same swizzled chunk.
+template <int ACT>
+__device__ __forceinline__ void epi_half(const uint32_t (&r)[32], uint8_t *row, int lane7,
+                                         int half, const __nv_bfloat16 *bias, bool has_res,
+                                         float alpha, bool has_alpha, bool rnd) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int cc = half * 4 + c;
+    uint4 *slot = reinterpret_cast<uint4 *>(row + ((cc ^ lane7) << 4));
+    uint4 bv = make_uint4(0, 0, 0, 0), rv = make_uint4(0, 0, 0, 0);
+    if (bias)
+      bv = __ldg(reinterpret_cast<const uint4 *>(bias) + cc);
+    if (has_res)
+      rv = *slot;
+    const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w}, rw[4] = {rv.x, rv.y, rv.z, rv.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float v0 = epi_math_t<ACT>(__uint_as_float(r[c * 8 + 2 * j]), bf16_lo(bw[j]),
+                                       bf16_lo(rw[j]), alpha, has_alpha, rnd);
+      const float v1 = epi_math_t<ACT>(__uint_as_float(r[c * 8 + 2 * j + 1]), bf16_hi(bw[j]),
+                                       bf16_hi(rw[j]), alpha, has_alpha, rnd);
+      ow[j] = pack_bf16x2(v0, v1);
+    }
+    *slot = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+
 template <int BN, bool B_KMAJOR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
-                         const __grid_constant__ CUtensorMap tmB, GemmShape sh, Epilogue ep,
+                         const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmC,
+                         const __grid_constant__ CUtensorMap tmR, GemmShape sh, Epilogue ep,
                          int *status) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atoms.
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t *bar_base = smem + STAGES * Cfg::STAGE_BYTES;
+  uint8_t *out_stage = smem + STAGES * Cfg::STAGE_BYTES;
+  uint8_t *bar_base = out_stage + Cfg::OUT_BYTES;
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(bar_base);
   uint64_t *empty_bar = full_bar + STAGES;
   uint64_t *tfull_bar = empty_bar + STAGES;
   uint64_t *tempty_bar = tfull_bar + 2;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty_bar + 2);
+  uint64_t *res_bar = tempty_bar + 2; // [4 epilogue warps][2 buffers]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(res_bar + 8);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -121,9 +200,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], 4);
     }
+    for (int b = 0; b < 8; ++b)
+      mbar_init(&res_bar[b], 1);
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    if (ep.tma_out) {
+      prefetch_tmap(&tmC);
+      if (ep.residual)
+        prefetch_tmap(&tmR);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -232,19 +318,104 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const bool split = ep.split_T > 0;
     const int HD = ep.split_H * ep.split_D;
     int it = 0;
+    int gcount = 0; // staged 64-column groups issued by this warp (selects the staging buffer)
     bool ok = true;
     for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       const int nt = static_cast<int>(tile % tiles_n);
       const int mt = static_cast<int>((tile / tiles_n) % tiles_m);
       const int bt = static_cast<int>(tile / (1ll * tiles_n * tiles_m));
-      const int buf = it & 1;
+      const int buf_idx = it & 1;
       const uint32_t use = static_cast<uint32_t>(it >> 1);
-      if (!mbar_wait(&tfull_bar[buf], use & 1)) {
+      if (!mbar_wait(&tfull_bar[buf_idx], use & 1)) {
         atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
         ok = false;
         break;
       }
       tc_fence_after();
+      if (ep.tma_out) {
+        // ---- staged epilogue: TMEM -> registers -> swizzled smem box -> TMA store ----
+        const int m0 = mt * BM + q * 32; // first row of this warp's 32-row slab
+        uint8_t *wbuf = out_stage + (warp - 2) * 2 * Cfg::OUT_BOX_BYTES;
+        const bool has_res = ep.residual != nullptr;
+        const bool has_alpha = ep.alpha != 1.0f;
+        if (m0 < sh.M) {
+#pragma unroll 1
+          for (int g = 0; g < BN / 64; ++g) {
+            const int n0 = nt * BN + g * 64;
+            if (n0 >= sh.N)
+              break; // warp-uniform
+            const int bsel = gcount & 1;
+            uint8_t *buf = wbuf + bsel * Cfg::OUT_BOX_BYTES;
+            // tensor-map coordinates, dimensions ordered by ascending stride
+            int c0, c1, c2, c3, c4;
+            if (ep.tma_mode == 2) { // [which][B][H][T][D]
+              c0 = n0 % ep.split_D, c1 = m0 % ep.split_T, c2 = (n0 / ep.split_D) % ep.split_H;
+              c3 = m0 / ep.split_T, c4 = n0 / HD;
+            } else if (ep.tma_mode == 1) { // [B][T][H][D]: batch = (b, h)
+              c0 = n0, c1 = bt % ep.batch_div, c2 = m0, c3 = bt / ep.batch_div, c4 = 0;
+            } else { // [batch][M][N]
+              c0 = n0, c1 = m0, c2 = bt, c3 = 0, c4 = 0;
+            }
+            if (lane == 0) {
+              bulk_wait_read<1>(); // the store issued from this buffer two groups ago has read it
+              if (has_res) {
+                mbar_arrive_expect_tx(&res_bar[(warp - 2) * 2 + bsel], Cfg::OUT_BOX_BYTES);
+                tma_load_5d(buf, &tmR, &res_bar[(warp - 2) * 2 + bsel], c0, c1, c2, c3, c4);
+              }
+            }
+            __syncwarp();
+            uint32_t r0[32], r1[32];
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                   static_cast<uint32_t>(buf_idx * BN + g * 64);
+            tmem_ld_32x32(taddr, r0);
+            tmem_ld_32x32(taddr + 32, r1);
+            tmem_ld_wait();
+            if (has_res) {
+              if (!mbar_wait(&res_bar[(warp - 2) * 2 + bsel], (gcount >> 1) & 1)) {
+                atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+                ok = false;
+                break;
+              }
+            }
+            uint8_t *row = buf + lane * 128;
+            const __nv_bfloat16 *bp = bias ? bias + n0 : nullptr;
+            const int l7 = lane & 7;
+            switch (ep.act) {
+            case ACT_RELU:
+              epi_half<ACT_RELU>(r0, row, l7, 0, bp, has_res, alpha, has_alpha, rnd);
+              epi_half<ACT_RELU>(r1, row, l7, 1, bp, has_res, alpha, has_alpha, rnd);
+              break;
+            case ACT_GELU:
+              epi_half<ACT_GELU>(r0, row, l7, 0, bp, has_res, alpha, has_alpha, rnd);
+              epi_half<ACT_GELU>(r1, row, l7, 1, bp, has_res, alpha, has_alpha, rnd);
+              break;
+            case ACT_SIGMOID:
+              epi_half<ACT_SIGMOID>(r0, row, l7, 0, bp, has_res, alpha, has_alpha, rnd);
+              epi_half<ACT_SIGMOID>(r1, row, l7, 1, bp, has_res, alpha, has_alpha, rnd);
+              break;
+            case ACT_TANH:
+              epi_half<ACT_TANH>(r0, row, l7, 0, bp, has_res, alpha, has_alpha, rnd);
+              epi_half<ACT_TANH>(r1, row, l7, 1, bp, has_res, alpha, has_alpha, rnd);
+              break;
+            default:
+              epi_half<ACT_NONE>(r0, row, l7, 0, bp, has_res, alpha, has_alpha, rnd);
+              epi_half<ACT_NONE>(r1, row, l7, 1, bp, has_res, alpha, has_alpha, rnd);
+            }
+            fence_proxy_async(); // generic-proxy writes → visible to the TMA store
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_5d(&tmC, buf, c0, c1, c2, c3, c4);
+              bulk_commit();
+            }
+            ++gcount;
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&tempty_bar[buf_idx]);
+        continue;
+      }
       const int m = mt * BM + q * 32 + lane;
       const bool row_ok = m < sh.M;
       const long long batch_off =
@@ -263,7 +434,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           break; // warp-uniform
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                          static_cast<uint32_t>(buf * BN + chunk * 32),
+                          static_cast<uint32_t>(buf_idx * BN + chunk * 32),
                       r);
         tmem_ld_wait();
         const bool full = (n0 + 32 <= sh.N) && ep.vec_ok;
@@ -339,8 +510,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       tc_fence_before();
       __syncwarp();
       if (lane == 0)
-        mbar_arrive(&tempty_bar[buf]);
+        mbar_arrive(&tempty_bar[buf_idx]);
     }
+    if (lane == 0)
+      bulk_wait<0>(); // every TMA store of this warp has completed before the CTA exits
   }
 
   tc_fence_before();
@@ -389,6 +562,69 @@ static bool encode_map3(CUtensorMap *map, const void *base, unsigned long long d
   return r == CUDA_SUCCESS;
 }
 
+// rank-5 bf16 map, 128-byte swizzle; dims/strides in elements, ascending strides.
+static bool encode_map5(CUtensorMap *map, const void *base, const unsigned long long (&d)[5],
+                        const unsigned long long (&st)[4], const unsigned (&bx)[5]) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn)
+    return false;
+  cuuint64_t dims[5], strides[4];
+  cuuint32_t box[5], estr[5] = {1, 1, 1, 1, 1};
+  for (int i = 0; i < 5; ++i)
+    dims[i] = d[i], box[i] = bx[i];
+  for (int i = 0; i < 4; ++i)
+    strides[i] = st[i] * 2ull;
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void *>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// Output / residual tensor maps for the staged epilogue. Returns false when the
+// output addressing cannot be expressed (the kernel then stores directly).
+static bool encode_out_maps(const Epilogue &ep, const GemmShape &sh, CUtensorMap *tmC,
+                            CUtensorMap *tmR, int *mode) {
+  auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!al(ep.c) || (ep.residual && !al(ep.residual)) || (ep.bias && !al(ep.bias)))
+    return false;
+  unsigned long long d[5], st[4];
+  unsigned bx[5] = {64, 32, 1, 1, 1};
+  const unsigned long long N = sh.N, M = sh.M;
+  if (ep.split_T > 0) {
+    const unsigned long long D = ep.split_D, T = ep.split_T, H = ep.split_H;
+    if (D % 64 || T % 32 || M % T || N % (H * D) || ep.split_which_stride % 8 ||
+        (N / (H * D) > 1 && ep.split_which_stride < M / T * H * T * D))
+      return false;
+    d[0] = D, d[1] = T, d[2] = H, d[3] = M / T, d[4] = N / (H * D);
+    st[0] = D, st[1] = T * D, st[2] = H * T * D;
+    st[3] = d[4] > 1 ? static_cast<unsigned long long>(ep.split_which_stride) : st[2] * d[3];
+    *mode = 2;
+  } else if (ep.batch_div > 1) {
+    const unsigned long long H = ep.batch_div, lo = ep.batch_lo, ld = ep.ldc, hi = ep.batch_hi;
+    if (sh.batch % ep.batch_div || lo % 8 || ld % 8 || hi % 8 || lo < N || ld < lo * H ||
+        (sh.batch / ep.batch_div > 1 && hi < ld * M))
+      return false;
+    d[0] = N, d[1] = H, d[2] = M, d[3] = sh.batch / ep.batch_div, d[4] = 1;
+    st[0] = lo, st[1] = ld, st[2] = d[3] > 1 ? hi : ld * M, st[3] = st[2] * d[3];
+    bx[1] = 1, bx[2] = 32;
+    *mode = 1;
+  } else {
+    const unsigned long long ld = ep.ldc, hi = ep.batch_hi;
+    if (ld % 8 || ld < N || (sh.batch > 1 && (hi % 8 || hi < ld * M)))
+      return false;
+    d[0] = N, d[1] = M, d[2] = sh.batch, d[3] = 1, d[4] = 1;
+    st[0] = ld, st[1] = sh.batch > 1 ? hi : ld * M, st[2] = st[1] * d[2], st[3] = st[2];
+    *mode = 0;
+  }
+  if (!encode_map5(tmC, ep.c, d, st, bx))
+    return false;
+  if (ep.residual && !encode_map5(tmR, ep.residual, d, st, bx))
+    return false;
+  if (!ep.residual)
+    *tmR = *tmC;
+  return true;
+}
+
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Returns 0 ok, 1 shape/alignment not supported by this kernel, 2 launch/encode failure.
@@ -428,6 +664,13 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
     return 2;
   const long long tiles = 1ll * ((sh.M + BM - 1) / BM) * ((sh.N + BN - 1) / BN) * sh.batch;
   const int grid = static_cast<int>(tiles < num_sms ? tiles : num_sms);
+  Epilogue ep2 = ep;
+  CUtensorMap tmC, tmR;
+  int mode = 0;
+  ep2.tma_out = encode_out_maps(ep, sh, &tmC, &tmR, &mode) ? 1 : 0;
+  ep2.tma_mode = mode;
+  if (!ep2.tma_out)
+    tmC = tmR = tmA; // placeholders, never dereferenced
 
 #define MU_LAUNCH(BN_, KM_)                                                                      \
   do {                                                                                           \
@@ -439,7 +682,8 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
         return 2;                                                                                \
       attr_set = true;                                                                           \
     }                                                                                            \
-    kern<<<grid, GEMM_THREADS, GemmCfg<BN_>::SMEM_BYTES, stream>>>(tmA, tmB, s2, ep, status);    \
+    kern<<<grid, GEMM_THREADS, GemmCfg<BN_>::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, s2, ep2,     \
+                                                                   status);                       \
   } while (0)
 
   if (op.b_kmajor) {

@@ -1,0 +1,142 @@
+"""GPU parity of the compiled executor against the CPU checker: decoder forward
+(bf16 2e-2, fp32 1e-4), MLP artifacts (fp32 logits bit-exact, argmax bit-exact),
+the reference's own known-answer artifacts, shape-contract and error behaviour."""
+import numpy as np
+import pytest
+
+import oracle
+from oracle import BF16, F32, I32
+from tests.test_oracle_vs_ref import gpt_params
+from tests.util import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import munet_b200 as mb
+    c = mb.Context(0)
+    yield c
+    c.close()
+
+
+def make_engine(ctx, dtype, **kw):
+    from munet_b200.inference import Engine
+    return Engine(ctx=ctx, compute_dtype=dtype, **kw)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("kmode", [oracle.K_LITERAL, oracle.K_MATH])
+@pytest.mark.parametrize("B,T,V,d,H,L", [(2, 32, 96, 64, 2, 2), (3, 24, 50, 48, 3, 1)])
+def test_gpt_decoder_matches_checker(ctx, dtype, kmode, B, T, V, d, H, L):
+    from munet_b200.inference import gpt_decoder_config, gpt_param_names
+    rng = np.random.default_rng(B * T + d)
+    ps = gpt_params(rng, V, T, d, L, dtype, std=0.08)
+    ids = rng.integers(0, V, (B, T)).astype(np.int32)
+    want = oracle.port().gpt_forward(ids, ps, V, d, H, L, dtype, kmode=kmode)
+    eng = make_engine(ctx, dtype, kmode=kmode, argmax=True)
+    eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)), tensor_dtype=dtype)
+    eng.compile((B, T), I32)
+    got, am = eng.run(ids)
+    assert got.shape == (B, T, V)
+    assert_close(got, want, dtype, what="decoder logits")
+    # argmax is computed on the device from the device logits: first-max rule
+    assert np.array_equal(am, oracle.port().argmax(got, dtype))
+    agree = float((am == oracle.port().argmax(want, dtype)).mean())
+    assert agree >= (0.999 if dtype == F32 else 0.9), f"argmax agreement {agree}"
+    st = eng.stats()
+    assert st["arena_bytes"] < st["unplanned_bytes"]  # the buffer plan reuses memory
+    eng.close()
+
+
+def mlp_artifact(tmp_path, rng, sizes, acts, name="mlp.npz", producer="munet"):
+    from munet_b200.inference import save_deploy
+    layers, tensors, idx = [], {}, 0
+    for i in range(len(sizes) - 1):
+        layers.append({"type": "Linear", "in_features": sizes[i], "out_features": sizes[i + 1], "bias": True})
+        tensors[f"{idx}.weight"] = (rng.standard_normal((sizes[i], sizes[i + 1])) *
+                                    np.sqrt(2.0 / sizes[i])).astype(np.float32)
+        tensors[f"{idx}.bias"] = np.zeros(sizes[i + 1], np.float32)
+        idx += 1
+        if i < len(acts) and acts[i]:
+            layers.append({"type": acts[i]})
+            idx += 1
+    path = str(tmp_path / name)
+    save_deploy(path, {"type": "Sequential", "layers": layers}, tensors, producer=producer)
+    return path, tensors
+
+
+def mlp_oracle(x, tensors, acts):
+    h, idx = x, 0
+    for i in range(len(acts) + 1):
+        a = acts[i] if i < len(acts) and acts[i] else None
+        h = oracle.port().linear(h, tensors[f"{idx}.weight"], tensors[f"{idx}.bias"], F32,
+                                 {"ReLU": "relu", "GELU": "gelu", None: "none"}[a])
+        idx += 2 if a else 1
+    return h
+
+
+def test_mlp_config_fp32_bit_exact(ctx, tmp_path):
+    """784→512→ReLU→512→ReLU→10, batch 256: logits and argmax identical to the reference."""
+    rng = np.random.default_rng(1001)
+    path, tensors = mlp_artifact(tmp_path, rng, [784, 512, 512, 10], ["ReLU", "ReLU"])
+    x = np.random.default_rng(2001).random((256, 784), dtype=np.float32)
+    want = mlp_oracle(x, tensors, ["ReLU", "ReLU"])
+    eng = make_engine(ctx, F32, argmax=True).load(path).compile((256, 784))
+    got, am = eng.run(x)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(am, oracle.port().argmax(want, F32))
+    if oracle.have_ref():
+        ref = oracle.ref().engine_run_npz(path, x)
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+    eng.close()
+
+
+def test_reference_known_answers(ctx, tmp_path):
+    """Artifacts with the values of the reference's own engine tests
+    (tests/test_inference.cpp:887-919 and :990-1022)."""
+    from munet_b200.inference import save_deploy
+    p1 = str(tmp_path / "kat1.npz")
+    save_deploy(p1, {"type": "Sequential", "layers": [
+        {"type": "Linear", "in_features": 2, "out_features": 2, "bias": True}, {"type": "ReLU"}]},
+        {"0.weight": np.array([[1, -1], [0.5, 2]], np.float32), "0.bias": np.array([0.25, -0.75], np.float32)})
+    eng = make_engine(ctx, F32).load(p1).compile((1, 2))
+    assert np.array_equal(eng.run(np.array([[2, 3]], np.float32)), np.array([[3.75, 3.25]], np.float32))
+    eng.close()
+    p2 = str(tmp_path / "kat2.npz")
+    save_deploy(p2, {"type": "Linear", "in_features": 2, "out_features": 2, "bias": True},
+                {"weight": np.array([[2, 0], [0, 3]], np.float32), "bias": np.array([1, -2], np.float32)},
+                producer="munet_nn")
+    eng = make_engine(ctx, F32).load(p2).compile((1, 2))
+    assert np.array_equal(eng.run(np.array([[4, 5]], np.float32)), np.array([[9, 13]], np.float32))
+    eng.close()
+    # Dropout is the identity in eval mode (tests/test_inference.cpp:921-939,1024-1060)
+    p3 = str(tmp_path / "kat3.npz")
+    save_deploy(p3, {"type": "Sequential", "layers": [
+        {"type": "Dropout", "p": 0.9}, {"type": "Linear", "in_features": 2, "out_features": 2, "bias": True}]},
+        {"1.weight": np.eye(2, dtype=np.float32), "1.bias": np.zeros(2, np.float32)})
+    eng = make_engine(ctx, F32).load(p3).compile((1, 2))
+    assert np.array_equal(eng.run(np.array([[7, 11]], np.float32)), np.array([[7, 11]], np.float32))
+    eng.close()
+
+
+def test_contract_and_errors(ctx, tmp_path):
+    import munet_b200 as mb
+    from munet_b200.inference import save_deploy
+    rng = np.random.default_rng(0)
+    path, _ = mlp_artifact(tmp_path, rng, [8, 4], [])
+    eng = make_engine(ctx, F32).load(path)
+    with pytest.raises(mb.MuNetError, match="before compile"):
+        eng.run(np.zeros((2, 8), np.float32))
+    eng.compile((2, 8))
+    with pytest.raises(mb.MuNetError, match="shape"):  # strict shape contract (tests/test_inference.cpp:402-438)
+        eng.run(np.zeros((3, 8), np.float32))
+    eng.close()
+    bad = str(tmp_path / "custom.npz")  # unknown node type must be rejected (tests/test_inference.cpp:974-988)
+    save_deploy(bad, {"type": "__custom__"}, {})
+    eng = make_engine(ctx, F32).load(bad)
+    with pytest.raises(mb.MuNetError, match="Unsupported serialized module type"):
+        eng.compile((1, 2))
+    eng.close()
+    with pytest.raises(mb.MuNetError, match="Unable to open"):
+        make_engine(ctx, F32).load(str(tmp_path / "missing.npz"))
