@@ -21,6 +21,8 @@ int launch_embedding(const int *, const void *, const void *, void *, long long,
 int launch_eltwise(const void *, const void *, const void *, void *, long long, int, int, int, int,
                    cudaStream_t);
 int launch_argmax(const void *, int *, long long, int, int, cudaStream_t);
+int launch_attention_tcgen05(const void *, const void *, const void *, void *, int, int, int, int,
+                             int, int, int *, cudaStream_t);
 } // namespace mu
 
 struct mu_ctx {
@@ -345,10 +347,12 @@ int mu_linear_qkv(mu_ctx *ctx, const void *x, const void *w_qkv, const void *bia
 }
 
 size_t mu_attention_workspace_bytes(int B, int H, int T, int D, int dtype) {
-  (void)D;
   if (B <= 0 || H <= 0 || T <= 0)
     return 0;
-  // one [B*H, T, T] score/probability buffer (softmax runs in place)
+  // the fused bf16 kernel (head size 64 or 128, T a multiple of 8) needs none
+  if (dtype == MU_BF16 && (D == 64 || D == 128) && T % 8 == 0)
+    return 0;
+  // composed path: one [B*H, T, T] score/probability buffer (softmax runs in place)
   return static_cast<size_t>(B) * H * T * T * esize(dtype);
 }
 
@@ -364,10 +368,22 @@ int mu_attention(mu_ctx *ctx, const void *q, const void *k, const void *v, void 
   if (B == 0 || T == 0)
     return MU_OK;
   MU_REQUIRE(q && k && v && out, "attention: null pointer");
-  MU_REQUIRE(workspace && workspace_bytes >= mu_attention_workspace_bytes(B, H, T, D, dtype),
-             "attention: workspace too small (%zu < %zu bytes)", workspace_bytes,
-             mu_attention_workspace_bytes(B, H, T, D, dtype));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "attention: cannot select device %d", ctx->device);
+  if (dtype == MU_BF16 && !ctx->force_simt) {
+    // fused tcgen05 kernel: scores and probabilities stay on chip, no workspace
+    int rc = mu::launch_attention_tcgen05(q, k, v, out, B, H, T, D, causal,
+                                          kmode == MU_K_LITERAL ? 1 : 0, ctx->d_status, st);
+    if (rc == 0)
+      return MU_OK;
+    if (rc == 2)
+      return cuda_fail(ctx, "attention", cudaGetLastError());
+  }
+  // composed path (any head size, float32): batched GEMM → softmax → batched GEMM
+  const size_t need = static_cast<size_t>(B) * H * T * T * esize(dtype);
+  MU_REQUIRE(workspace && workspace_bytes >= need,
+             "attention: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
   const int BH = B * H;
   const long long Ntot = 1ll * BH * T;
   const int E = H * D;

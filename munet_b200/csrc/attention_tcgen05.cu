@@ -1,0 +1,485 @@
+// Fused attention core for sm_100a (bf16): S = scale·Q·K', causal mask, online
+// softmax, O = P·V — scores and probabilities never touch HBM.
+//
+// Replaces the scale-mul → mask build → masked_fill → softmax → matmul chain of
+// MultiHeadAttention::forward_impl (src/nn/attention.hpp:64-99), which the
+// reference runs as five full passes over a [B·H·T, B·H·T] matrix (two of them
+// on the host). Only the row's own head block is ever touched here.
+//
+// One CTA = one (head, 128-query tile); 192 threads:
+//   warp 0    TMA producer: Q once, then K/V tiles of 128 keys through a ring.
+//   warp 1    tcgen05.mma issuer: S_j = Q·K_j' (M=128,N=128) into a double-
+//             buffered TMEM S tile, O_j = P_j·V_j (M=128,N=D) into a double-
+//             buffered TMEM O tile.
+//   warps 2-5 one query row per thread (TMEM lane = row): rounding/scale/mask,
+//             running max and sum, P_j → swizzled smem (A operand of P·V),
+//             O accumulated in registers with the online-softmax correction,
+//             final O/l staged to smem and written with TMA (token-major,
+//             heads merged: the [B,T,H·D] layout out_proj consumes).
+// K addressing: LITERAL reads K's [N,D] buffer as a row-major [D,N] matrix
+// (what the reference computes, see include/munet_b200.h), MATH is Q·Kᵀ.
+// Numerics follow the reference's bf16 pipeline where it is cheap to: scores are
+// rounded to bf16, multiplied by the bf16-rounded scale and rounded again before
+// the softmax; P is rounded to bf16 before P·V; fp32 accumulation elsewhere.
+#include "common.h"
+#include "ptx.cuh"
+#include <cuda.h>
+
+namespace mu {
+
+constexpr int ATT_THREADS = 192;
+constexpr int BQ = 128, BKV = 128;
+
+template <int D> struct AttCfg {
+  static constexpr int Q_BYTES = BQ * D * 2;
+  static constexpr int K_BYTES = BKV * D * 2;
+  static constexpr int V_BYTES = BKV * D * 2;
+  static constexpr int P_BYTES = BQ * BKV * 2; // one of two buffers
+  static constexpr int STAGES = D == 128 ? 2 : 4;
+  static constexpr int KV_STAGE = K_BYTES + V_BYTES;
+  static constexpr int SMEM_BYTES = Q_BYTES + STAGES * KV_STAGE + 2 * P_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 512; // S0 S1 at 0/128, O0 O1 at 256/256+D
+};
+
+struct AttParams {
+  int T, H, BH;
+  int causal;
+  float scale;   // 1/sqrt(D) as float
+  int n_qtiles;
+};
+
+template <int D, bool LITERAL>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
+                         const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmV,
+                         const __grid_constant__ CUtensorMap tmO, AttParams prm, int *status) {
+  using Cfg = AttCfg<D>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int DB = D / 64; // 64-element boxes along the head dim
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t *sQ = smem;
+  uint8_t *sKV = sQ + Cfg::Q_BYTES;
+  uint8_t *sP = sKV + STAGES * Cfg::KV_STAGE;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(sP + 2 * Cfg::P_BYTES);
+  uint64_t *q_full = bars;
+  uint64_t *kv_full = q_full + 1;
+  uint64_t *kv_empty = kv_full + STAGES;
+  uint64_t *s_full = kv_empty + STAGES;
+  uint64_t *s_empty = s_full + 2;
+  uint64_t *p_full = s_empty + 2;
+  uint64_t *o_full = p_full + 2;
+  uint64_t *o_empty = o_full + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  // heavy (late) query tiles first: under the causal mask tile i has i+1 key tiles
+  const int qt = prm.n_qtiles - 1 - static_cast<int>(blockIdx.x);
+  const int q0 = qt * BQ;
+  const int kv_len = prm.causal ? min(prm.T, q0 + BQ) : prm.T;
+  const int nk = (kv_len + BKV - 1) / BKV;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&s_empty[b], 4);
+      mbar_init(&p_full[b], 4);
+      mbar_init(&o_full[b], 1);
+      mbar_init(&o_empty[b], 4);
+    }
+    fence_barrier_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+      for (int db = 0; db < DB; ++db)
+        tma_load_3d(sQ + db * (BQ * 128), &tmQ, q_full, db * 64, q0, bh);
+      bool ok = true;
+      for (int j = 0; j < nk && ok; ++j) {
+        const int stage = j % STAGES;
+        if (!mbar_wait(&kv_empty[stage], ((j / STAGES) & 1) ^ 1)) {
+          atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
+          ok = false;
+          break;
+        }
+        uint8_t *sK = sKV + stage * Cfg::KV_STAGE;
+        uint8_t *sV = sK + Cfg::K_BYTES;
+        mbar_arrive_expect_tx(&kv_full[stage], Cfg::KV_STAGE);
+        const int k0 = j * BKV;
+        if (LITERAL) {
+          // K' tile = rows d, columns bh*T + k0.. of the [D, N] view: [dbox][nbox][64 x 128 B]
+#pragma unroll
+          for (int db = 0; db < DB; ++db)
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb)
+              tma_load_3d(sK + (db * 2 + nb) * 8192, &tmK, &kv_full[stage],
+                          bh * prm.T + k0 + nb * 64, db * 64, 0);
+        } else {
+#pragma unroll
+          for (int db = 0; db < DB; ++db)
+            tma_load_3d(sK + db * (BKV * 128), &tmK, &kv_full[stage], db * 64, k0, bh);
+        }
+        // V tile as MN-major B operand: [keybox][dbox][64 keys x 128 B]
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int db = 0; db < DB; ++db)
+            tma_load_3d(sV + (kb * DB + db) * 8192, &tmV, &kv_full[stage], db * 64,
+                        k0 + kb * 64, bh);
+      }
+      if (!ok)
+        for (int i = 0; i < 64; ++i)
+          __nanosleep(1000);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc(1u, 0u, LITERAL ? 1u : 0u, BQ, BKV);
+      constexpr uint32_t idesc_pv = make_idesc(1u, 0u, 1u, BQ, D);
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok)
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+      const uint32_t q_addr = smem_u32(sQ);
+      auto issue_pv = [&](int i) -> bool {
+        const int b = i & 1;
+        const uint32_t par = static_cast<uint32_t>(i >> 1) & 1;
+        if (!mbar_wait(&p_full[b], par) || !mbar_wait(&o_empty[b], par ^ 1))
+          return false;
+        tc_fence_after();
+        const uint32_t p_addr = smem_u32(sP + b * Cfg::P_BYTES);
+        const uint32_t v_addr = smem_u32(sKV + (i % STAGES) * Cfg::KV_STAGE + Cfg::K_BYTES);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k) {
+          const uint64_t ad = make_smem_desc(p_addr + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc(v_addr + (k / 4) * (DB * 8192) + (k % 4) * 2048, 8192, 1024);
+          umma_f16(tmem_O + b * D, ad, bd, idesc_pv, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&o_full[b]);
+        umma_commit(&kv_empty[i % STAGES]);
+        return true;
+      };
+      for (int j = 0; j < nk && ok; ++j) {
+        const int stage = j % STAGES, b = j & 1;
+        if (!mbar_wait(&kv_full[stage], (j / STAGES) & 1) ||
+            !mbar_wait(&s_empty[b], ((j >> 1) & 1) ^ 1)) {
+          atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sKV + stage * Cfg::KV_STAGE);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t ad = make_smem_desc(q_addr + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
+          const uint64_t bd =
+              LITERAL ? make_smem_desc(k_addr + (k / 4) * (2 * 8192) + (k % 4) * 2048, 8192, 1024)
+                      : make_smem_desc(k_addr + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
+          umma_f16(tmem_S + b * BKV, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[b]);
+        if (j > 0 && !issue_pv(j - 1)) {
+          atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+          ok = false;
+        }
+      }
+      if (ok && nk > 0 && !issue_pv(nk - 1))
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+    }
+    __syncwarp();
+  } else {
+    // ------------------- softmax / correction / output (warps 2..5) -----------
+    const int q = warp & 3;
+    const int row = q * 32 + lane;       // row inside the query tile = TMEM lane
+    const int qrow = q0 + row;           // position in the sequence
+    const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+    const float scale_b = bf16_round(prm.scale);
+    constexpr float L2E = 1.4426950408889634f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_pending = 1.f;
+    float o_acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i)
+      o_acc[i] = 0.f;
+    bool ok = true;
+
+    auto consume_o = [&](int i, float a) -> bool {
+      const int b = i & 1;
+      if (!mbar_wait(&o_full[b], static_cast<uint32_t>(i >> 1) & 1))
+        return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_O + lane_sel + b * D + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+          o_acc[c * 32 + k] = fmaf(o_acc[c * 32 + k], a, __uint_as_float(r[k]));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&o_empty[b]);
+      return true;
+    };
+
+    for (int j = 0; j < nk && ok; ++j) {
+      const int b = j & 1;
+      if (!mbar_wait(&s_full[b], static_cast<uint32_t>(j >> 1) & 1)) {
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int k0 = j * BKV;
+      // keys this row may see inside the tile: [0, lim)
+      int lim = prm.T - k0;
+      if (prm.causal)
+        lim = min(lim, qrow - k0 + 1);
+      const bool need_mask = (k0 + BKV > prm.T) || (prm.causal && k0 + BKV > q0); // warp-uniform
+      const uint32_t s_addr = tmem_S + lane_sel + b * BKV;
+      // pass 1: row maximum of the rounded, scaled scores
+      float mx = m_run;
+#pragma unroll
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          float x = bf16_round(bf16_round(__uint_as_float(r[k])) * scale_b);
+          if (need_mask && c * 32 + k >= lim)
+            x = -INFINITY;
+          mx = fmaxf(mx, x);
+        }
+      }
+      // rows past the end of the sequence see no key at all: keep them finite
+      const float m_use = (mx == -INFINITY) ? 0.f : mx;
+      const float mL = m_use * L2E;
+      // pass 2: probabilities → bf16 → swizzled smem (K-major A operand of P·V)
+      uint8_t *prow = sP + b * Cfg::P_BYTES + row * 128;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int k = 0; k < 32; k += 2) {
+          float x0 = bf16_round(bf16_round(__uint_as_float(r[k])) * scale_b);
+          float x1 = bf16_round(bf16_round(__uint_as_float(r[k + 1])) * scale_b);
+          float p0 = exp2f(fmaf(x0, L2E, -mL));
+          float p1 = exp2f(fmaf(x1, L2E, -mL));
+          if (need_mask) {
+            if (c * 32 + k >= lim)
+              p0 = 0.f;
+            if (c * 32 + k + 1 >= lim)
+              p1 = 0.f;
+          }
+          sum += p0 + p1;
+          pk[k / 2] = pack_bf16x2(p0, p1);
+        }
+        // 32 columns = four 16-byte chunks; chunk index inside the 64-column box
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int gc = c * 4 + ch;          // 16-byte chunk 0..15 of the 128-key row
+          const int box = gc >> 3, cc = gc & 7;
+          *reinterpret_cast<uint4 *>(prow + box * (BQ * 128) + ((cc ^ (lane & 7)) << 4)) =
+              make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[b]);
+        mbar_arrive(&p_full[b]);
+      }
+      const float alpha = exp2f((m_run - m_use) * L2E); // first tile: exp2(-inf) = 0
+      l_run = l_run * alpha + sum;
+      m_run = m_use;
+      if (j > 0) {
+        if (!consume_o(j - 1, alpha_pending)) {
+          atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+          ok = false;
+          break;
+        }
+      }
+      alpha_pending = alpha;
+    }
+    if (ok && nk > 0 && !consume_o(nk - 1, alpha_pending)) {
+      atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+      ok = false;
+    }
+    if (ok) {
+      // normalise, stage this warp's 32 rows in the (now idle) P buffer, TMA-store
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      uint8_t *orow = sP + row * 128;
+#pragma unroll
+      for (int gc = 0; gc < D / 8; ++gc) {
+        const int box = gc >> 3, cc = gc & 7;
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          w[k] = pack_bf16x2(o_acc[gc * 8 + 2 * k] * inv, o_acc[gc * 8 + 2 * k + 1] * inv);
+        *reinterpret_cast<uint4 *>(orow + box * (BQ * 128) + ((cc ^ (lane & 7)) << 4)) =
+            make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0 && q0 + q * 32 < prm.T) {
+        const int bb = bh / prm.H, hh = bh % prm.H;
+#pragma unroll
+        for (int db = 0; db < DB; ++db)
+          tma_store_5d(&tmO, sP + db * (BQ * 128) + q * 32 * 128, db * 64, hh, q0 + q * 32, bb, 0);
+        bulk_commit();
+        bulk_wait<0>();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1)
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn att_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault,
+                                         &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+static bool att_map(CUtensorMap *map, const void *base, int rank, const unsigned long long *d,
+                    const unsigned long long *st, const unsigned *bx) {
+  EncodeTiledFn fn = att_encode_fn();
+  if (!fn)
+    return false;
+  cuuint64_t dims[5], strides[4];
+  cuuint32_t box[5], estr[5] = {1, 1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i)
+    dims[i] = d[i], box[i] = bx[i];
+  for (int i = 0; i + 1 < rank; ++i)
+    strides[i] = st[i] * 2ull;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void *>(base), dims, strides,
+            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Returns 0 ok, 1 shape/alignment outside this kernel's envelope, 2 launch failure.
+int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *out, int B, int H,
+                             int T, int D, int causal, int literal, int *status,
+                             cudaStream_t stream) {
+  auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if ((D != 64 && D != 128) || T <= 0 || B <= 0 || H <= 0)
+    return 1;
+  if (!al(q) || !al(k) || !al(v) || !al(out))
+    return 1;
+  if (literal && (T % 8))
+    return 1; // column offset bh*T must stay 16-byte aligned
+  const unsigned long long BH = 1ull * B * H, uT = T, uD = D, Ntot = BH * uT, E = 1ull * H * D;
+  if (BH > 65535 || Ntot > 0x7fffffffull)
+    return 1;
+  CUtensorMap tmQ, tmK, tmV, tmO;
+  {
+    const unsigned long long d[3] = {uD, uT, BH}, st[2] = {uD, uT * uD};
+    const unsigned bq[3] = {64, BQ, 1}, bv[3] = {64, 64, 1};
+    if (!att_map(&tmQ, q, 3, d, st, bq) || !att_map(&tmV, v, 3, d, st, bv))
+      return 2;
+    if (!literal) {
+      const unsigned bk[3] = {64, BKV, 1};
+      if (!att_map(&tmK, k, 3, d, st, bk))
+        return 2;
+    }
+  }
+  if (literal) {
+    const unsigned long long d[3] = {Ntot, uD, 1}, st[2] = {Ntot, Ntot * uD};
+    const unsigned bk[3] = {64, 64, 1};
+    if (!att_map(&tmK, k, 3, d, st, bk))
+      return 2;
+  }
+  {
+    // out[b][t][h][d], dimensions by ascending stride: d, h, t, b
+    const unsigned long long d[5] = {uD, static_cast<unsigned long long>(H), uT,
+                                     static_cast<unsigned long long>(B), 1};
+    const unsigned long long st[4] = {uD, E, uT * E, uT * E * B};
+    const unsigned bx[5] = {64, 1, 32, 1, 1};
+    if (!att_map(&tmO, out, 5, d, st, bx))
+      return 2;
+  }
+  AttParams prm;
+  prm.T = T, prm.H = H, prm.BH = static_cast<int>(BH), prm.causal = causal;
+  prm.scale = 1.0f / sqrtf(static_cast<float>(D));
+  prm.n_qtiles = (T + BQ - 1) / BQ;
+  dim3 grid(prm.n_qtiles, static_cast<unsigned>(BH));
+
+#define MU_ATT_LAUNCH(D_, L_)                                                                    \
+  do {                                                                                           \
+    auto kern = attention_tcgen05_kernel<D_, L_>;                                                \
+    static bool attr_set = false;                                                                \
+    if (!attr_set) {                                                                             \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
+                               AttCfg<D_>::SMEM_BYTES) != cudaSuccess)                           \
+        return 2;                                                                                \
+      attr_set = true;                                                                           \
+    }                                                                                            \
+    kern<<<grid, ATT_THREADS, AttCfg<D_>::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, prm, status); \
+  } while (0)
+
+  if (D == 128) {
+    if (literal)
+      MU_ATT_LAUNCH(128, true);
+    else
+      MU_ATT_LAUNCH(128, false);
+  } else {
+    if (literal)
+      MU_ATT_LAUNCH(64, true);
+    else
+      MU_ATT_LAUNCH(64, false);
+  }
+#undef MU_ATT_LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+} // namespace mu
