@@ -108,6 +108,28 @@ int mu_attention(mu_ctx *ctx, const void *q, const void *k, const void *v, void 
                  int T, int D, int causal, int kmode, int dtype, void *workspace,
                  size_t workspace_bytes, void *stream);
 
+/* ---- attention core without any allocation ---------------------------------
+ * No counterpart in the reference. For callers that may not allocate device
+ * memory at all (a latency-critical loop that must stay off the allocator's
+ * lock, a process with a memory budget fixed up front, a host that owns every
+ * byte and only lends pointers): the same computation as mu_attention's composed
+ * path, with the [B*H,T,T] score matrix kept in an array that is part of the
+ * library image (MU_ATTENTION_STATIC_SCRATCH_BYTES on every device that loads the
+ * library, until process exit). It takes no context and calls no cudaMalloc,
+ * cudaFree or allocating library routine.
+ *  - B*H*T*T*sizeof(dtype) beyond the array is rejected with MU_ERR_SIZE.
+ *  - The first call on a device looks the array up (cudaGetSymbolAddress with
+ *    that device current); make that first call before any stream capture.
+ *  - All calls share the array: two calls whose kernels overlap on the GPU
+ *    (different streams, or concurrent host threads) race. Serialise them.
+ *  - sync_and_check != 0 synchronises `stream` and reports a latched device fault;
+ *    with 0 the call is asynchronous and such a fault goes unreported.
+ *  - err/err_len: optional buffer that receives the failure text. */
+#define MU_ATTENTION_STATIC_SCRATCH_BYTES 67108864u
+int mu_attention_static_scratch(int device, const void *q, const void *k, const void *v, void *out,
+                                int B, int H, int T, int D, int causal, int kmode, int dtype,
+                                void *stream, int sync_and_check, char *err, size_t err_len);
+
 /* ---- normalisation / softmax ----------------------------------------------
  * ops::layer_norm (src/core/ops/normalization.cpp:125-224; host-only in the
  * reference) and Backend::softmax over the last dim (src/core/backend.hpp:243). */

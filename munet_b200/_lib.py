@@ -52,6 +52,8 @@ SIGNATURES = {
     "mu_linear_qkv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "mu_attention_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "mu_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "mu_attention_static_scratch": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i,
+                                         C.c_char_p, _sz]),
     "mu_layer_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _i, _f, _i, _vp]),
     "mu_softmax": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
     "mu_embedding": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
