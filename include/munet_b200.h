@@ -200,6 +200,12 @@ int mu_engine_run(mu_engine *engine, const void *input, int input_on_host, void 
 int mu_engine_profile(mu_engine *engine, int reps, int capacity, int *n_ops, int *kinds, float *ms,
                       double *flops, double *bytes, void *stream);
 void *mu_engine_output_ptr(const mu_engine *engine);
+/* Host-only: parse + validate a deploy artifact exactly as mu_engine_load does
+ * (parse_and_validate_artifact, src/inference_serialization.cpp:919-1033) and
+ * write a JSON summary {"config": <module tree>, "tensors": {name: {dtype, shape}}}.
+ * Needs no device. Returns MU_OK, MU_ERR_INVALID (text in err) or MU_ERR_SIZE. */
+int mu_artifact_inspect(const char *path, char *json_out, size_t json_cap, char *err,
+                        size_t err_len);
 void *mu_engine_argmax_ptr(const mu_engine *engine);
 
 #ifdef __cplusplus

@@ -73,6 +73,7 @@ SIGNATURES = {
     "mu_engine_profile": (_i, [_vp, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_f),
                                C.POINTER(C.c_double), C.POINTER(C.c_double), _vp]),
     "mu_engine_output_ptr": (_vp, [_vp]),
+    "mu_artifact_inspect": (_i, [C.c_char_p, C.c_char_p, _sz, C.c_char_p, _sz]),
     "mu_engine_argmax_ptr": (_vp, [_vp]),
 }
 

@@ -261,8 +261,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         lim = min(lim, qrow - k0 + 1);
       const bool need_mask = (k0 + BKV > prm.T) || (prm.causal && k0 + BKV > q0); // warp-uniform
       const uint32_t s_addr = tmem_S + lane_sel + b * BKV;
-      // pass 1: row maximum of the rounded, scaled scores
-      float mx = m_run;
+      // pass 1: row maximum. Rounding and the (positive) scale are monotone, so the
+      // maximum of the transformed scores is the transform of the raw maximum.
+      float raw_mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < BKV / 32; ++c) {
         uint32_t r[32];
@@ -270,12 +271,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          float x = bf16_round(bf16_round(__uint_as_float(r[k])) * scale_b);
+          float x = __uint_as_float(r[k]);
           if (need_mask && c * 32 + k >= lim)
             x = -INFINITY;
-          mx = fmaxf(mx, x);
+          raw_mx = fmaxf(raw_mx, x);
         }
       }
+      const float mx = fmaxf(m_run, bf16_round(bf16_round(raw_mx) * scale_b));
       // rows past the end of the sequence see no key at all: keep them finite
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
       const float mL = m_use * L2E;
@@ -290,8 +292,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         uint32_t pk[16];
 #pragma unroll
         for (int k = 0; k < 32; k += 2) {
-          float x0 = bf16_round(bf16_round(__uint_as_float(r[k])) * scale_b);
-          float x1 = bf16_round(bf16_round(__uint_as_float(r[k + 1])) * scale_b);
+          // s = bf16(bf16(acc) * bf16(scale)): packed converts, two columns at a time
+          uint32_t u = pack_bf16x2(__uint_as_float(r[k]), __uint_as_float(r[k + 1]));
+          u = pack_bf16x2(bf16_lo(u) * scale_b, bf16_hi(u) * scale_b);
+          const float x0 = bf16_lo(u), x1 = bf16_hi(u);
           float p0 = exp2f(fmaf(x0, L2E, -mL));
           float p1 = exp2f(fmaf(x1, L2E, -mL));
           if (need_mask) {

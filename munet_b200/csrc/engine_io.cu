@@ -423,3 +423,80 @@ bool load_artifact(const std::string &path, Json *config,
 }
 
 } // namespace mu
+
+// ---------------------------------------------------------------------------
+// Host-only inspection of a deploy artifact (no device needed): validates it
+// exactly like mu_engine_load and returns a JSON summary
+//   {"config": <module tree>, "tensors": {"name": {"dtype": d, "shape": [...]}, ...}}
+// ---------------------------------------------------------------------------
+namespace {
+void json_escape(const std::string &in, std::string *out) {
+  for (char c : in) {
+    if (c == '"' || c == '\\') { out->push_back('\\'); out->push_back(c); }
+    else if (c == '\n') *out += "\\n";
+    else if (c == '\t') *out += "\\t";
+    else if (static_cast<unsigned char>(c) < 0x20) { char b[8]; snprintf(b, sizeof(b), "\\u%04x", c); *out += b; }
+    else out->push_back(c);
+  }
+}
+void json_dump(const mu::Json &j, std::string *out) {
+  using mu::Json;
+  switch (j.kind) {
+  case Json::NUL: *out += "null"; break;
+  case Json::BOOL: *out += j.b ? "true" : "false"; break;
+  case Json::NUM: {
+    char b[64];
+    if (j.num == static_cast<long long>(j.num)) snprintf(b, sizeof(b), "%lld", static_cast<long long>(j.num));
+    else snprintf(b, sizeof(b), "%.17g", j.num);
+    *out += b;
+    break;
+  }
+  case Json::STR: out->push_back('"'); json_escape(j.str, out); out->push_back('"'); break;
+  case Json::ARR:
+    out->push_back('[');
+    for (size_t i = 0; i < j.arr.size(); ++i) { if (i) out->push_back(','); json_dump(j.arr[i], out); }
+    out->push_back(']');
+    break;
+  case Json::OBJ:
+    out->push_back('{');
+    for (size_t i = 0; i < j.obj.size(); ++i) {
+      if (i) out->push_back(',');
+      out->push_back('"'); json_escape(j.obj[i].first, out); *out += "\":";
+      json_dump(j.obj[i].second, out);
+    }
+    out->push_back('}');
+    break;
+  }
+}
+} // namespace
+
+extern "C" int mu_artifact_inspect(const char *path, char *json_out, size_t json_cap, char *err,
+                                   size_t err_len) {
+  if (err && err_len) err[0] = 0;
+  if (!path || !json_out || json_cap == 0) return 1;
+  mu::Json config;
+  std::map<std::string, mu::NamedTensor> tensors;
+  std::string why;
+  if (!mu::load_artifact(path, &config, &tensors, &why)) {
+    if (err && err_len) snprintf(err, err_len, "%s", why.c_str());
+    return 1;
+  }
+  std::string out = "{\"config\":";
+  json_dump(config, &out);
+  out += ",\"tensors\":{";
+  bool first = true;
+  for (auto &kv : tensors) {
+    if (!first) out.push_back(',');
+    first = false;
+    out.push_back('"'); json_escape(kv.first, &out); out += "\":{\"dtype\":" + std::to_string(kv.second.dtype) + ",\"shape\":[";
+    for (size_t i = 0; i < kv.second.shape.size(); ++i) { if (i) out.push_back(','); out += std::to_string(kv.second.shape[i]); }
+    out += "]}";
+  }
+  out += "}}";
+  if (out.size() + 1 > json_cap) {
+    if (err && err_len) snprintf(err, err_len, "summary needs %zu bytes", out.size() + 1);
+    return 7;
+  }
+  memcpy(json_out, out.c_str(), out.size() + 1);
+  return 0;
+}

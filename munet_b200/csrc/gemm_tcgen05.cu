@@ -91,45 +91,73 @@ __device__ __forceinline__ float epi_math(float x, float bias, float res, bool h
   return x;
 }
 
-// Same chain with the activation fixed at compile time (hot path).
+// The same chain on a PAIR of adjacent columns with the activation fixed at compile
+// time (hot path). Rounding two values costs one packed convert plus two bit ops,
+// which halves the load on the conversion (XU) pipe.
+__device__ __forceinline__ void round2(float &a, float &b) {
+  const uint32_t u = pack_bf16x2(a, b);
+  a = bf16_lo(u);
+  b = bf16_hi(u);
+}
+__device__ __forceinline__ float fast_sigmoid(float t) {
+  return __fdividef(1.0f, 1.0f + __expf(-t));
+}
+
 template <int ACT>
-__device__ __forceinline__ float epi_math_t(float x, float bias, float res, float alpha,
-                                            bool has_alpha, bool rnd) {
+__device__ __forceinline__ uint32_t epi_pair(float x0, float x1, float b0, float b1, float r0,
+                                             float r1, float alpha, bool has_alpha, bool has_bias,
+                                             bool has_res, bool rnd) {
   if (rnd) {
-    x = bf16_round(x);
-    if (has_alpha)
-      x = bf16_round(x * alpha);
-    x = bf16_round(x + bias); // bias == 0 when absent: value-preserving
-    if (ACT == ACT_RELU) {
-      x = fmaxf(x, 0.0f);
-    } else if (ACT == ACT_GELU) {
-      const float t = bf16_round(x * 1.703125f); // bf16(1.702)
-      const float s = bf16_round(__fdividef(1.0f, 1.0f + __expf(-t)));
-      x = bf16_round(x * s);
-    } else if (ACT == ACT_SIGMOID) {
-      x = bf16_round(__fdividef(1.0f, 1.0f + __expf(-x)));
-    } else if (ACT == ACT_TANH) {
-      const float t = bf16_round(x * 2.0f);
-      const float s = bf16_round(__fdividef(1.0f, 1.0f + __expf(-t)));
-      x = bf16_round(s * 2.0f - 1.0f);
+    round2(x0, x1);
+    if (has_alpha) {
+      x0 *= alpha, x1 *= alpha;
+      round2(x0, x1);
     }
-    x = bf16_round(x + res);
+    if (has_bias) {
+      x0 += b0, x1 += b1;
+      round2(x0, x1);
+    }
+    if (ACT == ACT_RELU) {
+      x0 = fmaxf(x0, 0.0f), x1 = fmaxf(x1, 0.0f);
+    } else if (ACT == ACT_GELU) {
+      float t0 = x0 * 1.703125f, t1 = x1 * 1.703125f; // bf16(1.702)
+      round2(t0, t1);
+      float s0 = fast_sigmoid(t0), s1 = fast_sigmoid(t1);
+      round2(s0, s1);
+      x0 *= s0, x1 *= s1;
+      if (has_res)
+        round2(x0, x1);
+    } else if (ACT == ACT_SIGMOID) {
+      x0 = fast_sigmoid(x0), x1 = fast_sigmoid(x1);
+      if (has_res)
+        round2(x0, x1);
+    } else if (ACT == ACT_TANH) {
+      float t0 = x0 * 2.0f, t1 = x1 * 2.0f;
+      round2(t0, t1);
+      float s0 = fast_sigmoid(t0), s1 = fast_sigmoid(t1);
+      round2(s0, s1);
+      x0 = s0 * 2.0f - 1.0f, x1 = s1 * 2.0f - 1.0f;
+      if (has_res)
+        round2(x0, x1);
+    }
+    if (has_res)
+      x0 += r0, x1 += r1;
   } else {
     if (has_alpha)
-      x = x * alpha;
-    x = x + bias;
+      x0 *= alpha, x1 *= alpha;
+    x0 += b0, x1 += b1;
     if (ACT == ACT_RELU) {
-      x = fmaxf(x, 0.0f);
+      x0 = fmaxf(x0, 0.0f), x1 = fmaxf(x1, 0.0f);
     } else if (ACT == ACT_GELU) {
-      x = x * __fdividef(1.0f, 1.0f + __expf(-1.702f * x));
+      x0 *= fast_sigmoid(1.702f * x0), x1 *= fast_sigmoid(1.702f * x1);
     } else if (ACT == ACT_SIGMOID) {
-      x = __fdividef(1.0f, 1.0f + __expf(-x));
+      x0 = fast_sigmoid(x0), x1 = fast_sigmoid(x1);
     } else if (ACT == ACT_TANH) {
-      x = 2.0f * __fdividef(1.0f, 1.0f + __expf(-2.0f * x)) - 1.0f;
+      x0 = 2.0f * fast_sigmoid(2.0f * x0) - 1.0f, x1 = 2.0f * fast_sigmoid(2.0f * x1) - 1.0f;
     }
-    x = x + res;
+    x0 += r0, x1 += r1;
   }
-  return x;
+  return pack_bf16x2(x0, x1); // the final rounding to the stored bf16
 }
 
 // One half (32 accumulator columns = four 16-byte chunks) of a staged 64-column
@@ -151,13 +179,10 @@ __device__ __forceinline__ void epi_half(const uint32_t (&r)[32], uint8_t *row, 
     const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w}, rw[4] = {rv.x, rv.y, rv.z, rv.w};
     uint32_t ow[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float v0 = epi_math_t<ACT>(__uint_as_float(r[c * 8 + 2 * j]), bf16_lo(bw[j]),
-                                       bf16_lo(rw[j]), alpha, has_alpha, rnd);
-      const float v1 = epi_math_t<ACT>(__uint_as_float(r[c * 8 + 2 * j + 1]), bf16_hi(bw[j]),
-                                       bf16_hi(rw[j]), alpha, has_alpha, rnd);
-      ow[j] = pack_bf16x2(v0, v1);
-    }
+    for (int j = 0; j < 4; ++j)
+      ow[j] = epi_pair<ACT>(__uint_as_float(r[c * 8 + 2 * j]), __uint_as_float(r[c * 8 + 2 * j + 1]),
+                            bf16_lo(bw[j]), bf16_hi(bw[j]), bf16_lo(rw[j]), bf16_hi(rw[j]), alpha,
+                            has_alpha, bias != nullptr, has_res, rnd);
     *slot = make_uint4(ow[0], ow[1], ow[2], ow[3]);
   }
 }

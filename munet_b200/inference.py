@@ -90,6 +90,17 @@ def save_deploy(path: str, config: dict, tensors: dict[str, np.ndarray], produce
         np.savez(f, **meta, **payload)
 
 
+def inspect_artifact(path: str) -> dict:
+    """Validate a deploy artifact on the host (no GPU) and return its module tree and
+    tensor table; raises MuNetError with the loader's message when it is rejected."""
+    cap = 1 << 22
+    out, err = C.create_string_buffer(cap), C.create_string_buffer(1024)
+    rc = lib().mu_artifact_inspect(path.encode(), out, cap, err, 1024)
+    if rc:
+        raise MuNetError(rc, err.value.decode())
+    return json.loads(out.value.decode())
+
+
 class Engine:
     """``load`` → ``compile`` → ``run``; one instance per device context."""
 
