@@ -138,6 +138,22 @@ int mu_layer_norm(mu_ctx *ctx, const void *x, const void *gamma, const void *bet
 int mu_softmax(mu_ctx *ctx, const void *x, void *y, long long rows, int cols, int dtype,
                void *stream);
 
+/* ---- spatial ops (float32, NCHW) -------------------------------------------
+ * BackendSpatialCapability::conv2d / max_pool2d (src/core/backend.hpp:294-300; CPU
+ * kernels src/backend/cpu_backend.hpp:768-796,833-855) and nn::GlobalAvgPool2d
+ * (src/nn/pooling.hpp:8-26). weight is [oC,iC,k,k]; stride/pad are square; bias may
+ * be NULL. mu_conv2d can fuse the ReLU module and a MaxPool2d(2,2,0) that follow it
+ * in a Sequential (relu != 0, pool == 2): y is then [B,oC,oH/2,oW/2].
+ * Every output is bit-identical to the reference CPU kernel (same summation order,
+ * no fused multiply-add). */
+int mu_conv2d(mu_ctx *ctx, const void *x, const void *w, const void *bias, void *y, int B, int iC,
+              int iH, int iW, int oC, int k, int stride, int pad, int relu, int pool, int dtype,
+              void *stream);
+int mu_max_pool2d(mu_ctx *ctx, const void *x, void *y, int B, int C, int H, int W, int k, int stride,
+                  int pad, int dtype, void *stream);
+int mu_global_avg_pool(mu_ctx *ctx, const void *x, void *y, int B, int C, int H, int W, int dtype,
+                       void *stream);
+
 /* ---- embedding -------------------------------------------------------------
  * nn::Embedding index path (src/nn/linear.hpp:92-131): out[b,t,:] = table[ids[b,t],:]
  * (+ pos[t,:] when pos != NULL — the token + position sum of the decoder).

@@ -54,6 +54,9 @@ SIGNATURES = {
     "mu_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "mu_attention_static_scratch": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i,
                                          C.c_char_p, _sz]),
+    "mu_conv2d": (_i, [_vp, _vp, _vp, _vp, _vp] + [_i] * 11 + [_vp]),
+    "mu_max_pool2d": (_i, [_vp, _vp, _vp] + [_i] * 8 + [_vp]),
+    "mu_global_avg_pool": (_i, [_vp, _vp, _vp] + [_i] * 5 + [_vp]),
     "mu_layer_norm": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _i, _f, _i, _vp]),
     "mu_softmax": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
     "mu_embedding": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
@@ -200,6 +203,20 @@ class Context:
     def eltwise(self, x, y, n, dtype, act="none", bias=None, cols=1, residual=None, stream=None):
         self._rc(self._lib.mu_eltwise(self._h, _ptr(x), _ptr(bias), _ptr(residual), _ptr(y), n, cols,
                                       ACT[act], dtype, _stream(stream)))
+
+    # -- spatial -----------------------------------------------------------------
+    def conv2d(self, x, w, bias, y, B, iC, iH, iW, oC, k, stride, pad, dtype, relu=False, pool=0,
+               stream=None):
+        self._rc(self._lib.mu_conv2d(self._h, _ptr(x), _ptr(w), _ptr(bias), _ptr(y), B, iC, iH, iW, oC,
+                                     k, stride, pad, int(relu), pool, dtype, _stream(stream)))
+
+    def max_pool2d(self, x, y, B, Cc, H, W, k, stride, pad, dtype, stream=None):
+        self._rc(self._lib.mu_max_pool2d(self._h, _ptr(x), _ptr(y), B, Cc, H, W, k, stride, pad, dtype,
+                                         _stream(stream)))
+
+    def global_avg_pool(self, x, y, B, Cc, H, W, dtype, stream=None):
+        self._rc(self._lib.mu_global_avg_pool(self._h, _ptr(x), _ptr(y), B, Cc, H, W, dtype,
+                                              _stream(stream)))
 
     def argmax(self, x, idx, rows, cols, dtype, stream=None):
         self._rc(self._lib.mu_argmax(self._h, _ptr(x), _ptr(idx), rows, cols, dtype, _stream(stream)))

@@ -156,6 +156,8 @@ void mu_ctx_destroy(mu_ctx *ctx) {
 }
 
 const char *mu_last_error(const mu_ctx *ctx) { return ctx ? ctx->err : "null context"; }
+// used by the entry points that live in other translation units
+int mu_set_error(mu_ctx *ctx, int code, const char *msg) { return fail(ctx, code, "%s", msg); }
 int mu_ctx_num_sms(const mu_ctx *ctx) { return ctx ? ctx->num_sms : 0; }
 int mu_ctx_force_simt(mu_ctx *ctx, int on) {
   if (!ctx)

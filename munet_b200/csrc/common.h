@@ -63,4 +63,12 @@ struct SimtArgs {
   Epilogue ep;
 };
 
+// float32 NCHW convolution, weight [oC,iC,k,k], square stride s / padding p.
+struct ConvArgs {
+  const float *x, *w, *bias;
+  float *y;
+  int B, iC, iH, iW, oC, oH, oW, k, s, p;
+  int relu, pool; // pool: 0 none, 2 = MaxPool2d(2,2,0) fused after the activation
+};
+
 } // namespace mu

@@ -34,7 +34,8 @@ using mu::NamedTensor;
 namespace {
 
 enum OpKind {
-  OP_EMBED, OP_LN, OP_LINEAR, OP_QKV, OP_ATTN, OP_ELTWISE, OP_ARGMAX, OP_ALLREDUCE
+  OP_EMBED, OP_LN, OP_LINEAR, OP_QKV, OP_ATTN, OP_ELTWISE, OP_ARGMAX, OP_CONV, OP_MAXPOOL, OP_GAP,
+  OP_ALLREDUCE
 };
 
 struct Tensor {
@@ -51,6 +52,7 @@ struct Op {
   int w = -1, b = -1, w2 = -1, b2 = -1;
   int M = 0, K = 0, N = 0, act = 0;
   int B = 0, T = 0, H = 0, D = 0, V = 0, causal = 0;
+  int iC = 0, iH = 0, iW = 0, oC = 0, ksz = 0, stride = 1, pad = 0, relu = 0, pool = 0; // spatial ops
   float eps = 1e-5f;
   long long n = 0;
   size_t ws_bytes = 0;
@@ -240,7 +242,10 @@ struct mu_engine {
     return id;
   }
 
-  int lower(const Json &node, const std::string &prefix, Val &v, const Json *next, bool *fused_next);
+  // next/next2: the following siblings inside a Sequential (fusion look-ahead);
+  // *fused_count = how many of them this node absorbed.
+  int lower(const Json &node, const std::string &prefix, Val &v, const Json *next, bool *fused_next,
+            const Json *next2 = nullptr, int *fused_count = nullptr);
   int lower_linear(const std::string &prefix, int K, int N, bool bias, int act, int res_tid, Val &v);
   int lower_mha(const std::string &prefix, int E, int H, bool causal, int res_tid, Val &v);
   int lower_block(const std::string &prefix, int d, int H, Val &v);
@@ -370,8 +375,9 @@ int mu_engine::lower_block(const std::string &prefix, int d, int H, Val &v) {
 }
 
 int mu_engine::lower(const Json &node, const std::string &prefix, Val &v, const Json *next,
-                     bool *fused_next) {
+                     bool *fused_next, const Json *next2, int *fused_count) {
   if (fused_next) *fused_next = false;
+  if (fused_count) *fused_count = 0;
   if (!node.is_object()) return fail(MU_ERR_INVALID, "Serialized module config root must be a JSON object");
   const Json *ty = node.get("type");
   if (!ty || !ty->is_string()) return fail(MU_ERR_INVALID, "module config is missing 'type'");
@@ -395,10 +401,13 @@ int mu_engine::lower(const Json &node, const std::string &prefix, Val &v, const 
     if (!layers || !layers->is_array()) return fail(MU_ERR_INVALID, "Sequential: missing 'layers'");
     for (size_t i = 0; i < layers->arr.size(); ++i) {
       const Json *nx = i + 1 < layers->arr.size() ? &layers->arr[i + 1] : nullptr;
+      const Json *nx2 = i + 2 < layers->arr.size() ? &layers->arr[i + 2] : nullptr;
       bool fused = false;
-      int rc = lower(layers->arr[i], prefix + std::to_string(i) + ".", v, nx, &fused);
+      int count = 0;
+      int rc = lower(layers->arr[i], prefix + std::to_string(i) + ".", v, nx, &fused, nx2, &count);
       if (rc) return rc;
-      if (fused) ++i;
+      if (count > 0) i += count;
+      else if (fused) ++i;
     }
     return MU_OK;
   }
@@ -420,6 +429,82 @@ int mu_engine::lower(const Json &node, const std::string &prefix, Val &v, const 
     op.in = v.tid, op.out = new_tensor(static_cast<size_t>(op.n) * esize(dtype));
     push(op);
     v.tid = op.out;
+    return MU_OK;
+  }
+  if (type == "Conv2d") { // src/nn/linear.hpp:39-64; ReLU and MaxPool2d(2,2,0) that follow are fused
+    int iC, oC, k, s, p;
+    if (!req_int("in_channels", &iC) || !req_int("out_channels", &oC) || !req_int("kernel_size", &k) ||
+        !req_int("stride", &s) || !req_int("padding", &p))
+      return fail(MU_ERR_INVALID, "Conv2d: missing in_channels/out_channels/kernel_size/stride/padding");
+    if (v.shape.size() != 4 || v.shape[1] != iC)
+      return fail(MU_ERR_INVALID, "Conv2d expects NCHW input with %d channels", iC);
+    if (dtype != MU_F32)
+      return fail(MU_ERR_UNSUPPORTED, "Conv2d: only float32 is implemented");
+    if (k <= 0 || s <= 0 || p < 0)
+      return fail(MU_ERR_INVALID, "Conv2d: bad kernel_size/stride/padding");
+    Op c;
+    c.kind = OP_CONV;
+    c.w = stage_weight({prefix + "weight"}, &why);
+    if (c.w >= 0) c.b = stage_weight({prefix + "bias"}, &why);
+    if (c.w < 0 || c.b < 0) return fail(MU_ERR_INVALID, "Conv2d '%s': %s", prefix.c_str(), why.c_str());
+    c.B = v.shape[0], c.iC = iC, c.iH = v.shape[2], c.iW = v.shape[3], c.oC = oC;
+    c.ksz = k, c.stride = s, c.pad = p;
+    int oH = (c.iH + 2 * p - k) / s + 1, oW = (c.iW + 2 * p - k) / s + 1;
+    if (oH <= 0 || oW <= 0) return fail(MU_ERR_INVALID, "Conv2d: kernel larger than the padded input");
+    // look ahead inside the enclosing Sequential: ReLU, then MaxPool2d(2,2,0)
+    int consumed = 0;
+    if (next && next->is_object() && next->get("type") && next->get("type")->is_string() &&
+        next->get("type")->str == "ReLU") {
+      c.relu = 1;
+      consumed = 1;
+      const Json *n2 = next2;
+      if (n2 && n2->is_object() && n2->get("type") && n2->get("type")->is_string() &&
+          n2->get("type")->str == "MaxPool2d") {
+        const Json *pk = n2->get("kernel_size"), *ps = n2->get("stride"), *pp = n2->get("padding");
+        if (pk && ps && pp && pk->is_number() && ps->is_number() && pp->is_number() &&
+            static_cast<int>(pk->num) == 2 && static_cast<int>(ps->num) == 2 &&
+            static_cast<int>(pp->num) == 0 && oH >= 2 && oW >= 2) {
+          c.pool = 2;
+          consumed = 2;
+          oH /= 2, oW /= 2;
+        }
+      }
+    }
+    c.in = v.tid;
+    c.out = new_tensor(static_cast<size_t>(c.B) * oC * oH * oW * 4);
+    push(c);
+    v.tid = c.out, v.shape = {c.B, oC, oH, oW};
+    if (fused_count) *fused_count = consumed;
+    if (fused_next) *fused_next = consumed > 0;
+    return MU_OK;
+  }
+  if (type == "MaxPool2d") { // src/nn/pooling.hpp:28-36
+    int k, s, p;
+    if (!req_int("kernel_size", &k) || !req_int("stride", &s) || !req_int("padding", &p))
+      return fail(MU_ERR_INVALID, "MaxPool2d: missing kernel_size/stride/padding");
+    if (v.shape.size() != 4) return fail(MU_ERR_INVALID, "MaxPool2d expects NCHW input");
+    if (dtype != MU_F32) return fail(MU_ERR_UNSUPPORTED, "MaxPool2d: only float32 is implemented");
+    if (k <= 0 || s <= 0 || p < 0) return fail(MU_ERR_INVALID, "MaxPool2d: bad kernel_size/stride/padding");
+    Op m;
+    m.kind = OP_MAXPOOL, m.B = v.shape[0], m.iC = v.shape[1], m.iH = v.shape[2], m.iW = v.shape[3];
+    m.ksz = k, m.stride = s, m.pad = p;
+    const int oH = (m.iH + 2 * p - k) / s + 1, oW = (m.iW + 2 * p - k) / s + 1;
+    if (oH <= 0 || oW <= 0) return fail(MU_ERR_INVALID, "MaxPool2d: window larger than the input");
+    m.in = v.tid;
+    m.out = new_tensor(static_cast<size_t>(m.B) * m.iC * oH * oW * 4);
+    push(m);
+    v.tid = m.out, v.shape = {m.B, m.iC, oH, oW};
+    return MU_OK;
+  }
+  if (type == "GlobalAvgPool2d") { // src/nn/pooling.hpp:8-26 → [B,C,1,1]
+    if (v.shape.size() != 4) return fail(MU_ERR_INVALID, "GlobalAvgPool2d expects NCHW input");
+    if (dtype != MU_F32) return fail(MU_ERR_UNSUPPORTED, "GlobalAvgPool2d: only float32 is implemented");
+    Op g;
+    g.kind = OP_GAP, g.B = v.shape[0], g.iC = v.shape[1], g.iH = v.shape[2], g.iW = v.shape[3];
+    g.in = v.tid;
+    g.out = new_tensor(static_cast<size_t>(g.B) * g.iC * 4);
+    push(g);
+    v.tid = g.out, v.shape = {g.B, g.iC, 1, 1};
     return MU_OK;
   }
   if (type == "Dropout") return MU_OK; // eval mode: identity (src/nn/activations.hpp:47-50)
@@ -623,6 +708,20 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       rc = mu_argmax(ctx, tptr(op.in), static_cast<int32_t *>(tptr(op.out)), op.M, op.N, dtype, st);
       n_launches += 1;
       break;
+    case OP_CONV:
+      rc = mu_conv2d(ctx, tptr(op.in), wptr(op.w), wptr(op.b), tptr(op.out), op.B, op.iC, op.iH, op.iW,
+                     op.oC, op.ksz, op.stride, op.pad, op.relu, op.pool, dtype, st);
+      n_launches += 1;
+      break;
+    case OP_MAXPOOL:
+      rc = mu_max_pool2d(ctx, tptr(op.in), tptr(op.out), op.B, op.iC, op.iH, op.iW, op.ksz, op.stride,
+                         op.pad, dtype, st);
+      n_launches += 1;
+      break;
+    case OP_GAP:
+      rc = mu_global_avg_pool(ctx, tptr(op.in), tptr(op.out), op.B, op.iC, op.iH, op.iW, dtype, st);
+      n_launches += 1;
+      break;
     default:
       rc = MU_ERR_UNSUPPORTED;
     }
@@ -664,6 +763,17 @@ void mu_engine::op_work(const Op &op, double *flops, double *bytes) const {
   case OP_ARGMAX:
     *bytes = es * op.M * op.N + 4.0 * op.M;
     break;
+  case OP_CONV: {
+    const double oH = (op.iH + 2 * op.pad - op.ksz) / op.stride + 1, oW = (op.iW + 2 * op.pad - op.ksz) / op.stride + 1;
+    *flops = 2.0 * op.B * op.oC * oH * oW * op.iC * op.ksz * op.ksz;
+    *bytes = 4.0 * (1.0 * op.B * op.iC * op.iH * op.iW + 1.0 * op.oC * op.iC * op.ksz * op.ksz +
+                    1.0 * op.B * op.oC * oH * oW / (op.pool == 2 ? 4 : 1));
+    break;
+  }
+  case OP_MAXPOOL:
+  case OP_GAP:
+    *bytes = 4.0 * op.B * op.iC * op.iH * op.iW;
+    break;
   default:
     break;
   }
@@ -673,7 +783,8 @@ extern "C" {
 
 // Eager (graph-free) forward with a CUDA-event pair around every op, `reps`
 // times; reports per-op mean milliseconds, kind and algorithmic work.
-// kinds: 0 embed, 1 layer_norm, 2 linear, 3 qkv linear, 4 attention, 5 eltwise, 6 argmax.
+// kinds: 0 embed, 1 layer_norm, 2 linear, 3 qkv linear, 4 attention, 5 eltwise, 6 argmax,
+// 7 conv2d, 8 max_pool2d, 9 global_avg_pool.
 int mu_engine_profile(mu_engine *e, int reps, int capacity, int *n_ops, int *kinds, float *ms,
                       double *flops, double *bytes, void *stream) {
   if (!e || !e->compiled || reps <= 0) return MU_ERR_INVALID;

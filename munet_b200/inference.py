@@ -224,7 +224,8 @@ class Engine:
                                          _stream(stream)))
         return out
 
-    OP_KINDS = ["embed", "layer_norm", "linear", "qkv_linear", "attention", "eltwise", "argmax"]
+    OP_KINDS = ["embed", "layer_norm", "linear", "qkv_linear", "attention", "eltwise", "argmax",
+                "conv2d", "max_pool2d", "global_avg_pool", "all_reduce"]
 
     def profile(self, reps: int = 1, stream=None) -> list[dict]:
         """Eager forward with CUDA events around every op: per-op ms + algorithmic work."""
