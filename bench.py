@@ -214,9 +214,13 @@ def run_ours(args, cfg):
     torch.cuda.empty_cache()
     stats = eng.stats()
 
+    # one seeded global batch of B*world sequences; every rank owns a contiguous shard of it
+    from munet_b200.sharding import max_over_ranks, shard_bounds
     ids_gen = torch.Generator(device="cpu")
-    ids_gen.manual_seed(2005 + rank)  # each rank owns its shard of the global batch
-    ids_host = torch.randint(0, V, (B, T), generator=ids_gen, dtype=torch.int32).pin_memory()
+    ids_gen.manual_seed(2005)
+    lo, hi = shard_bounds(B * world, rank, world)
+    ids_host = torch.randint(0, V, (B * world, T), generator=ids_gen, dtype=torch.int32)[lo:hi]
+    ids_host = ids_host.contiguous().pin_memory()
     ids_dev = ids_host.to(dev)
     am_host = torch.empty((B, T), dtype=torch.int32).pin_memory()
     stream = torch.cuda.current_stream()
@@ -247,10 +251,7 @@ def run_ours(args, cfg):
             fn()
         e1.record(stream)
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        return max_over_ranks(e0.elapsed_time(e1), device=dev)
 
     for _ in range(max(args.warmup, 3)):
         step_device()

@@ -1,0 +1,184 @@
+// B200Backend — a MuNet `Backend` (src/core/backend.hpp:347-759) whose capabilities
+// forward to the C ABI of libmunet_b200.so. This header is compiled against the
+// MuNet headers (include path = its `src/`); it contains no kernels.
+//
+// Advertised (query_support): Matmul, UnaryActivation (relu, sigmoid), Softmax for
+// float32 and bfloat16; Convolution and Pooling for float32. Binary elementwise ops,
+// reductions, concat, batch-norm and random fill are not advertised, so MuNet's
+// dispatcher routes them to its CPU fallback exactly as it does for any partial
+// backend (src/core/op_dispatch.cpp:670-718). Backward/optimizer entry points are
+// training-only and throw.
+//
+// Errors follow the reference convention: std::runtime_error with the C ABI's
+// message (src/backend/cuda_backend.cu:15-31). copy() is complete on return
+// because callers read host memory right after it (src/tensor.cpp:342-351).
+#pragma once
+
+#include "core/backend.hpp"
+#include "munet_b200.h"
+#include "storage.hpp"
+
+#include <stdexcept>
+#include <string>
+
+namespace munet {
+
+class B200Backend : public Backend,
+                    public BackendAllocationTransferCapability,
+                    public BackendElementwiseCapability,
+                    public BackendBlasCapability,
+                    public BackendSpatialCapability {
+public:
+  explicit B200Backend(int index) {
+    const int rc = mu_ctx_create(index, &ctx_);
+    if (rc != MU_OK)
+      throw std::runtime_error("B200Backend: cannot create a context on device " +
+                               std::to_string(index) + " (status " + std::to_string(rc) + ")");
+  }
+  ~B200Backend() override { mu_ctx_destroy(ctx_); }
+  const char *name() const override { return "b200"; }
+
+  BackendAllocationTransferCapability *allocation_transfer_capability() override { return this; }
+  const BackendAllocationTransferCapability *allocation_transfer_capability() const override { return this; }
+  BackendElementwiseCapability *elementwise_capability() override { return this; }
+  const BackendElementwiseCapability *elementwise_capability() const override { return this; }
+  BackendBlasCapability *blas_capability() override { return this; }
+  const BackendBlasCapability *blas_capability() const override { return this; }
+  BackendSpatialCapability *spatial_capability() override { return this; }
+  const BackendSpatialCapability *spatial_capability() const override { return this; }
+
+  BackendSupport query_support(BackendFeature feature, DataType dtype,
+                               const Shape *shape) const override {
+    BackendSupport s = Backend::query_support(feature, dtype, shape);
+    const bool f32 = dtype == DataType::Float32, bf16 = dtype == DataType::BFloat16;
+    switch (feature) {
+    case BackendFeature::Matmul:
+    case BackendFeature::UnaryActivation:
+    case BackendFeature::Softmax:
+      s.available = f32 || bf16;
+      break;
+    case BackendFeature::Convolution:
+    case BackendFeature::Pooling:
+      s.available = f32;
+      break;
+    default:
+      s.available = false; // CPU fallback decided by MuNet's dispatcher
+    }
+    return s;
+  }
+
+  // ---- allocation / transfer ------------------------------------------------
+  void *allocate(size_t bytes) override {
+    void *p = nullptr;
+    check(mu_alloc(ctx_, bytes, &p));
+    return p;
+  }
+  void deallocate(void *ptr) override { check(mu_free(ctx_, ptr)); }
+  void memset(void *ptr, int value, size_t bytes) override {
+    if (bytes == 0) return;
+    // no memset in the C ABI: stage a host buffer (rare, start-up only)
+    std::string host(bytes, static_cast<char>(value));
+    check(mu_copy(ctx_, ptr, host.data(), bytes, MU_COPY_H2D, nullptr));
+    check(mu_check(ctx_, nullptr));
+  }
+  void copy(const void *src, void *dst, size_t bytes, Device src_dev, Device dst_dev) override {
+    const bool s_host = src_dev.type == DeviceType::CPU, d_host = dst_dev.type == DeviceType::CPU;
+    if (s_host && d_host) { std::memcpy(dst, src, bytes); return; }
+    const int kind = s_host ? MU_COPY_H2D : (d_host ? MU_COPY_D2H : MU_COPY_D2D);
+    check(mu_copy(ctx_, dst, src, bytes, kind, nullptr));
+    check(mu_check(ctx_, nullptr));
+  }
+  void synchronize() override { check(mu_synchronize(ctx_)); check(mu_check(ctx_, nullptr)); }
+  void all_reduce(Storage &, size_t) override { training_only("all_reduce"); }
+  double get_last_kernel_time_us() override { return 0.0; }
+  void to_contiguous(const Storage &src, Storage &dst, const Shape &shape, const Strides &strides,
+                     size_t offset) override {
+    // strided gather on the host side of the boundary (head split/merge permutes);
+    // the executor never needs it because its GEMM epilogues write the final layout
+    const size_t es = dtype_size(src.dtype());
+    std::string in(src.size_bytes(), 0), out(numel(shape) * es, 0);
+    check(mu_copy(ctx_, in.data(), src.data(), in.size(), MU_COPY_D2H, nullptr));
+    check(mu_check(ctx_, nullptr));
+    const size_t total = numel(shape);
+    for (size_t linear = 0; linear < total; ++linear) {
+      size_t rem = linear, off = offset;
+      for (int d = static_cast<int>(shape.size()) - 1; d >= 0; --d) {
+        off += (rem % shape[d]) * strides[d];
+        rem /= shape[d];
+      }
+      std::memcpy(&out[linear * es], &in[off * es], es);
+    }
+    check(mu_copy(ctx_, dst.data(), out.data(), out.size(), MU_COPY_H2D, nullptr));
+    check(mu_check(ctx_, nullptr));
+  }
+
+  // ---- BLAS --------------------------------------------------------------------
+  void matmul(const Storage &a, const Storage &b, Storage &out, int M, int K, int N, bool transA,
+              bool transB) override {
+    check(mu_matmul(ctx_, a.data(), b.data(), out.data(), M, K, N, transA, transB, code(a), nullptr));
+  }
+  void batched_matmul(const Storage &a, const Storage &b, Storage &out, int batch, int M, int K,
+                      int N, bool transA, bool transB, int64_t sa, int64_t sb, int64_t so) override {
+    check(mu_batched_matmul(ctx_, a.data(), b.data(), out.data(), batch, M, K, N, transA, transB, sa,
+                            sb, so, code(a), nullptr));
+  }
+
+  // ---- elementwise ---------------------------------------------------------------
+  void relu(const Storage &in, Storage &out, size_t n) override { unary(in, out, n, MU_ACT_RELU); }
+  void sigmoid(const Storage &in, Storage &out, size_t n) override { unary(in, out, n, MU_ACT_SIGMOID); }
+  void softmax(const Storage &in, Storage &out, int rows, int cols) override {
+    check(mu_softmax(ctx_, in.data(), out.data(), rows, cols, code(in), nullptr));
+  }
+  void add(const Storage &, const Storage &, Storage &, const BroadcastInfo &) override { not_advertised("add"); }
+  void sub(const Storage &, const Storage &, Storage &, const BroadcastInfo &) override { not_advertised("sub"); }
+  void mul(const Storage &, const Storage &, Storage &, const BroadcastInfo &) override { not_advertised("mul"); }
+  void div(const Storage &, const Storage &, Storage &, const BroadcastInfo &) override { not_advertised("div"); }
+  void broadcast_row(const Storage &, Storage &, int, int) override { not_advertised("broadcast_row"); }
+  void exp(const Storage &, Storage &, size_t) override { not_advertised("exp"); }
+  void log(const Storage &, Storage &, size_t) override { not_advertised("log"); }
+  void sqrt(const Storage &, Storage &, size_t) override { not_advertised("sqrt"); }
+  void rsqrt(const Storage &, Storage &, size_t) override { not_advertised("rsqrt"); }
+  void sin(const Storage &, Storage &, size_t) override { not_advertised("sin"); }
+  void cos(const Storage &, Storage &, size_t) override { not_advertised("cos"); }
+  void relu_backward(const Storage &, const Storage &, Storage &, size_t) override { training_only("relu_backward"); }
+  void sigmoid_backward(const Storage &, const Storage &, Storage &, size_t) override { training_only("sigmoid_backward"); }
+  void softmax_backward(const Storage &, const Storage &, Storage &, int, int) override { training_only("softmax_backward"); }
+
+  // ---- spatial ---------------------------------------------------------------------
+  void conv2d(const Storage &in, const Storage &weight, const Storage *bias, Storage &out, int B,
+              int iC, int iH, int iW, int oC, int kH, int kW, int s, int p) override {
+    if (kH != kW) throw std::runtime_error("B200Backend: conv2d needs a square kernel");
+    check(mu_conv2d(ctx_, in.data(), weight.data(), bias ? bias->data() : nullptr, out.data(), B, iC,
+                    iH, iW, oC, kH, s, p, 0, 0, code(in), nullptr));
+  }
+  void max_pool2d(const Storage &in, Storage &out, int B, int C, int iH, int iW, int k, int s,
+                  int p) override {
+    check(mu_max_pool2d(ctx_, in.data(), out.data(), B, C, iH, iW, k, s, p, code(in), nullptr));
+  }
+  void upsample2d(const Storage &, Storage &, int, int, int, int, int) override { not_advertised("upsample2d"); }
+  void conv2d_backward(const Storage &, const Storage &, const Storage &, Storage &, Storage &,
+                       Storage *, int, int, int, int, int, int, int, int, int) override { training_only("conv2d_backward"); }
+  void max_pool2d_backward(const Storage &, const Storage &, Storage &, int, int, int, int, int, int,
+                           int) override { training_only("max_pool2d_backward"); }
+  void upsample2d_backward(const Storage &, Storage &, int, int, int, int, int) override { training_only("upsample2d_backward"); }
+
+private:
+  mu_ctx *ctx_ = nullptr;
+  static int code(const Storage &s) { return static_cast<int>(s.dtype()); } // same enum order
+  void check(int rc) const {
+    if (rc != MU_OK) throw std::runtime_error(std::string("B200Backend: ") + mu_last_error(ctx_));
+  }
+  void unary(const Storage &in, Storage &out, size_t n, int act) {
+    check(mu_eltwise(ctx_, in.data(), nullptr, nullptr, out.data(), static_cast<long long>(n), 1, act,
+                     code(in), nullptr));
+  }
+  [[noreturn]] static void not_advertised(const char *op) {
+    throw std::runtime_error(std::string("B200Backend: '") + op +
+                             "' is not advertised by query_support and must not be dispatched here");
+  }
+  [[noreturn]] static void training_only(const char *op) {
+    throw std::runtime_error(std::string("B200Backend: '") + op + "' is a training-only entry point");
+  }
+};
+
+} // namespace munet

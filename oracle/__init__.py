@@ -35,6 +35,10 @@ def build(ref: bool = True) -> None:
     if ref and os.path.isdir(os.environ.get("MUNET_REF", "/root/reference")):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "-j8",
                                "REF=" + os.environ.get("MUNET_REF", "/root/reference")])
+        lib_dir = os.path.join(_HERE, "..", "munet_b200", "lib", "libmunet_b200.so")
+        if os.path.exists(lib_dir):  # drop-in proof: reference core + our Backend adapter
+            subprocess.check_call(["make", "-s", "-C", _HERE, "refb200", "-j8",
+                                   "REF=" + os.environ.get("MUNET_REF", "/root/reference")])
 
 
 def to_bf16(a) -> np.ndarray:
@@ -263,3 +267,40 @@ def ref() -> Ref:
 
 def have_ref() -> bool:
     return os.path.exists(REF_PATH)
+
+
+REF_B200_PATH = os.path.join(_HERE, "_ref", "libmunet_ref_b200.so")
+
+
+def have_ref_b200() -> bool:
+    return os.path.exists(REF_B200_PATH)
+
+
+class RefB200:
+    """The unmodified reference core with munet_b200's Backend adapter registered as its
+    CUDA backend (oracle/ref_b200_driver.cpp): MuNet's own Engine drives the B200 kernels."""
+
+    def __init__(self):
+        self.lib = C.CDLL(REF_B200_PATH)
+        self.lib.refb200_last_error.restype = C.c_char_p
+
+    def register(self):
+        if self.lib.refb200_register() != 0:
+            raise RuntimeError(self.lib.refb200_last_error().decode())
+
+    def plugin_status(self):
+        buf = C.create_string_buffer(4096)
+        active = self.lib.refb200_plugin_status(buf, 4096)
+        return bool(active), buf.value.decode()
+
+    def engine_run_npz(self, path, x, dtype=F32, device_index=0, out_capacity=1 << 22):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        shape = (C.c_int * x.ndim)(*x.shape)
+        out = np.empty(out_capacity, np.float32)
+        oshape, ond = (C.c_int * 8)(), C.c_int(0)
+        rc = self.lib.refb200_engine_run_npz(path.encode(), device_index, dtype, _p(x), shape, x.ndim,
+                                             _p(out), C.c_long(out_capacity), oshape, C.byref(ond))
+        if rc != 0:
+            raise RuntimeError(self.lib.refb200_last_error().decode())
+        shp = tuple(oshape[i] for i in range(ond.value))
+        return out[: int(np.prod(shp))].reshape(shp).copy()
