@@ -168,6 +168,15 @@ int mu_embedding(mu_ctx *ctx, const int32_t *ids, const void *table, const void 
 int mu_eltwise(mu_ctx *ctx, const void *x, const void *bias, const void *residual, void *y,
                long long n, int cols, int act, int dtype, void *stream);
 
+/* Broadcasting binary ops: BackendElementwiseCapability::add / sub / mul / div with a
+ * BroadcastInfo (src/core/backend.hpp:214-221, src/types.hpp:420-425): up to 6 output
+ * dims, per-dimension element strides of each operand (0 = broadcast along that dim).
+ * float32 results are bit-identical to the reference CPU kernels. */
+enum mu_binary_op { MU_OP_ADD = 0, MU_OP_SUB = 1, MU_OP_MUL = 2, MU_OP_DIV = 3 };
+int mu_binary_broadcast(mu_ctx *ctx, int op, const void *a, const void *b, void *out, int ndim,
+                        const int *out_shape, const long long *strides_a,
+                        const long long *strides_b, int dtype, void *stream);
+
 /* ---- argmax ---------------------------------------------------------------
  * The reference has no argmax op; its demos take np.argmax of the logits
  * (demos/transformers/decoder_block_demo.py:112). First maximum wins. */

@@ -62,6 +62,8 @@ SIGNATURES = {
     "mu_embedding": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "mu_eltwise": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp]),
     "mu_argmax": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
+    "mu_binary_broadcast": (_i, [_vp, _i, _vp, _vp, _vp, _i, C.POINTER(_i), C.POINTER(_ll),
+                                 C.POINTER(_ll), _i, _vp]),
     "mu_engine_create": (_i, [_vp, C.POINTER(_vp)]),
     "mu_engine_destroy": (None, [_vp]),
     "mu_engine_last_error": (C.c_char_p, [_vp]),
@@ -217,6 +219,15 @@ class Context:
     def global_avg_pool(self, x, y, B, Cc, H, W, dtype, stream=None):
         self._rc(self._lib.mu_global_avg_pool(self._h, _ptr(x), _ptr(y), B, Cc, H, W, dtype,
                                               _stream(stream)))
+
+    def binary(self, op, a, b, out, out_shape, strides_a, strides_b, dtype, stream=None):
+        """op in add/sub/mul/div; strides in elements, 0 = broadcast along that dim."""
+        n = len(out_shape)
+        code = {"add": 0, "sub": 1, "mul": 2, "div": 3}[op]
+        self._rc(self._lib.mu_binary_broadcast(
+            self._h, code, _ptr(a), _ptr(b), _ptr(out), n, (C.c_int * max(n, 1))(*out_shape),
+            (C.c_longlong * max(n, 1))(*strides_a), (C.c_longlong * max(n, 1))(*strides_b), dtype,
+            _stream(stream)))
 
     def argmax(self, x, idx, rows, cols, dtype, stream=None):
         self._rc(self._lib.mu_argmax(self._h, _ptr(x), _ptr(idx), rows, cols, dtype, _stream(stream)))

@@ -2,9 +2,9 @@
 // forward to the C ABI of libmunet_b200.so. This header is compiled against the
 // MuNet headers (include path = its `src/`); it contains no kernels.
 //
-// Advertised (query_support): Matmul, UnaryActivation (relu, sigmoid), Softmax for
-// float32 and bfloat16; Convolution and Pooling for float32. Binary elementwise ops,
-// reductions, concat, batch-norm and random fill are not advertised, so MuNet's
+// Advertised (query_support): Matmul, ElementwiseBinary (add/sub/mul/div with
+// broadcasting), UnaryActivation (relu, sigmoid), Softmax for float32 and bfloat16;
+// Convolution and Pooling for float32. Row broadcast, reductions, concat, batch-norm and random fill are not advertised, so MuNet's
 // dispatcher routes them to its CPU fallback exactly as it does for any partial
 // backend (src/core/op_dispatch.cpp:670-718). Backward/optimizer entry points are
 // training-only and throw.
@@ -55,6 +55,7 @@ public:
     case BackendFeature::Matmul:
     case BackendFeature::UnaryActivation:
     case BackendFeature::Softmax:
+    case BackendFeature::ElementwiseBinary:
       s.available = f32 || bf16;
       break;
     case BackendFeature::Convolution:
@@ -129,10 +130,10 @@ public:
   void softmax(const Storage &in, Storage &out, int rows, int cols) override {
     check(mu_softmax(ctx_, in.data(), out.data(), rows, cols, code(in), nullptr));
   }
-  void add(const Storage &, const Storage &, Storage &, const BroadcastInfo &) override { not_advertised("add"); }
-  void sub(const Storage &, const Storage &, Storage &, const BroadcastInfo &) override { not_advertised("sub"); }
-  void mul(const Storage &, const Storage &, Storage &, const BroadcastInfo &) override { not_advertised("mul"); }
-  void div(const Storage &, const Storage &, Storage &, const BroadcastInfo &) override { not_advertised("div"); }
+  void add(const Storage &a, const Storage &b, Storage &o, const BroadcastInfo &i) override { binary(MU_OP_ADD, a, b, o, i); }
+  void sub(const Storage &a, const Storage &b, Storage &o, const BroadcastInfo &i) override { binary(MU_OP_SUB, a, b, o, i); }
+  void mul(const Storage &a, const Storage &b, Storage &o, const BroadcastInfo &i) override { binary(MU_OP_MUL, a, b, o, i); }
+  void div(const Storage &a, const Storage &b, Storage &o, const BroadcastInfo &i) override { binary(MU_OP_DIV, a, b, o, i); }
   void broadcast_row(const Storage &, Storage &, int, int) override { not_advertised("broadcast_row"); }
   void exp(const Storage &, Storage &, size_t) override { not_advertised("exp"); }
   void log(const Storage &, Storage &, size_t) override { not_advertised("log"); }
@@ -171,6 +172,19 @@ private:
   void unary(const Storage &in, Storage &out, size_t n, int act) {
     check(mu_eltwise(ctx_, in.data(), nullptr, nullptr, out.data(), static_cast<long long>(n), 1, act,
                      code(in), nullptr));
+  }
+  void binary(int op, const Storage &a, const Storage &b, Storage &out, const BroadcastInfo &info) {
+    const int nd = static_cast<int>(info.out_shape.size());
+    if (nd > 6) throw std::runtime_error("B200Backend: broadcasting supports at most 6 dimensions");
+    int shape[6];
+    long long sa[6], sb[6];
+    for (int d = 0; d < nd; ++d) {
+      shape[d] = info.out_shape[d];
+      sa[d] = info.strides_a[d];
+      sb[d] = info.strides_b[d];
+    }
+    check(mu_binary_broadcast(ctx_, op, a.data(), b.data(), out.data(), nd, shape, sa, sb, code(a),
+                              nullptr));
   }
   [[noreturn]] static void not_advertised(const char *op) {
     throw std::runtime_error(std::string("B200Backend: '") + op +
