@@ -98,6 +98,12 @@ int mu_linear(mu_ctx *ctx, const void *x, const void *w, const void *bias, const
 int mu_linear_qkv(mu_ctx *ctx, const void *x, const void *w_qkv, const void *bias_qkv, void *q,
                   void *k, void *v, int B, int T, int E, int H, int dtype, void *stream);
 
+/* Same with the input width separate from the produced heads: w is [K_in, 3*H*D]. Used
+ * for a tensor-parallel shard that computes H = num_heads / tp_size of the heads. */
+int mu_linear_qkv_heads(mu_ctx *ctx, const void *x, const void *w_qkv, const void *bias_qkv, void *q,
+                        void *k, void *v, int B, int T, int K_in, int H, int D, int dtype,
+                        void *stream);
+
 /* ---- attention core --------------------------------------------------------
  * The scale / mask / softmax / P·V part of MultiHeadAttention::forward_impl
  * (src/nn/attention.hpp:64-99) on head-major q,k,v [B*H*T, D]; `out` is the merged
@@ -183,6 +189,24 @@ int mu_binary_broadcast(mu_ctx *ctx, int op, const void *a, const void *b, void 
 int mu_argmax(mu_ctx *ctx, const void *x, int32_t *idx, long long rows, int cols, int dtype,
               void *stream);
 
+/* ---- all-reduce ------------------------------------------------------------
+ * Backend::all_reduce (src/core/backend.hpp:199,473-477): elementwise SUM over the
+ * participants (src/core/all_reduce_runtime.hpp:85-133). The reference stages every
+ * buffer through host memory inside one process; here each process owns one GPU and the
+ * sum runs in NCCL over NVLink. The 128-byte id from mu_comm_unique_id (rank 0) is
+ * handed to the other ranks by the host (e.g. torch.distributed broadcast). A NULL comm
+ * or a world of 1 makes mu_all_reduce_sum a no-op. mu_comm_check is a non-blocking host
+ * check for a failed peer. */
+typedef struct mu_comm mu_comm;
+int mu_comm_unique_id(void *out, size_t capacity);
+int mu_comm_create(mu_ctx *ctx, const void *unique_id, int rank, int world, mu_comm **out);
+void mu_comm_destroy(mu_comm *comm);
+int mu_comm_rank(const mu_comm *comm);
+int mu_comm_world(const mu_comm *comm);
+int mu_all_reduce_sum(mu_ctx *ctx, mu_comm *comm, void *buffer, long long n, int dtype,
+                      void *stream);
+int mu_comm_check(mu_ctx *ctx, mu_comm *comm);
+
 /* ---- compiled inference executor -------------------------------------------
  * Stands in for munet::inference::Engine (src/inference.hpp:292-801) and
  * load_serialized (src/inference_serialization.cpp:1086-1089).
@@ -212,6 +236,11 @@ int mu_engine_load_memory(mu_engine *engine, const char *config_json, int n_tens
                           const char *const *names, const void *const *data, const int *dtypes,
                           const int *ndims, const long long *shapes, int on_device,
                           int compute_dtype);
+/* Tensor parallelism (no counterpart in the reference, which has none): options "tp_size" and
+ * "tp_rank" plus a communicator of that size shard every decoder block Megatron-style —
+ * q/k/v and fc1 by output columns (heads), out_proj and fc2 by input rows with an all-reduce
+ * of the partial sums, the LM head by vocabulary columns (output = this rank's slab). */
+int mu_engine_set_comm(mu_engine *engine, mu_comm *comm);
 int mu_engine_compile(mu_engine *engine, const int *input_shape, int ndim, int input_dtype);
 int mu_engine_output_shape(const mu_engine *engine, int *shape, int *ndim, int *dtype);
 int mu_engine_stats(const mu_engine *engine, long long *arena_bytes, long long *weight_bytes,

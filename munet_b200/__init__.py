@@ -7,8 +7,8 @@ never falls back to another implementation: if the native library is missing,
 loading fails with an error that says how to build it.
 """
 from ._lib import (  # noqa: F401
-    ACT, BF16, F32, I32, K_LITERAL, K_MATH, Context, MuNetError, lib, lib_path,
+    ACT, BF16, F32, I32, K_LITERAL, K_MATH, Comm, Context, MuNetError, lib, lib_path,
 )
 
-__all__ = ["ACT", "BF16", "F32", "I32", "K_LITERAL", "K_MATH", "Context", "MuNetError", "lib",
+__all__ = ["ACT", "BF16", "F32", "I32", "K_LITERAL", "K_MATH", "Comm", "Context", "MuNetError", "lib",
            "lib_path"]

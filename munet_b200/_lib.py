@@ -50,6 +50,7 @@ SIGNATURES = {
     "mu_batched_matmul": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _i, _vp]),
     "mu_linear": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "mu_linear_qkv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "mu_linear_qkv_heads": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "mu_attention_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "mu_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "mu_attention_static_scratch": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i,
@@ -64,6 +65,13 @@ SIGNATURES = {
     "mu_argmax": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
     "mu_binary_broadcast": (_i, [_vp, _i, _vp, _vp, _vp, _i, C.POINTER(_i), C.POINTER(_ll),
                                  C.POINTER(_ll), _i, _vp]),
+    "mu_comm_unique_id": (_i, [_vp, _sz]),
+    "mu_comm_create": (_i, [_vp, _vp, _i, _i, C.POINTER(_vp)]),
+    "mu_comm_destroy": (None, [_vp]),
+    "mu_comm_rank": (_i, [_vp]),
+    "mu_comm_world": (_i, [_vp]),
+    "mu_all_reduce_sum": (_i, [_vp, _vp, _vp, _ll, _i, _vp]),
+    "mu_comm_check": (_i, [_vp, _vp]),
     "mu_engine_create": (_i, [_vp, C.POINTER(_vp)]),
     "mu_engine_destroy": (None, [_vp]),
     "mu_engine_last_error": (C.c_char_p, [_vp]),
@@ -71,6 +79,7 @@ SIGNATURES = {
     "mu_engine_load": (_i, [_vp, C.c_char_p, _i]),
     "mu_engine_load_memory": (_i, [_vp, C.c_char_p, _i, C.POINTER(C.c_char_p), C.POINTER(_vp),
                                    C.POINTER(_i), C.POINTER(_i), C.POINTER(_ll), _i, _i]),
+    "mu_engine_set_comm": (_i, [_vp, _vp]),
     "mu_engine_compile": (_i, [_vp, C.POINTER(_i), _i, _i]),
     "mu_engine_output_shape": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "mu_engine_stats": (_i, [_vp] + [C.POINTER(_ll)] * 5),
@@ -231,3 +240,51 @@ class Context:
 
     def argmax(self, x, idx, rows, cols, dtype, stream=None):
         self._rc(self._lib.mu_argmax(self._h, _ptr(x), _ptr(idx), rows, cols, dtype, _stream(stream)))
+
+    def all_reduce_sum(self, comm, buf, n, dtype, stream=None):
+        self._rc(self._lib.mu_all_reduce_sum(self._h, comm._h if comm else None, _ptr(buf), n, dtype,
+                                             _stream(stream)))
+
+
+class Comm:
+    """One NCCL communicator (one process per GPU). ``unique_id`` is the 128-byte id made by
+    ``Comm.new_unique_id()`` on one rank and handed to the others by the host."""
+
+    def __init__(self, ctx: "Context", unique_id: bytes, rank: int, world: int):
+        self._lib = lib()
+        self.ctx = ctx
+        h = _vp()
+        buf = C.create_string_buffer(bytes(unique_id), 128)
+        rc = self._lib.mu_comm_create(ctx._h, buf, rank, world, C.byref(h))
+        if rc != 0:
+            raise MuNetError(rc, self._lib.mu_last_error(ctx._h).decode())
+        self._h = h
+        self.rank, self.world = rank, world
+
+    @staticmethod
+    def new_unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        rc = lib().mu_comm_unique_id(buf, 128)
+        if rc != 0:
+            raise MuNetError(rc, "mu_comm_unique_id failed (is libnccl.so.2 loadable?)")
+        return buf.raw
+
+    @classmethod
+    def from_torch_distributed(cls, ctx: "Context"):
+        """Build the communicator over the default torch.distributed group (id exchanged there)."""
+        import torch
+        import torch.distributed as dist
+        rank, world = dist.get_rank(), dist.get_world_size()
+        ids = [cls.new_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        return cls(ctx, ids[0], rank, world)
+
+    def check(self):
+        rc = self._lib.mu_comm_check(self.ctx._h, self._h)
+        if rc != 0:
+            raise MuNetError(rc, self._lib.mu_last_error(self.ctx._h).decode())
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.mu_comm_destroy(self._h)
+            self._h = None

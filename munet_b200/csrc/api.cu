@@ -308,26 +308,31 @@ int mu_linear(mu_ctx *ctx, const void *x, const void *w, const void *bias, const
   return run_gemm(ctx, op, sh, ep, dtype, static_cast<cudaStream_t>(stream), "linear");
 }
 
-int mu_linear_qkv(mu_ctx *ctx, const void *x, const void *w_qkv, const void *bias_qkv, void *q,
-                  void *k, void *v, int B, int T, int E, int H, int dtype, void *stream) {
+// x[B*T, K_in] · w[K_in, 3*H*D] (+ bias[3*H*D]) written head-major: q, k, v each [B*H*T, D].
+// H is the number of heads this call produces (all of them, or one rank's share under
+// tensor parallelism), so the output width H*D may differ from K_in.
+int mu_linear_qkv_heads(mu_ctx *ctx, const void *x, const void *w_qkv, const void *bias_qkv, void *q,
+                        void *k, void *v, int B, int T, int K_in, int H, int D, int dtype,
+                        void *stream) {
   if (!ctx)
     return MU_ERR_INVALID;
-  MU_REQUIRE(B >= 0 && T >= 0 && E > 0 && H > 0 && E % H == 0, "linear_qkv: bad dimensions");
+  MU_REQUIRE(B >= 0 && T >= 0 && K_in > 0 && H > 0 && D > 0, "linear_qkv: bad dimensions");
   if (B == 0 || T == 0)
     return MU_OK;
   MU_REQUIRE(x && w_qkv && q && k && v, "linear_qkv: null pointer");
+  const int E = H * D; // output width of each of q, k, v
   const long long per = 1ll * B * T * E;
   const size_t es = esize(dtype);
   // q, k, v are addressed from q with one stride; they may be separate buffers
   const long long dk = (static_cast<const char *>(k) - static_cast<const char *>(q));
   const long long dv = (static_cast<const char *>(v) - static_cast<const char *>(q));
   mu::GemmOperands op;
-  op.a = x, op.lda = E, op.b = w_qkv, op.ldb = 3ll * E;
+  op.a = x, op.lda = K_in, op.b = w_qkv, op.ldb = 3ll * E;
   mu::Epilogue ep;
   ep.bias = bias_qkv, ep.round_each = 1;
-  ep.split_T = T, ep.split_H = H, ep.split_D = E / H;
+  ep.split_T = T, ep.split_H = H, ep.split_D = D;
   if (dk == static_cast<long long>(per * es) && dv == 2 * dk) {
-    mu::GemmShape sh{B * T, 3 * E, E, 1};
+    mu::GemmShape sh{B * T, 3 * E, K_in, 1};
     ep.c = q, ep.split_which_stride = per;
     return run_gemm(ctx, op, sh, ep, dtype, static_cast<cudaStream_t>(stream), "linear_qkv");
   }
@@ -340,12 +345,20 @@ int mu_linear_qkv(mu_ctx *ctx, const void *x, const void *w_qkv, const void *bia
     epi.c = outs[i];
     epi.bias = bias_qkv ? static_cast<const char *>(bias_qkv) + 1ll * i * E * es : nullptr;
     epi.split_which_stride = 0;
-    mu::GemmShape sh{B * T, E, E, 1};
+    mu::GemmShape sh{B * T, E, K_in, 1};
     int rc = run_gemm(ctx, opi, sh, epi, dtype, static_cast<cudaStream_t>(stream), "linear_qkv");
     if (rc)
       return rc;
   }
   return MU_OK;
+}
+
+int mu_linear_qkv(mu_ctx *ctx, const void *x, const void *w_qkv, const void *bias_qkv, void *q,
+                  void *k, void *v, int B, int T, int E, int H, int dtype, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(E > 0 && H > 0 && E % H == 0, "linear_qkv: bad dimensions");
+  return mu_linear_qkv_heads(ctx, x, w_qkv, bias_qkv, q, k, v, B, T, E, H, E / H, dtype, stream);
 }
 
 size_t mu_attention_workspace_bytes(int B, int H, int T, int D, int dtype) {

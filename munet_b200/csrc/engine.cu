@@ -74,6 +74,10 @@ struct Val {
   }
 };
 
+// Rows [r0,r1) x columns [c0,c1) of a parameter viewed as [prod(leading dims), last dim]
+// (negative = whole extent): the tensor-parallel shard of a weight or bias.
+struct Slice { long long r0 = -1, r1 = -1, c0 = -1, c1 = -1; };
+
 size_t esize(int dt) { return (dt == MU_F32 || dt == MU_I32) ? 4 : 2; }
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -92,6 +96,10 @@ struct mu_engine {
   int kmode = MU_K_LITERAL;
   int use_graph = 1;
   int want_argmax = 0;
+  // Megatron-style tensor parallelism over `comm` (decoder blocks only): this rank computes
+  // heads / MLP columns [tp_rank/tp_size) and all-reduces the row-parallel partial sums.
+  int tp_rank = 0, tp_size = 1;
+  mu_comm *comm = nullptr;
   Json config;
   std::map<std::string, NamedTensor> params;
   bool loaded = false, compiled = false;
@@ -101,7 +109,7 @@ struct mu_engine {
   std::vector<Weight> weights;
   std::map<std::string, int> weight_ids;
   std::vector<uint8_t> weight_stage; // host staging of converted weights
-  struct DevCopy { size_t dst, dst_pitch; const void *src; size_t width, rows; };
+  struct DevCopy { size_t dst, dst_pitch; const void *src; size_t src_pitch, width, rows; };
   std::vector<DevCopy> dev_copies;   // weights whose source already lives on the device
   std::vector<bool> dev_weight;      // per weight: filled by device copies
   void *weight_slab = nullptr;
@@ -169,14 +177,19 @@ struct mu_engine {
   }
 
   // Stage a parameter (converted to the compute dtype) into the weight slab.
-  // `parts` are concatenated along the last axis (fused q/k/v weights).
-  int stage_weight(const std::vector<std::string> &parts, std::string *why) {
+  // `parts` are concatenated along the last axis (fused q/k/v weights); `sl` selects the
+  // same sub-block of every part.
+  int stage_weight(const std::vector<std::string> &parts, std::string *why, Slice sl = Slice()) {
     std::string key;
     for (auto &p : parts) key += p + "|";
+    key += std::to_string(sl.r0) + "," + std::to_string(sl.r1) + "," + std::to_string(sl.c0) + "," +
+           std::to_string(sl.c1);
     auto it = weight_ids.find(key);
     if (it != weight_ids.end()) return it->second;
-    std::vector<const NamedTensor *> ts;
+    struct Part { const NamedTensor *t; long long R, C, r0, r1, c0, c1; };
+    std::vector<Part> ps;
     long long rows = -1, cols_total = 0;
+    bool any_dev = false;
     for (auto &p : parts) {
       const NamedTensor *t = find_param(p);
       if (!t) { *why = "missing tensor '" + p + "'"; return -1; }
@@ -185,52 +198,58 @@ struct mu_engine {
                ", expected float32 or the compute dtype";
         return -1;
       }
-      long long r = 1;
-      for (size_t i = 0; i + 1 < t->shape.size(); ++i) r *= t->shape[i];
-      long long c = t->shape.empty() ? 1 : t->shape.back();
-      if (parts.size() == 1) { r = 1; c = t->numel(); }
-      if (rows >= 0 && r != rows) { *why = "concat shape mismatch at '" + p + "'"; return -1; }
-      rows = r;
-      cols_total += c;
-      ts.push_back(t);
+      Part q;
+      q.t = t;
+      q.C = t->shape.empty() ? 1 : t->shape.back();
+      q.R = q.C > 0 ? t->numel() / q.C : 0;
+      q.r0 = sl.r0 < 0 ? 0 : sl.r0, q.r1 = sl.r1 < 0 ? q.R : sl.r1;
+      q.c0 = sl.c0 < 0 ? 0 : sl.c0, q.c1 = sl.c1 < 0 ? q.C : sl.c1;
+      if (q.r0 > q.r1 || q.r1 > q.R || q.c0 > q.c1 || q.c1 > q.C) {
+        *why = "slice out of range for '" + p + "'";
+        return -1;
+      }
+      if (rows >= 0 && q.r1 - q.r0 != rows) { *why = "concat shape mismatch at '" + p + "'"; return -1; }
+      rows = q.r1 - q.r0;
+      cols_total += q.c1 - q.c0;
+      any_dev = any_dev || t->on_device;
+      ps.push_back(q);
     }
     const size_t es = esize(dtype);
     Weight w;
     w.bytes = static_cast<size_t>(rows) * cols_total * es;
     w.offset = align_up(weight_bytes, 256);
     weight_bytes = w.offset + w.bytes;
-    bool any_dev = false;
-    for (auto *t : ts) any_dev = any_dev || t->on_device;
+    long long col0 = 0;
     if (any_dev) {
       // device-resident sources: strided device-to-device copies into the slab
-      long long col0 = 0;
-      for (auto *t : ts) {
-        if (!t->on_device || t->dtype != dtype) {
+      for (auto &q : ps) {
+        if (!q.t->on_device || q.t->dtype != dtype) {
           *why = "device-resident tensors must all be on the device and already have the compute dtype";
           return -1;
         }
-        const long long c = parts.size() == 1 ? t->numel() : t->shape.back();
+        const char *src = static_cast<const char *>(q.t->data) + (q.r0 * q.C + q.c0) * es;
         dev_copies.push_back({w.offset + static_cast<size_t>(col0) * es,
-                              static_cast<size_t>(cols_total) * es, t->data,
-                              static_cast<size_t>(c) * es, static_cast<size_t>(rows)});
-        col0 += c;
+                              static_cast<size_t>(cols_total) * es, src,
+                              static_cast<size_t>(q.C) * es,
+                              static_cast<size_t>(q.c1 - q.c0) * es, static_cast<size_t>(rows)});
+        col0 += q.c1 - q.c0;
       }
       dev_weight.push_back(true);
     } else {
       dev_weight.push_back(false);
       if (weight_stage.size() < weight_bytes) weight_stage.resize(weight_bytes);
       uint8_t *dst = weight_stage.data() + w.offset;
-      long long col0 = 0;
-      for (auto *t : ts) {
-        const long long c = parts.size() == 1 ? t->numel() : t->shape.back();
+      for (auto &q : ps) {
+        const long long c = q.c1 - q.c0;
         for (long long r = 0; r < rows; ++r) {
           uint8_t *d = dst + (static_cast<size_t>(r) * cols_total + col0) * es;
-          if (t->dtype == dtype) {
-            memcpy(d, static_cast<const uint8_t *>(t->data) + static_cast<size_t>(r) * c * es, c * es);
+          const long long src_index = (q.r0 + r) * q.C + q.c0;
+          if (q.t->dtype == dtype) {
+            memcpy(d, static_cast<const uint8_t *>(q.t->data) + static_cast<size_t>(src_index) * es, c * es);
           } else { // float32 → bfloat16, Tensor::to(DataType) semantics (src/tensor.cpp:249-284)
-            const float *s = static_cast<const float *>(t->data) + r * c;
+            const float *src = static_cast<const float *>(q.t->data) + src_index;
             uint16_t *o = reinterpret_cast<uint16_t *>(d);
-            for (long long i = 0; i < c; ++i) o[i] = f2bf(s[i]);
+            for (long long i = 0; i < c; ++i) o[i] = f2bf(src[i]);
           }
         }
         col0 += c;
@@ -246,8 +265,12 @@ struct mu_engine {
   // *fused_count = how many of them this node absorbed.
   int lower(const Json &node, const std::string &prefix, Val &v, const Json *next, bool *fused_next,
             const Json *next2 = nullptr, int *fused_count = nullptr);
-  int lower_linear(const std::string &prefix, int K, int N, bool bias, int act, int res_tid, Val &v);
-  int lower_mha(const std::string &prefix, int E, int H, bool causal, int res_tid, Val &v);
+  // par: 0 replicated, 1 column-parallel (this rank's slice of the outputs), 2 row-parallel
+  // (this rank's slice of the inputs; partial sums are all-reduced, then bias/residual)
+  int lower_linear(const std::string &prefix, int K, int N, bool bias, int act, int res_tid, Val &v,
+                   int par = 0);
+  int lower_mha(const std::string &prefix, int E, int H, bool causal, int res_tid, Val &v,
+                bool shard = false);
   int lower_block(const std::string &prefix, int d, int H, Val &v);
   int plan_and_allocate();
   int launch_all(cudaStream_t st);
@@ -278,37 +301,71 @@ int act_code(const std::string &type) {
 // nn::Linear (src/nn/linear.hpp:9-37): weight [in,out], optional bias [out];
 // the following activation module and a residual add ride in the GEMM epilogue.
 int mu_engine::lower_linear(const std::string &prefix, int K, int N, bool bias, int act,
-                            int res_tid, Val &v) {
-  if (v.shape.empty() || v.shape.back() != K)
+                            int res_tid, Val &v, int par) {
+  if (tp_size <= 1) par = 0;
+  if (par && (N % tp_size || K % tp_size))
+    return fail(MU_ERR_INVALID, "Linear '%s': %dx%d does not divide over %d tensor-parallel ranks",
+                prefix.c_str(), K, N, tp_size);
+  const int Kl = par == 2 ? K / tp_size : K, Nl = par == 1 ? N / tp_size : N;
+  if (v.shape.empty() || v.shape.back() != Kl)
     return fail(MU_ERR_INVALID, "Linear '%s': input last dim %d != in_features %d", prefix.c_str(),
-                v.shape.empty() ? -1 : v.shape.back(), K);
+                v.shape.empty() ? -1 : v.shape.back(), Kl);
   std::string why;
+  Slice wsl, bsl;
+  if (par == 1) wsl.c0 = bsl.c0 = 1ll * tp_rank * Nl, wsl.c1 = bsl.c1 = 1ll * (tp_rank + 1) * Nl;
+  if (par == 2) wsl.r0 = 1ll * tp_rank * Kl, wsl.r1 = 1ll * (tp_rank + 1) * Kl;
   Op op;
   op.kind = OP_LINEAR;
-  op.w = stage_weight({prefix + "weight"}, &why);
+  op.w = stage_weight({prefix + "weight"}, &why, wsl);
   if (op.w < 0) return fail(MU_ERR_INVALID, "Linear '%s': %s", prefix.c_str(), why.c_str());
+  int bias_id = -1;
   if (bias) {
-    op.b = stage_weight({prefix + "bias"}, &why);
-    if (op.b < 0) return fail(MU_ERR_INVALID, "Linear '%s': %s", prefix.c_str(), why.c_str());
+    bias_id = stage_weight({prefix + "bias"}, &why, bsl);
+    if (bias_id < 0) return fail(MU_ERR_INVALID, "Linear '%s': %s", prefix.c_str(), why.c_str());
   }
-  op.M = static_cast<int>(v.numel() / K), op.K = K, op.N = N, op.act = act;
-  op.in = v.tid, op.res = res_tid;
+  op.M = static_cast<int>(v.numel() / Kl), op.K = Kl, op.N = Nl, op.act = act;
+  op.in = v.tid;
+  if (par == 2) {
+    // partial = x_local · W[rows of this rank]; sum over ranks; then the bias (once) and the
+    // residual, like the unsharded layer
+    if (act != MU_ACT_NONE) return fail(MU_ERR_INVALID, "row-parallel Linear cannot carry an activation");
+    op.out = new_tensor(static_cast<size_t>(op.M) * Nl * esize(dtype));
+    push(op);
+    Op ar;
+    ar.kind = OP_ALLREDUCE, ar.in = op.out, ar.out = op.out, ar.n = 1ll * op.M * Nl;
+    push(ar);
+    Op e;
+    e.kind = OP_ELTWISE, e.in = op.out, e.b = bias_id, e.N = Nl, e.n = 1ll * op.M * Nl, e.res = res_tid;
+    if (res_tid >= 0) {
+      e.out = new_tensor(0);
+      tensors[e.out].alias_of = root(res_tid);
+    } else {
+      e.out = op.out;
+    }
+    push(e);
+    v.tid = e.out;
+    v.shape.back() = Nl;
+    return MU_OK;
+  }
+  op.b = bias_id;
+  op.res = res_tid;
   if (res_tid >= 0) {
     // x + f(x): the epilogue reads and writes the same element, so the residual
     // stream is updated in place.
     op.out = new_tensor(0);
     tensors[op.out].alias_of = root(res_tid);
   } else {
-    op.out = new_tensor(static_cast<size_t>(op.M) * N * esize(dtype));
+    op.out = new_tensor(static_cast<size_t>(op.M) * Nl * esize(dtype));
   }
   push(op);
   v.tid = op.out;
-  v.shape.back() = N;
+  v.shape.back() = Nl;
   return MU_OK;
 }
 
 // nn::MultiHeadAttention::forward_impl (src/nn/attention.hpp:34-103).
-int mu_engine::lower_mha(const std::string &prefix, int E, int H, bool causal, int res_tid, Val &v) {
+int mu_engine::lower_mha(const std::string &prefix, int E, int H, bool causal, int res_tid, Val &v,
+                         bool shard) {
   if (v.shape.size() != 3)
     return fail(MU_ERR_INVALID, "MultiHeadAttention expects input shape [B,T,E]");
   if (v.shape[2] != E)
@@ -316,16 +373,25 @@ int mu_engine::lower_mha(const std::string &prefix, int E, int H, bool causal, i
   if (H <= 0 || E % H)
     return fail(MU_ERR_INVALID, "MultiHeadAttention: embed_dim must be divisible by num_heads");
   const int B = v.shape[0], T = v.shape[1], D = E / H;
-  const size_t per = static_cast<size_t>(B) * T * E * esize(dtype);
+  const bool tp = tp_size > 1 && shard;
+  if (tp && H % tp_size)
+    return fail(MU_ERR_INVALID, "MultiHeadAttention: %d heads do not divide over %d ranks", H, tp_size);
+  const int Hfull = H;
+  if (tp) H = H / tp_size; // this rank's heads [tp_rank*H, (tp_rank+1)*H)
+  const int El = H * D;
+  const size_t per = static_cast<size_t>(B) * T * El * esize(dtype);
   std::string why;
+  Slice sl;
+  if (tp) sl.c0 = 1ll * tp_rank * El, sl.c1 = 1ll * (tp_rank + 1) * El;
+  (void)Hfull;
   Op q;
   q.kind = OP_QKV;
-  q.w = stage_weight({prefix + "q_proj.weight", prefix + "k_proj.weight", prefix + "v_proj.weight"}, &why);
+  q.w = stage_weight({prefix + "q_proj.weight", prefix + "k_proj.weight", prefix + "v_proj.weight"}, &why, sl);
   if (q.w >= 0)
-    q.b = stage_weight({prefix + "q_proj.bias", prefix + "k_proj.bias", prefix + "v_proj.bias"}, &why);
+    q.b = stage_weight({prefix + "q_proj.bias", prefix + "k_proj.bias", prefix + "v_proj.bias"}, &why, sl);
   if (q.w < 0 || q.b < 0)
     return fail(MU_ERR_INVALID, "MultiHeadAttention '%s': %s", prefix.c_str(), why.c_str());
-  q.B = B, q.T = T, q.K = E, q.H = H;
+  q.B = B, q.T = T, q.K = E, q.H = H, q.D = D;
   q.in = v.tid;
   q.out = new_tensor(3 * per); // q | k | v, head-major, contiguous
   push(q);
@@ -338,8 +404,8 @@ int mu_engine::lower_mha(const std::string &prefix, int E, int H, bool causal, i
   a.out = new_tensor(per);
   push(a);
   v.tid = a.out;
-  v.shape = {B * T, E};
-  int rc = lower_linear(prefix + "out_proj.", E, E, true, MU_ACT_NONE, res_tid, v);
+  v.shape = {B * T, El};
+  int rc = lower_linear(prefix + "out_proj.", E, E, true, MU_ACT_NONE, res_tid, v, tp ? 2 : 0);
   v.shape = {B, T, E};
   return rc;
 }
@@ -363,10 +429,10 @@ int mu_engine::lower_block(const std::string &prefix, int d, int H, Val &v) {
     h.tid = n.out;
     int rc;
     if (half == 0) {
-      rc = lower_mha(prefix + "attn.", d, H, true, v.tid, h);
+      rc = lower_mha(prefix + "attn.", d, H, true, v.tid, h, true);
     } else {
-      rc = lower_linear(prefix + "ff.0.", d, 4 * d, true, MU_ACT_GELU, -1, h);
-      if (rc == MU_OK) rc = lower_linear(prefix + "ff.2.", 4 * d, d, true, MU_ACT_NONE, v.tid, h);
+      rc = lower_linear(prefix + "ff.0.", d, 4 * d, true, MU_ACT_GELU, -1, h, 1);
+      if (rc == MU_OK) rc = lower_linear(prefix + "ff.2.", 4 * d, d, true, MU_ACT_NONE, v.tid, h, 2);
     }
     if (rc) return rc;
     v.tid = h.tid;
@@ -598,7 +664,8 @@ int mu_engine::lower(const Json &node, const std::string &prefix, Val &v, const 
     n.out = new_tensor(static_cast<size_t>(B) * T * d * esize(dtype));
     push(n);
     v.tid = n.out;
-    return lower_linear(prefix + "head.", d, V, true, MU_ACT_NONE, -1, v);
+    // under tensor parallelism the LM head is column-parallel: each rank owns a vocabulary slab
+    return lower_linear(prefix + "head.", d, V, true, MU_ACT_NONE, -1, v, 1);
   }
   return fail(MU_ERR_UNSUPPORTED, "Unsupported serialized module type for C++ reconstruction: %s",
               type.c_str());
@@ -649,7 +716,7 @@ int mu_engine::plan_and_allocate() {
       return fail(MU_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(cudaGetLastError()));
   }
   for (auto &d : dev_copies)
-    if (cudaMemcpy2D(static_cast<char *>(weight_slab) + d.dst, d.dst_pitch, d.src, d.width, d.width,
+    if (cudaMemcpy2D(static_cast<char *>(weight_slab) + d.dst, d.dst_pitch, d.src, d.src_pitch, d.width,
                      d.rows, cudaMemcpyDeviceToDevice) != cudaSuccess)
       return fail(MU_ERR_CUDA, "weight copy failed: %s", cudaGetErrorString(cudaGetLastError()));
   std::vector<uint8_t>().swap(weight_stage);
@@ -686,9 +753,9 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       break;
     case OP_QKV: {
       char *base = static_cast<char *>(tptr(op.out));
-      const size_t per = static_cast<size_t>(op.B) * op.T * op.K * esize(dtype);
-      rc = mu_linear_qkv(ctx, tptr(op.in), wptr(op.w), wptr(op.b), base, base + per, base + 2 * per,
-                         op.B, op.T, op.K, op.H, dtype, st);
+      const size_t per = static_cast<size_t>(op.B) * op.T * op.H * op.D * esize(dtype);
+      rc = mu_linear_qkv_heads(ctx, tptr(op.in), wptr(op.w), wptr(op.b), base, base + per, base + 2 * per,
+                               op.B, op.T, op.K, op.H, op.D, dtype, st);
       n_launches += 1;
       break;
     }
@@ -701,7 +768,12 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       break;
     }
     case OP_ELTWISE:
-      rc = mu_eltwise(ctx, tptr(op.in), nullptr, tptr(op.res), tptr(op.out), op.n, 1, op.act, dtype, st);
+      rc = mu_eltwise(ctx, tptr(op.in), wptr(op.b), tptr(op.res), tptr(op.out), op.n,
+                      op.b >= 0 ? op.N : 1, op.act, dtype, st);
+      n_launches += 1;
+      break;
+    case OP_ALLREDUCE:
+      rc = mu_all_reduce_sum(ctx, comm, tptr(op.in), op.n, dtype, st);
       n_launches += 1;
       break;
     case OP_ARGMAX:
@@ -742,8 +814,8 @@ void mu_engine::op_work(const Op &op, double *flops, double *bytes) const {
     *bytes = es * (1.0 * op.M * op.K + 1.0 * op.K * op.N + 1.0 * op.M * op.N * (op.res >= 0 ? 2 : 1));
     break;
   case OP_QKV:
-    *flops = 2.0 * op.B * op.T * op.K * 3.0 * op.K;
-    *bytes = es * (1.0 * op.B * op.T * op.K * 4 + 3.0 * op.K * op.K);
+    *flops = 2.0 * op.B * op.T * op.K * 3.0 * op.H * op.D;
+    *bytes = es * (1.0 * op.B * op.T * (op.K + 3.0 * op.H * op.D) + 3.0 * op.K * op.H * op.D);
     break;
   case OP_ATTN: {
     const double sq = 1.0 * op.B * op.H * op.T * op.T * op.D;
@@ -762,6 +834,9 @@ void mu_engine::op_work(const Op &op, double *flops, double *bytes) const {
     break;
   case OP_ARGMAX:
     *bytes = es * op.M * op.N + 4.0 * op.M;
+    break;
+  case OP_ALLREDUCE:
+    *bytes = es * op.n; // bytes each rank contributes
     break;
   case OP_CONV: {
     const double oH = (op.iH + 2 * op.pad - op.ksz) / op.stride + 1, oW = (op.iW + 2 * op.pad - op.ksz) / op.stride + 1;
@@ -846,6 +921,8 @@ int mu_engine_set_option(mu_engine *e, const char *name, int value) {
     e->kmode = value;
   } else if (n == "use_graph") e->use_graph = value;
   else if (n == "argmax") e->want_argmax = value;
+  else if (n == "tp_rank") e->tp_rank = value;
+  else if (n == "tp_size") e->tp_size = value;
   else return e->fail(MU_ERR_INVALID, "unknown option '%s'", name);
   return MU_OK;
 }
@@ -892,9 +969,28 @@ int mu_engine_load_memory(mu_engine *e, const char *config_json, int n_tensors,
   return finish_load(e, compute_dtype);
 }
 
+// Communicator for the tensor-parallel all-reduces (options "tp_size"/"tp_rank" select the shard).
+int mu_engine_set_comm(mu_engine *e, mu_comm *comm) {
+  if (!e) return MU_ERR_INVALID;
+  e->comm = comm;
+  return MU_OK;
+}
+
 int mu_engine_compile(mu_engine *e, const int *input_shape, int ndim, int input_dtype) {
   if (!e || !input_shape || ndim <= 0) return MU_ERR_INVALID;
   if (!e->loaded) return e->fail(MU_ERR_INVALID, "Engine: no module loaded");
+  if (e->tp_size < 1 || e->tp_rank < 0 || e->tp_rank >= e->tp_size)
+    return e->fail(MU_ERR_INVALID, "Engine: bad tensor-parallel rank %d of %d", e->tp_rank, e->tp_size);
+  if (e->tp_size > 1 && (!e->comm || mu_comm_world(e->comm) != e->tp_size))
+    return e->fail(MU_ERR_INVALID, "Engine: tp_size %d needs a communicator of that size", e->tp_size);
+  if (e->tp_size > 1 && e->kmode == MU_K_LITERAL)
+    // literal K addressing reinterprets the WHOLE head-major K buffer ([B*H*T, D] read as
+    // [D, B*H*T]), so a score mixes rows of every head: it does not commute with sharding heads
+    return e->fail(MU_ERR_UNSUPPORTED,
+                   "Engine: tensor parallelism needs kmode = MU_K_MATH (literal K addressing reads "
+                   "across all heads and cannot be sharded by head)");
+  if (e->tp_size > 1 && e->want_argmax)
+    return e->fail(MU_ERR_UNSUPPORTED, "Engine: argmax over a vocabulary-sharded head is not implemented");
   e->release_compiled();
   e->weight_bytes = 0;
   Val v;

@@ -105,7 +105,7 @@ class Engine:
     """``load`` → ``compile`` → ``run``; one instance per device context."""
 
     def __init__(self, ctx: Context | None = None, device: int = 0, compute_dtype: int = F32,
-                 kmode: int = 0, use_graph: bool = True, argmax: bool = False):
+                 kmode: int = 0, use_graph: bool = True, argmax: bool = False, comm=None):
         self._lib = lib()
         self.ctx = ctx or Context(device)
         self.compute_dtype = compute_dtype
@@ -119,6 +119,11 @@ class Engine:
         self._opt("kmode", kmode)
         self._opt("use_graph", int(use_graph))
         self._opt("argmax", int(argmax))
+        self.comm = comm
+        if comm is not None and comm.world > 1:  # tensor-parallel shard of the decoder blocks
+            self._opt("tp_size", comm.world)
+            self._opt("tp_rank", comm.rank)
+            self._rc(self._lib.mu_engine_set_comm(self._h, comm._h))
         self.input_shape = None
         self.output_shape = None
 
