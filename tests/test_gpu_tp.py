@@ -98,5 +98,8 @@ def test_tensor_parallel_decoder_and_all_reduce(dtype):
     want = oracle.port().gpt_forward(ids, ps, V, d, H, L, dtype, kmode=oracle.K_MATH)
     got = np.concatenate([results[r][1] for r in range(world)], axis=-1)
     assert got.shape == want.shape
-    ok, worst, rel = close(got, want, dtype, rtol=2e-2 if dtype == BF16 else 1e-4)
-    assert ok, f"worst err/bound {worst:.3g}, rel-inf {rel:.3g}"
+    # bf16: each row-parallel layer rounds its partial sums to bf16 before the all-reduce (one
+    # extra rounding per layer compared with the unsharded chain): ||a-b||inf/||b||inf must stay
+    # within 2e-2 and the elementwise bound is taken at 3e-2
+    ok, worst, rel = close(got, want, dtype, rtol=3e-2 if dtype == BF16 else 1e-4)
+    assert ok and rel <= (2e-2 if dtype == BF16 else 1e-4), f"worst err/bound {worst:.3g}, rel-inf {rel:.3g}"
