@@ -161,14 +161,16 @@ def run_reference(args, cfg):
     print(json.dumps(line))
 
 
-def workload_config(cfg, n_gpus):
+def workload_config(cfg, n_gpus, tp=1):
     return {
         "workload": (f"GPT decoder forward: {cfg['n_layers']}L d{cfg['d_model']} h{cfg['n_heads']} "
                      f"vocab {cfg['vocab']} seq {cfg['seq']} batch {cfg['batch']}/GPU, pre-LN, "
                      "causal, 4x GELU MLP, weights N(0,0.02), uniform random ids"),
-        "global_batch": cfg["batch"] * n_gpus, "seq_len": cfg["seq"],
-        "parallelism": f"batch-sharded x{n_gpus}, full replica per GPU, no collective",
-        "attention_k_addressing": "literal (reference semantics)",
+        "global_batch": cfg["batch"] * (n_gpus if tp == 1 else 1), "seq_len": cfg["seq"],
+        "parallelism": (f"batch-sharded x{n_gpus}, full replica per GPU, no collective" if tp == 1 else
+                        f"tensor-parallel x{tp} (Megatron column/row split, NCCL all-reduce), one replica"),
+        "attention_k_addressing": ("literal (reference semantics)" if tp == 1 else
+                                   "math (true Q.K^T; literal addressing cannot be head-sharded)"),
         "l2": "no flush needed: per-step working set (2.7 GB weights + >6 GB activations) >> 126 MB L2",
         "e2e_result": "argmax token ids [batch, seq] int32 read back to the host",
     }
@@ -207,7 +209,17 @@ def run_ours(args, cfg):
             tensors[name] = w(*shape)
 
     ctx = mb.Context(local)
-    eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_LITERAL, argmax=True)
+    tp = args.tp
+    comm = None
+    if tp > 1:
+        # tensor-parallel variant: all ranks form ONE model replica and run the SAME batch; heads,
+        # MLP columns and the vocabulary are split over ranks, partial sums meet in an NCCL
+        # all-reduce. Needs true Q.K^T (literal K addressing reads across heads).
+        if world != tp:
+            raise SystemExit("--tp N runs one tensor-parallel group: launch exactly N ranks")
+        comm = mb.Comm.from_torch_distributed(ctx)
+    eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_MATH if tp > 1 else mb.K_LITERAL,
+                 argmax=tp == 1, comm=comm)
     eng.load(gpt_decoder_config(V, T, d, H, L), tensors)
     eng.compile((B, T), mb.I32)
     del tensors
@@ -218,7 +230,7 @@ def run_ours(args, cfg):
     from munet_b200.sharding import max_over_ranks, shard_bounds
     ids_gen = torch.Generator(device="cpu")
     ids_gen.manual_seed(2005)
-    lo, hi = shard_bounds(B * world, rank, world)
+    lo, hi = shard_bounds(B * world, rank, world) if tp == 1 else (0, B)
     ids_host = torch.randint(0, V, (B * world, T), generator=ids_gen, dtype=torch.int32)[lo:hi]
     ids_host = ids_host.contiguous().pin_memory()
     ids_dev = ids_host.to(dev)
@@ -231,11 +243,20 @@ def run_ours(args, cfg):
         if rc:
             raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
 
+    Vl = V // tp
+    last_host = torch.empty((B, Vl), dtype=torch.bfloat16).pin_memory() if tp > 1 else None
+
     def step_e2e():
-        rc = lib.mu_engine_run(eng._h, ids_host.data_ptr(), 1, None, 0, am_host.data_ptr(), 1,
-                               stream.cuda_stream)
+        rc = lib.mu_engine_run(eng._h, ids_host.data_ptr(), 1, None, 0,
+                               am_host.data_ptr() if tp == 1 else None, 1, stream.cuda_stream)
         if rc:
             raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
+        if tp > 1:  # result = next-token logits (this rank's vocabulary slab) of every sequence
+            base = eng.output_ptr
+            for b in range(B):
+                lib.mu_copy(ctx._h, last_host.data_ptr() + b * Vl * 2,
+                            base + ((b * T + T - 1) * Vl) * 2, Vl * 2, 2, stream.cuda_stream)
+            ctx.check(stream)
 
     def barrier():
         torch.cuda.synchronize()
@@ -266,7 +287,7 @@ def run_ours(args, cfg):
     ms_e2e = timed(step_e2e, args.steps)
     ctx.check()
 
-    tokens_step = B * T * world
+    tokens_step = B * T * (world if tp == 1 else 1)
     value = tokens_step * args.steps / (ms_total / 1e3)
     e2e_value = tokens_step * args.steps / (ms_e2e / 1e3)
 
@@ -306,9 +327,9 @@ def run_ours(args, cfg):
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": workload_config(cfg, world),
+            "data": "synthetic", "config": workload_config(cfg, world, tp), "scaling_note": "strong (one batch over tp ranks)" if tp > 1 else None,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": B * T * 4 * world,
-                    "d2h_bytes_per_step": B * T * 4 * world, "ms_per_step": ms_e2e / args.steps},
+                    "d2h_bytes_per_step": (B * T * 4 * world if tp == 1 else B * Vl * 2 * world), "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": stats["n_launches"] * args.steps,
             "roofline": roofline, "clocks": clocks,
             "model_tflops_per_s": flops_step * args.steps / (ms_total / 1e3) / 1e12,
@@ -334,6 +355,7 @@ def main():
     ap.add_argument("--config", default="gpt_l", choices=sorted(CONFIGS))
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (variant run)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.batch:
