@@ -1,0 +1,109 @@
+"""GPU parity at the BASELINE transformer configs (bf16, literal K addressing).
+
+The CPU checker cannot run the full batches, so parity uses what the domain offers:
+sequences are independent (Engine::run_batch is a loop over inputs) and attention is
+causal, hence the logits of the first P positions of one sequence depend only on its
+first P tokens. The engine runs the FULL config; the checker runs a prefix of selected
+sequences through all layers; plus shard invariance: a sequence's logits do not depend
+on which batch (shard) it is run in."""
+import numpy as np
+import pytest
+
+import oracle
+from oracle import BF16, I32
+from tests.util import close
+
+pytestmark = pytest.mark.gpu
+
+
+def decoder_weights(rng, V, T, d, L):
+    """N(0, 0.02) weights, zero biases, LayerNorm gamma 1 / beta 0 (bf16 bit patterns)."""
+    def w(*s):
+        return oracle.to_bf16((rng.standard_normal(s) * 0.02).astype(np.float32))
+    one, zero = oracle.to_bf16(np.ones(d, np.float32)), oracle.to_bf16(np.zeros(d, np.float32))
+
+    def z(n):
+        return oracle.to_bf16(np.zeros(n, np.float32))
+    ps = [w(V, d), w(T, d)]
+    for _ in range(L):
+        ps += [one, zero]
+        for _ in range(4):
+            ps += [w(d, d), z(d)]
+        ps += [one, zero, w(d, 4 * d), z(4 * d), w(4 * d, d), z(d)]
+    ps += [one, zero, w(d, V), z(V)]
+    return ps
+
+
+@pytest.mark.parametrize("name,V,T,d,H,L,B,prefix", [
+    ("gpt_s", 8192, 256, 512, 8, 6, 32, 256),
+    ("gpt_l", 32000, 1024, 2048, 16, 24, 8, 48),
+])
+def test_full_config_prefix_parity_math_mode(name, V, T, d, H, L, B, prefix):
+    """Full-size config on the GPU (true Q.K^T) vs the checker on a token prefix of two sequences."""
+    import munet_b200 as mb
+    from munet_b200.inference import Engine, gpt_decoder_config, gpt_param_names
+    seed = 4 if name == "gpt_s" else 5
+    rng = np.random.default_rng(1000 + seed)
+    ps = decoder_weights(rng, V, T, d, L)
+    ids = np.random.default_rng(2000 + seed).integers(0, V, (B, T)).astype(np.int32)
+    ctx = mb.Context(0)
+    eng = Engine(ctx=ctx, compute_dtype=BF16, kmode=mb.K_MATH, argmax=True)
+    eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)), tensor_dtype=BF16)
+    eng.compile((B, T), I32)
+    logits, am = eng.run(ids)
+    assert logits.shape == (B, T, V) and np.isfinite(oracle.from_bf16(logits[:, ::max(1, T // 8)])).all()
+    # device argmax == first-max argmax of the device logits (bit-exact index rule)
+    assert np.array_equal(am, oracle.port().argmax(logits, BF16))
+    for b in (0, B - 1):
+        sub_ps = list(ps)
+        sub_ps[1] = ps[1][:prefix]  # positional table rows 0..prefix-1
+        want = oracle.port().gpt_forward(ids[b:b + 1, :prefix], sub_ps, V, d, H, L, BF16, kmode=oracle.K_MATH)
+        got = logits[b:b + 1, :prefix]
+        # Deep bf16 stacks: two valid evaluation orders of the same bf16 pipeline (fp32 vs double
+        # accumulation, online vs two-pass softmax) drift apart by rounding noise that grows with
+        # depth. Criteria at full size: max error within 2e-2 of the largest logit, RMS error within
+        # 2e-2 of the RMS logit, and no element further than 5x the elementwise small-shape bound
+        # (measured: 2.2x at 6 layers, 3.7x at 24 layers).
+        ok, worst, rel = close(got, want, BF16, rtol=2e-2)
+        g, w_ = oracle.from_bf16(got).astype(np.float64), oracle.from_bf16(want).astype(np.float64)
+        rel_rms = float(np.sqrt(np.mean((g - w_) ** 2)) / np.sqrt(np.mean(w_ ** 2)))
+        assert rel <= 2e-2 and rel_rms <= 2e-2 and worst <= 5.0, \
+            f"{name} seq {b}: worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}"
+        agree = float((oracle.port().argmax(got, BF16) == oracle.port().argmax(want, BF16)).mean())
+        assert agree >= 0.9, f"{name} seq {b}: argmax agreement {agree}"
+    # shard invariance (math mode): sequences 0 and B-1 run alone give bit-identical logits
+    sub = np.ascontiguousarray(ids[[0, B - 1]])
+    eng2 = Engine(ctx=ctx, compute_dtype=BF16, kmode=mb.K_MATH)
+    eng2.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)), tensor_dtype=BF16)
+    eng2.compile(sub.shape, I32)
+    logits_sub = eng2.run(sub)
+    assert np.array_equal(logits_sub[0], logits[0]) and np.array_equal(logits_sub[1], logits[B - 1])
+    eng.close()
+    eng2.close()
+    ctx.close()
+
+
+def test_gpt_s_literal_mode_full_batch_geometry():
+    """Config 4 geometry (H8 D64 T256) in the reference's literal K addressing: the checker needs the
+    whole batch (scores read K rows of every head), so the batch is reduced to 2 and the layers to 2;
+    the attention shapes per head are the config's."""
+    import munet_b200 as mb
+    from munet_b200.inference import Engine, gpt_decoder_config, gpt_param_names
+    V, T, d, H, L, B = 8192, 256, 512, 8, 2, 2
+    rng = np.random.default_rng(1004)
+    ps = decoder_weights(rng, V, T, d, L)
+    ids = np.random.default_rng(2004).integers(0, V, (B, T)).astype(np.int32)
+    want = oracle.port().gpt_forward(ids, ps, V, d, H, L, BF16, kmode=oracle.K_LITERAL)
+    ctx = mb.Context(0)
+    eng = Engine(ctx=ctx, compute_dtype=BF16, kmode=mb.K_LITERAL)
+    eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)), tensor_dtype=BF16)
+    eng.compile((B, T), I32)
+    got = eng.run(ids)
+    ok, worst, rel = close(got, want, BF16, rtol=2e-2)
+    g, w_ = oracle.from_bf16(got).astype(np.float64), oracle.from_bf16(want).astype(np.float64)
+    rel_rms = float(np.sqrt(np.mean((g - w_) ** 2)) / np.sqrt(np.mean(w_ ** 2)))
+    # same full-size criteria as above (measured: worst element 1.6x the small-shape bound)
+    assert rel <= 2e-2 and rel_rms <= 2e-2 and worst <= 5.0, \
+        f"worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}"
+    eng.close()
+    ctx.close()
