@@ -6,12 +6,13 @@
 // reference runs as five full passes over a [B·H·T, B·H·T] matrix (two of them
 // on the host). Only the row's own head block is ever touched here.
 //
-// One CTA = one (head, 128-query tile); 192 threads:
+// One CTA = one (head, 128-query tile); 320 threads:
 //   warp 0    TMA producer: Q once, then K/V tiles of 128 keys through a ring.
 //   warp 1    tcgen05.mma issuer: S_j = Q·K_j' (M=128,N=128) into a double-
 //             buffered TMEM S tile, O_j = P_j·V_j (M=128,N=D) into a double-
 //             buffered TMEM O tile.
-//   warps 2-5 one query row per thread (TMEM lane = row): rounding/scale/mask,
+//   warps 2-9 two threads per query row (TMEM lane = row, each owns half of the
+//             columns; two warps per scheduler): rounding/scale/mask,
 //             running max and sum, P_j → swizzled smem (A operand of P·V),
 //             O accumulated in registers with the online-softmax correction,
 //             final O/l staged to smem and written with TMA (token-major,
@@ -27,7 +28,7 @@
 
 namespace mu {
 
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320; // producer warp, MMA warp, 8 softmax warps
 constexpr int BQ = 128, BKV = 128;
 
 template <int D> struct AttCfg {
@@ -37,7 +38,9 @@ template <int D> struct AttCfg {
   static constexpr int P_BYTES = BQ * BKV * 2; // one of two buffers
   static constexpr int STAGES = D == 128 ? 2 : 4;
   static constexpr int KV_STAGE = K_BYTES + V_BYTES;
-  static constexpr int SMEM_BYTES = Q_BYTES + STAGES * KV_STAGE + 2 * P_BYTES + 1024 + 256;
+  static constexpr int XCHG_BYTES = 1024; // row maxima / sums exchanged between paired softmax warps
+  static constexpr int SMEM_BYTES =
+      Q_BYTES + STAGES * KV_STAGE + 2 * P_BYTES + XCHG_BYTES + 1024 /*align*/ + 512 /*barriers*/;
   static constexpr int TMEM_COLS = 512; // S0 S1 at 0/128, O0 O1 at 256/256+D
 };
 
@@ -62,7 +65,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
   uint8_t *sQ = smem;
   uint8_t *sKV = sQ + Cfg::Q_BYTES;
   uint8_t *sP = sKV + STAGES * Cfg::KV_STAGE;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(sP + 2 * Cfg::P_BYTES);
+  uint8_t *xchg = sP + 2 * Cfg::P_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(xchg + Cfg::XCHG_BYTES);
   uint64_t *q_full = bars;
   uint64_t *kv_full = q_full + 1;
   uint64_t *kv_empty = kv_full + STAGES;
@@ -71,7 +75,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
   uint64_t *p_full = s_empty + 2;
   uint64_t *o_full = p_full + 2;
   uint64_t *o_empty = o_full + 2;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_empty + 2);
+  uint64_t *xbar = o_empty + 2; // [quarter][tile parity]: paired softmax warps
+  uint64_t *xend = xbar + 8;    // [quarter][0: row sums, 1: output staged]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(xend + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.y;
@@ -89,10 +95,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_empty[b], 4);
-      mbar_init(&p_full[b], 4);
+      mbar_init(&s_empty[b], 8);
+      mbar_init(&p_full[b], 8);
       mbar_init(&o_full[b], 1);
-      mbar_init(&o_empty[b], 4);
+      mbar_init(&o_empty[b], 8);
+    }
+    for (int i = 0; i < 8; ++i) {
+      mbar_init(&xbar[i], 2);
+      mbar_init(&xend[i], 2);
     }
     fence_barrier_init();
     prefetch_tmap(&tmQ);
@@ -211,19 +221,35 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
     }
     __syncwarp();
   } else {
-    // ------------------- softmax / correction / output (warps 2..5) -----------
+    // ------------- softmax / correction / output (warps 2..9, two per row quarter) -------
+    // Warps w and w+4 share the TMEM lane quarter q = w & 3 (rows q*32..q*32+31); `half`
+    // selects which 64 score columns and which D/2 output columns a thread owns. Two warps
+    // per scheduler hide each other's dependent-issue latency. The pair agrees on the row
+    // maximum through shared memory and a (bounded) mbarrier; row sums stay partial until the end.
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = q * 32 + lane;       // row inside the query tile = TMEM lane
     const int qrow = q0 + row;           // position in the sequence
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     const float scale_b = bf16_round(prm.scale);
     constexpr float L2E = 1.4426950408889634f;
+    constexpr int SC = BKV / 2; // score columns per thread
+    constexpr int DH = D / 2;   // output columns per thread
+    uint16_t *xm = reinterpret_cast<uint16_t *>(xchg); // [tile parity][half][row] partial maxima (bf16)
+    float *xl = reinterpret_cast<float *>(xchg);       // [half][row] partial row sums (end only)
     float m_run = -INFINITY, l_run = 0.f, alpha_pending = 1.f;
-    float o_acc[D];
+    float o_acc[DH];
 #pragma unroll
-    for (int i = 0; i < D; ++i)
+    for (int i = 0; i < DH; ++i)
       o_acc[i] = 0.f;
     bool ok = true;
+
+    auto pair_sync = [&](uint64_t *bar, uint32_t parity) -> bool {
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(bar);
+      return mbar_wait(bar, parity);
+    };
 
     auto consume_o = [&](int i, float a) -> bool {
       const int b = i & 1;
@@ -231,9 +257,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         return false;
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < DH / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem_O + lane_sel + b * D + c * 32, r);
+        tmem_ld_32x32(tmem_O + lane_sel + b * D + half * DH + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < 32; ++k)
@@ -260,24 +286,33 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       if (prm.causal)
         lim = min(lim, qrow - k0 + 1);
       const bool need_mask = (k0 + BKV > prm.T) || (prm.causal && k0 + BKV > q0); // warp-uniform
-      const uint32_t s_addr = tmem_S + lane_sel + b * BKV;
-      // pass 1: row maximum. Rounding and the (positive) scale are monotone, so the
-      // maximum of the transformed scores is the transform of the raw maximum.
+      const uint32_t s_addr = tmem_S + lane_sel + b * BKV + half * SC;
+      // pass 1: maximum over this thread's columns. Rounding and the (positive) scale are
+      // monotone, so the maximum of the transformed scores is the transform of the raw maximum.
       float raw_mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = 0; c < SC / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(s_addr + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
           float x = __uint_as_float(r[k]);
-          if (need_mask && c * 32 + k >= lim)
+          if (need_mask && half * SC + c * 32 + k >= lim)
             x = -INFINITY;
           raw_mx = fmaxf(raw_mx, x);
         }
       }
-      const float mx = fmaxf(m_run, bf16_round(bf16_round(raw_mx) * scale_b));
+      const float mine = bf16_round(bf16_round(raw_mx) * scale_b); // exactly a bf16 value (or -inf)
+      xm[(b * 2 + half) * BQ + row] = static_cast<uint16_t>(__float_as_uint(mine) >> 16);
+      if (!pair_sync(&xbar[q * 2 + b], static_cast<uint32_t>(j >> 1) & 1)) {
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      const float other =
+          __uint_as_float(static_cast<uint32_t>(xm[(b * 2 + (half ^ 1)) * BQ + row]) << 16);
+      const float mx = fmaxf(m_run, fmaxf(mine, other));
       // rows past the end of the sequence see no key at all: keep them finite
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
       const float mL = m_use * L2E;
@@ -285,7 +320,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       uint8_t *prow = sP + b * Cfg::P_BYTES + row * 128;
       float sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = 0; c < SC / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(s_addr + c * 32, r);
         tmem_ld_wait();
@@ -299,20 +334,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
           float p0 = exp2f(fmaf(x0, L2E, -mL));
           float p1 = exp2f(fmaf(x1, L2E, -mL));
           if (need_mask) {
-            if (c * 32 + k >= lim)
+            if (half * SC + c * 32 + k >= lim)
               p0 = 0.f;
-            if (c * 32 + k + 1 >= lim)
+            if (half * SC + c * 32 + k + 1 >= lim)
               p1 = 0.f;
           }
           sum += p0 + p1;
           pk[k / 2] = pack_bf16x2(p0, p1);
         }
-        // 32 columns = four 16-byte chunks; chunk index inside the 64-column box
+        // 32 columns = four 16-byte chunks of this thread's 64-column box (box index = half)
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-          const int gc = c * 4 + ch;          // 16-byte chunk 0..15 of the 128-key row
-          const int box = gc >> 3, cc = gc & 7;
-          *reinterpret_cast<uint4 *>(prow + box * (BQ * 128) + ((cc ^ (lane & 7)) << 4)) =
+          const int cc = c * 4 + ch;
+          *reinterpret_cast<uint4 *>(prow + half * (BQ * 128) + ((cc ^ (lane & 7)) << 4)) =
               make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
         }
       }
@@ -340,22 +374,30 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       ok = false;
     }
     if (ok) {
-      // normalise, stage this warp's 32 rows in the (now idle) P buffer, TMA-store
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      // full row sum = the pair's partial sums (every P·V has completed: xchg is idle)
+      xl[half * BQ + row] = l_run;
+      ok = pair_sync(&xend[q * 2 + 0], 0);
+      const float l_all = ok ? l_run + xl[(half ^ 1) * BQ + row] : 1.f;
+      // normalise and stage this thread's D/2 columns in the (now idle) P buffer
+      const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
       uint8_t *orow = sP + row * 128;
 #pragma unroll
-      for (int gc = 0; gc < D / 8; ++gc) {
+      for (int i = 0; i < DH / 8; ++i) {
+        const int gc = (half * DH) / 8 + i;
         const int box = gc >> 3, cc = gc & 7;
         uint32_t w[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          w[k] = pack_bf16x2(o_acc[gc * 8 + 2 * k] * inv, o_acc[gc * 8 + 2 * k + 1] * inv);
+          w[k] = pack_bf16x2(o_acc[i * 8 + 2 * k] * inv, o_acc[i * 8 + 2 * k + 1] * inv);
         *reinterpret_cast<uint4 *>(orow + box * (BQ * 128) + ((cc ^ (lane & 7)) << 4)) =
             make_uint4(w[0], w[1], w[2], w[3]);
       }
       fence_proxy_async();
-      __syncwarp();
-      if (lane == 0 && q0 + q * 32 < prm.T) {
+      if (ok)
+        ok = pair_sync(&xend[q * 2 + 1], 0);
+      if (!ok)
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+      if (ok && half == 0 && lane == 0 && q0 + q * 32 < prm.T) {
         const int bb = bh / prm.H, hh = bh % prm.H;
 #pragma unroll
         for (int db = 0; db < DB; ++db)
