@@ -5,13 +5,13 @@
 // add of nn::Linear (src/nn/linear.hpp:28-34), the activation module that
 // follows it and the residual add of the decoder block.
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM, 320 threads):
 //   warp 0   TMA producer: A [128 x 64] and B [64 x BN] tiles, 128-byte swizzle,
 //            STAGES-deep mbarrier ring. No cluster multicast anywhere.
 //   warp 1   allocates TMEM and issues tcgen05.mma (kind::f16, M=128, N=BN, K=16)
 //            from one thread; accumulators are double-buffered in TMEM so the
 //            epilogue of tile i overlaps the main loop of tile i+1.
-//   warps 2-5 epilogue: tcgen05.ld 32 lanes x 32 columns, scale / bias /
+//   warps 2-9 epilogue (two per TMEM lane quarter, alternate 64-column groups): tcgen05.ld 32 lanes x 32 columns, scale / bias /
 //            activation / residual in registers, 128-bit stores.
 // A is row-major [M,K] (K-major operand). B is either row-major [K,N] as MuNet
 // stores Linear weights (MN-major operand) or row-major [N,K] (K-major, "B
@@ -25,7 +25,7 @@ namespace mu {
 
 constexpr int BM = 128;
 constexpr int BK = 64; // 64 bf16 = 128 bytes = one swizzle row
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320; // TMA warp, MMA warp, 8 epilogue warps
 
 template <int BN> struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -33,9 +33,9 @@ template <int BN> struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int TMEM_COLS = 2 * BN;
-  // epilogue staging: per epilogue warp two [32 rows x 64 cols] bf16 boxes (128-byte rows)
+  // epilogue staging: one [32 rows x 64 cols] bf16 box (128-byte rows) per epilogue warp
   static constexpr int OUT_BOX_BYTES = 32 * 128;
-  static constexpr int OUT_BYTES = 4 * 2 * OUT_BOX_BYTES;
+  static constexpr int OUT_BYTES = 8 * OUT_BOX_BYTES;
   static constexpr int SMEM_BYTES =
       STAGES * STAGE_BYTES + OUT_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
@@ -205,7 +205,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t *empty_bar = full_bar + STAGES;
   uint64_t *tfull_bar = empty_bar + STAGES;
   uint64_t *tempty_bar = tfull_bar + 2;
-  uint64_t *res_bar = tempty_bar + 2; // [4 epilogue warps][2 buffers]
+  uint64_t *res_bar = tempty_bar + 2; // one per epilogue warp
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(res_bar + 8);
 
   const int warp = threadIdx.x >> 5;
@@ -223,7 +223,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], 4);
+      mbar_init(&tempty_bar[b], 8);
     }
     for (int b = 0; b < 8; ++b)
       mbar_init(&res_bar[b], 1);
@@ -333,8 +333,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     __syncwarp();
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
+    // ---------------- epilogue (warps 2..9) ----------------
+    // Two warps per TMEM lane quarter (warp & 3): they take alternate 64-column groups of the
+    // tile, so every scheduler has two epilogue warps to hide each other's latencies.
     const int q = warp & 3; // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;
     const bool rnd = ep.round_each != 0;
     const float alpha = (rnd && ep.alpha != 1.0f) ? bf16_round(ep.alpha) : ep.alpha;
     const __nv_bfloat16 *bias = static_cast<const __nv_bfloat16 *>(ep.bias);
@@ -343,7 +346,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const bool split = ep.split_T > 0;
     const int HD = ep.split_H * ep.split_D;
     int it = 0;
-    int gcount = 0; // staged 64-column groups issued by this warp (selects the staging buffer)
+    int gcount = 0; // staged 64-column groups issued by this warp (phase of its residual barrier)
     bool ok = true;
     for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       const int nt = static_cast<int>(tile % tiles_n);
@@ -360,17 +363,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       if (ep.tma_out) {
         // ---- staged epilogue: TMEM -> registers -> swizzled smem box -> TMA store ----
         const int m0 = mt * BM + q * 32; // first row of this warp's 32-row slab
-        uint8_t *wbuf = out_stage + (warp - 2) * 2 * Cfg::OUT_BOX_BYTES;
+        uint8_t *buf = out_stage + (warp - 2) * Cfg::OUT_BOX_BYTES;
         const bool has_res = ep.residual != nullptr;
         const bool has_alpha = ep.alpha != 1.0f;
         if (m0 < sh.M) {
 #pragma unroll 1
-          for (int g = 0; g < BN / 64; ++g) {
+          for (int g = half; g < BN / 64; g += 2) {
             const int n0 = nt * BN + g * 64;
             if (n0 >= sh.N)
               break; // warp-uniform
-            const int bsel = gcount & 1;
-            uint8_t *buf = wbuf + bsel * Cfg::OUT_BOX_BYTES;
             // tensor-map coordinates, dimensions ordered by ascending stride
             int c0, c1, c2, c3, c4;
             if (ep.tma_mode == 2) { // [which][B][H][T][D]
@@ -382,10 +383,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               c0 = n0, c1 = m0, c2 = bt, c3 = 0, c4 = 0;
             }
             if (lane == 0) {
-              bulk_wait_read<1>(); // the store issued from this buffer two groups ago has read it
+              bulk_wait_read<0>(); // the previous store from this buffer has finished reading it
               if (has_res) {
-                mbar_arrive_expect_tx(&res_bar[(warp - 2) * 2 + bsel], Cfg::OUT_BOX_BYTES);
-                tma_load_5d(buf, &tmR, &res_bar[(warp - 2) * 2 + bsel], c0, c1, c2, c3, c4);
+                mbar_arrive_expect_tx(&res_bar[warp - 2], Cfg::OUT_BOX_BYTES);
+                tma_load_5d(buf, &tmR, &res_bar[warp - 2], c0, c1, c2, c3, c4);
               }
             }
             __syncwarp();
@@ -396,7 +397,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             tmem_ld_32x32(taddr + 32, r1);
             tmem_ld_wait();
             if (has_res) {
-              if (!mbar_wait(&res_bar[(warp - 2) * 2 + bsel], (gcount >> 1) & 1)) {
+              if (!mbar_wait(&res_bar[warp - 2], gcount & 1)) {
                 atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
                 ok = false;
                 break;
@@ -453,7 +454,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         row_off = batch_off + 1ll * m * ep.ldc;
       }
 #pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+      for (int chunk = half; chunk < BN / 32; chunk += 2) {
         const int n0 = nt * BN + chunk * 32;
         if (n0 >= sh.N)
           break; // warp-uniform
