@@ -13,7 +13,7 @@ namespace mu {
 int launch_gemm_bf16_tcgen05(const GemmOperands &, const GemmShape &, const Epilogue &, int *status,
                              int num_sms, cudaStream_t);
 int launch_gemm_simt(const SimtArgs &, cudaStream_t);
-int launch_layer_norm(const void *, const void *, const void *, void *, long long, int, float, int,
+int launch_layer_norm(const void *, const void *, const void *, void *, long long, int, float, int, int *, int,
                       cudaStream_t);
 int launch_softmax(const void *, void *, long long, int, float, int, int, int, cudaStream_t);
 int launch_embedding(const int *, const void *, const void *, void *, long long, int, int, int, int,
@@ -447,7 +447,7 @@ int mu_layer_norm(mu_ctx *ctx, const void *x, const void *gamma, const void *bet
   MU_REQUIRE(x && gamma && beta && y, "LayerNorm: null pointer");
   if (!set_device(ctx))
     return fail(ctx, MU_ERR_CUDA, "LayerNorm: cannot select device");
-  int rc = mu::launch_layer_norm(x, gamma, beta, y, rows, cols, eps, dtype,
+  int rc = mu::launch_layer_norm(x, gamma, beta, y, rows, cols, eps, dtype, ctx->d_status, ctx->num_sms,
                                  static_cast<cudaStream_t>(stream));
   if (rc == 1)
     return fail(ctx, MU_ERR_UNSUPPORTED, "LayerNorm: dtype %d not implemented", dtype);

@@ -88,6 +88,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   }
 }
 
+// ---- untiled bulk copy global -> shared (both addresses and the size multiples of 16 B) ----
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes,
+                                          uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 // ---- TMA loads (tile mode, no multicast) ----
 __device__ __forceinline__ void prefetch_tmap(const void *tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

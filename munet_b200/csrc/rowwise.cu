@@ -430,14 +430,18 @@ static int ln_t(const void *x, const void *g, const void *b, void *y, long long 
         (const T *)x, (const T *)g, (const T *)b, (T *)y, rows, cols, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
+int launch_layer_norm_bf16_rows(const void *, const void *, const void *, void *, long long, int,
+                                float, int *, int, cudaStream_t); // layer_norm_bf16.cu
 int launch_layer_norm(const void *x, const void *g, const void *b, void *y, long long rows,
-                      int cols, float eps, int dtype, cudaStream_t st) {
+                      int cols, float eps, int dtype, int *status, int num_sms, cudaStream_t st) {
   if (rows <= 0)
     return 0;
   if (dtype == F32)
     return ln_t<float>(x, g, b, y, rows, cols, eps, st);
-  if (dtype == BF16)
-    return ln_t<__nv_bfloat16>(x, g, b, y, rows, cols, eps, st);
+  if (dtype == BF16) {
+    const int rc = launch_layer_norm_bf16_rows(x, g, b, y, rows, cols, eps, status, num_sms, st);
+    return rc == 1 ? ln_t<__nv_bfloat16>(x, g, b, y, rows, cols, eps, st) : rc;
+  }
   return 1;
 }
 

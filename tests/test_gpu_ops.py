@@ -112,7 +112,8 @@ def test_matmul_transA_is_rejected(ctx):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("rows,cols", [(64, 512), (1000, 2048), (7, 200), (5, 33), (3, 4096)])
+@pytest.mark.parametrize("rows,cols", [(64, 512), (1000, 2048), (7, 200), (5, 33), (3, 4096),
+                                       (1, 2048), (2371, 1024), (40003, 512), (20011, 2048)])
 def test_layer_norm(ctx, dtype, rows, cols):
     rng = np.random.default_rng(rows + cols)
     x = rnd(rng, (rows, cols), dtype, 2.0)
