@@ -28,7 +28,8 @@
 
 namespace mu {
 
-constexpr int ATT_THREADS = 320; // producer warp, MMA warp, 8 softmax warps
+constexpr int ATT_PARTS = 2;   // softmax warps per TMEM lane quarter (each owns 1/PARTS of the columns)
+constexpr int ATT_THREADS = 64 + 128 * ATT_PARTS; // producer warp, MMA warp, softmax warps
 constexpr int BQ = 128, BKV = 128;
 
 template <int D> struct AttCfg {
@@ -38,9 +39,10 @@ template <int D> struct AttCfg {
   static constexpr int P_BYTES = BQ * BKV * 2; // one of two buffers
   static constexpr int STAGES = D == 128 ? 2 : 4;
   static constexpr int KV_STAGE = K_BYTES + V_BYTES;
-  static constexpr int XCHG_BYTES = 1024; // row maxima / sums exchanged between paired softmax warps
+  // row maxima [tile parity][part][row] as bf16; the partial row sums [part][row] as fp32 reuse it
+  static constexpr int XCHG_BYTES = ATT_PARTS * BQ * 4;
   static constexpr int SMEM_BYTES =
-      Q_BYTES + STAGES * KV_STAGE + 2 * P_BYTES + XCHG_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+      Q_BYTES + STAGES * KV_STAGE + 2 * P_BYTES + XCHG_BYTES + 512 /*barriers*/;
   static constexpr int TMEM_COLS = 512; // S0 S1 at 0/128, O0 O1 at 256/256+D
 };
 
@@ -60,17 +62,27 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
   using Cfg = AttCfg<D>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int DB = D / 64; // 64-element boxes along the head dim
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw;
+  if (smem_u32(smem_raw) & 1023u) { // swizzled TMA boxes need 1024-byte alignment
+    if (threadIdx.x == 0)
+      atomicCAS(status, 0, MU_DEV_BAD_INDEX);
+    return;
+  }
   uint8_t *sQ = smem;
   uint8_t *sKV = sQ + Cfg::Q_BYTES;
   uint8_t *sP = sKV + STAGES * Cfg::KV_STAGE;
   uint8_t *xchg = sP + 2 * Cfg::P_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(xchg + Cfg::XCHG_BYTES);
   uint64_t *q_full = bars;
-  uint64_t *kv_full = q_full + 1;
-  uint64_t *kv_empty = kv_full + STAGES;
-  uint64_t *s_full = kv_empty + STAGES;
+  // K and V have their own full/empty rings over the same stage memory: a K buffer is free as
+  // soon as its Q·K' has run, long before the P·V that frees the V buffer of the same tile, so
+  // the next K tiles are requested a whole softmax tile earlier than with a joint barrier.
+  uint64_t *k_full = q_full + 1;
+  uint64_t *k_empty = k_full + STAGES;
+  uint64_t *v_full = k_empty + STAGES;
+  uint64_t *v_empty = v_full + STAGES;
+  uint64_t *s_full = v_empty + STAGES;
   uint64_t *s_empty = s_full + 2;
   uint64_t *p_full = s_empty + 2;
   uint64_t *o_full = p_full + 2;
@@ -90,19 +102,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_empty[b], 8);
-      mbar_init(&p_full[b], 8);
+      mbar_init(&s_empty[b], 4 * ATT_PARTS);
+      mbar_init(&p_full[b], 4 * ATT_PARTS);
       mbar_init(&o_full[b], 1);
-      mbar_init(&o_empty[b], 8);
+      mbar_init(&o_empty[b], 4 * ATT_PARTS);
     }
     for (int i = 0; i < 8; ++i) {
-      mbar_init(&xbar[i], 2);
-      mbar_init(&xend[i], 2);
+      mbar_init(&xbar[i], ATT_PARTS);
+      mbar_init(&xend[i], ATT_PARTS);
     }
     fence_barrier_init();
     prefetch_tmap(&tmQ);
@@ -130,14 +144,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       bool ok = true;
       for (int j = 0; j < nk && ok; ++j) {
         const int stage = j % STAGES;
-        if (!mbar_wait(&kv_empty[stage], ((j / STAGES) & 1) ^ 1)) {
+        if (!mbar_wait(&k_empty[stage], ((j / STAGES) & 1) ^ 1)) {
           atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
           ok = false;
           break;
         }
         uint8_t *sK = sKV + stage * Cfg::KV_STAGE;
         uint8_t *sV = sK + Cfg::K_BYTES;
-        mbar_arrive_expect_tx(&kv_full[stage], Cfg::KV_STAGE);
+        mbar_arrive_expect_tx(&k_full[stage], Cfg::K_BYTES);
         const int k0 = j * BKV;
         if (LITERAL) {
           // K' tile = rows d, columns bh*T + k0.. of the [D, N] view: [dbox][nbox][64 x 128 B]
@@ -145,19 +159,25 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
           for (int db = 0; db < DB; ++db)
 #pragma unroll
             for (int nb = 0; nb < 2; ++nb)
-              tma_load_3d(sK + (db * 2 + nb) * 8192, &tmK, &kv_full[stage],
+              tma_load_3d(sK + (db * 2 + nb) * 8192, &tmK, &k_full[stage],
                           bh * prm.T + k0 + nb * 64, db * 64, 0);
         } else {
 #pragma unroll
           for (int db = 0; db < DB; ++db)
-            tma_load_3d(sK + db * (BKV * 128), &tmK, &kv_full[stage], db * 64, k0, bh);
+            tma_load_3d(sK + db * (BKV * 128), &tmK, &k_full[stage], db * 64, k0, bh);
         }
+        if (!mbar_wait(&v_empty[stage], ((j / STAGES) & 1) ^ 1)) {
+          atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&v_full[stage], Cfg::V_BYTES);
         // V tile as MN-major B operand: [keybox][dbox][64 keys x 128 B]
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
           for (int db = 0; db < DB; ++db)
-            tma_load_3d(sV + (kb * DB + db) * 8192, &tmV, &kv_full[stage], db * 64,
+            tma_load_3d(sV + (kb * DB + db) * 8192, &tmV, &v_full[stage], db * 64,
                         k0 + kb * 64, bh);
       }
       if (!ok)
@@ -177,7 +197,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       auto issue_pv = [&](int i) -> bool {
         const int b = i & 1;
         const uint32_t par = static_cast<uint32_t>(i >> 1) & 1;
-        if (!mbar_wait(&p_full[b], par) || !mbar_wait(&o_empty[b], par ^ 1))
+        if (!mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1) || !mbar_wait(&p_full[b], par) ||
+            !mbar_wait(&o_empty[b], par ^ 1))
           return false;
         tc_fence_after();
         const uint32_t p_addr = smem_u32(sP + b * Cfg::P_BYTES);
@@ -189,12 +210,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
           umma_f16(tmem_O + b * D, ad, bd, idesc_pv, k != 0 ? 1u : 0u);
         }
         umma_commit(&o_full[b]);
-        umma_commit(&kv_empty[i % STAGES]);
+        umma_commit(&v_empty[i % STAGES]);
         return true;
       };
       for (int j = 0; j < nk && ok; ++j) {
         const int stage = j % STAGES, b = j & 1;
-        if (!mbar_wait(&kv_full[stage], (j / STAGES) & 1) ||
+        if (!mbar_wait(&k_full[stage], (j / STAGES) & 1) ||
             !mbar_wait(&s_empty[b], ((j >> 1) & 1) ^ 1)) {
           atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
           ok = false;
@@ -211,6 +232,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
           umma_f16(tmem_S + b * BKV, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[b]);
+        umma_commit(&k_empty[stage]);
         if (j > 0 && !issue_pv(j - 1)) {
           atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
           ok = false;
@@ -227,14 +249,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
     // per scheduler hide each other's dependent-issue latency. The pair agrees on the row
     // maximum through shared memory and a (bounded) mbarrier; row sums stay partial until the end.
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 2) >> 2; // which 1/PARTS of the columns
     const int row = q * 32 + lane;       // row inside the query tile = TMEM lane
     const int qrow = q0 + row;           // position in the sequence
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     const float scale_b = bf16_round(prm.scale);
     constexpr float L2E = 1.4426950408889634f;
-    constexpr int SC = BKV / 2; // score columns per thread
-    constexpr int DH = D / 2;   // output columns per thread
+    constexpr int SC = BKV / ATT_PARTS; // score columns per thread
+    constexpr int DH = D / ATT_PARTS;   // output columns per thread
     uint16_t *xm = reinterpret_cast<uint16_t *>(xchg); // [tile parity][half][row] partial maxima (bf16)
     float *xl = reinterpret_cast<float *>(xchg);       // [half][row] partial row sums (end only)
     float m_run = -INFINITY, l_run = 0.f, alpha_pending = 1.f;
@@ -256,14 +278,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       if (!mbar_wait(&o_full[b], static_cast<uint32_t>(i >> 1) & 1))
         return false;
       tc_fence_after();
+      if constexpr (DH % 32 == 0) {
 #pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_O + lane_sel + b * D + half * DH + c * 32, r);
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_O + lane_sel + b * D + half * DH + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 32; ++k)
+            o_acc[c * 32 + k] = fmaf(o_acc[c * 32 + k], a, __uint_as_float(r[k]));
+        }
+      } else {
+        static_assert(DH % 32 == 0 || DH == 16, "output columns per thread");
+        uint32_t r[16];
+        tmem_ld_32x16(tmem_O + lane_sel + b * D + half * DH, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int k = 0; k < 32; ++k)
-          o_acc[c * 32 + k] = fmaf(o_acc[c * 32 + k], a, __uint_as_float(r[k]));
+        for (int k = 0; k < 16; ++k)
+          o_acc[k] = fmaf(o_acc[k], a, __uint_as_float(r[k]));
       }
       tc_fence_before();
       __syncwarp();
@@ -287,78 +319,86 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         lim = min(lim, qrow - k0 + 1);
       const bool need_mask = (k0 + BKV > prm.T) || (prm.causal && k0 + BKV > q0); // warp-uniform
       const uint32_t s_addr = tmem_S + lane_sel + b * BKV + half * SC;
-      // pass 1: maximum over this thread's columns. Rounding and the (positive) scale are
-      // monotone, so the maximum of the transformed scores is the transform of the raw maximum.
-      float raw_mx = -INFINITY;
+      // pass 1: first rounding (fp32 accumulator -> bf16, packed pairs kept in registers), mask,
+      // and the maximum over this thread's columns on the packed values. Rounding and the
+      // (positive) scale are monotone, so the maximum of the transformed scores is the transform
+      // of the maximum.
+      uint32_t sp[SC / 2];
+      uint32_t mx2 = 0xFF80FF80u; // (-inf, -inf)
+      {
+        uint32_t r[SC / 32][32];
 #pragma unroll
-      for (int c = 0; c < SC / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
+        for (int c = 0; c < SC / 32; ++c)
+          tmem_ld_32x32(s_addr + c * 32, r[c]);
         tmem_ld_wait();
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          float x = __uint_as_float(r[k]);
-          if (need_mask && half * SC + c * 32 + k >= lim)
-            x = -INFINITY;
-          raw_mx = fmaxf(raw_mx, x);
-        }
+        for (int c = 0; c < SC / 32; ++c)
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            uint32_t u = pack_bf16x2(__uint_as_float(r[c][k]), __uint_as_float(r[c][k + 1]));
+            if (need_mask) {
+              const int col = half * SC + c * 32 + k;
+              if (col >= lim)
+                u = (u & 0xFFFF0000u) | 0x0000FF80u;
+              if (col + 1 >= lim)
+                u = (u & 0x0000FFFFu) | 0xFF800000u;
+            }
+            sp[c * 16 + k / 2] = u;
+            mx2 = bf16x2_max(mx2, u);
+          }
       }
-      const float mine = bf16_round(bf16_round(raw_mx) * scale_b); // exactly a bf16 value (or -inf)
-      xm[(b * 2 + half) * BQ + row] = static_cast<uint16_t>(__float_as_uint(mine) >> 16);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&s_empty[b]); // the scores now live in registers
+      const float raw_mx = fmaxf(bf16_lo(mx2), bf16_hi(mx2));
+      const float mine = bf16_round(raw_mx * scale_b); // exactly a bf16 value (or -inf)
+      xm[(b * ATT_PARTS + half) * BQ + row] = static_cast<uint16_t>(__float_as_uint(mine) >> 16);
       if (!pair_sync(&xbar[q * 2 + b], static_cast<uint32_t>(j >> 1) & 1)) {
         atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
         ok = false;
         break;
       }
-      const float other =
-          __uint_as_float(static_cast<uint32_t>(xm[(b * 2 + (half ^ 1)) * BQ + row]) << 16);
-      const float mx = fmaxf(m_run, fmaxf(mine, other));
+      float mx = m_run;
+#pragma unroll
+      for (int pt = 0; pt < ATT_PARTS; ++pt)
+        mx = fmaxf(mx, __uint_as_float(static_cast<uint32_t>(xm[(b * ATT_PARTS + pt) * BQ + row]) << 16));
       // rows past the end of the sequence see no key at all: keep them finite
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
       const float mL = m_use * L2E;
-      // pass 2: probabilities → bf16 → swizzled smem (K-major A operand of P·V)
+      // pass 2: second rounding (times the bf16 scale, one packed multiply), probabilities ->
+      // bf16 -> swizzled smem (K-major A operand of P·V). Masked columns hold -inf: exp2 gives 0.
       uint8_t *prow = sP + b * Cfg::P_BYTES + row * 128;
-      float sum = 0.f;
+      const uint32_t scale2 = (__float_as_uint(scale_b) >> 16) * 0x00010001u;
+      float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
       for (int c = 0; c < SC / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          // s = bf16(bf16(acc) * bf16(scale)): packed converts, two columns at a time
-          uint32_t u = pack_bf16x2(__uint_as_float(r[k]), __uint_as_float(r[k + 1]));
-          u = pack_bf16x2(bf16_lo(u) * scale_b, bf16_hi(u) * scale_b);
-          const float x0 = bf16_lo(u), x1 = bf16_hi(u);
-          float p0 = exp2f(fmaf(x0, L2E, -mL));
-          float p1 = exp2f(fmaf(x1, L2E, -mL));
-          if (need_mask) {
-            if (half * SC + c * 32 + k >= lim)
-              p0 = 0.f;
-            if (half * SC + c * 32 + k + 1 >= lim)
-              p1 = 0.f;
-          }
-          sum += p0 + p1;
-          pk[k / 2] = pack_bf16x2(p0, p1);
+        for (int k = 0; k < 16; ++k) {
+          const uint32_t u = bf16x2_mul(sp[c * 16 + k], scale2);
+          const float p0 = ex2_approx(fmaf(bf16_lo(u), L2E, -mL));
+          const float p1 = ex2_approx(fmaf(bf16_hi(u), L2E, -mL));
+          sum0 += p0;
+          sum1 += p1;
+          pk[k] = pack_bf16x2(p0, p1);
         }
-        // 32 columns = four 16-byte chunks of this thread's 64-column box (box index = half)
+        // 32 columns = four 16-byte chunks of one 64-column box of the P tile
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-          const int cc = c * 4 + ch;
-          *reinterpret_cast<uint4 *>(prow + half * (BQ * 128) + ((cc ^ (lane & 7)) << 4)) =
+          const int col16 = (half * SC) / 8 + c * 4 + ch; // 16-byte chunk index inside the row
+          const int cc = col16 & 7;
+          *reinterpret_cast<uint4 *>(prow + (col16 >> 3) * (BQ * 128) + ((cc ^ (lane & 7)) << 4)) =
               make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
         }
       }
       tc_fence_before();
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_empty[b]);
+      if (lane == 0)
         mbar_arrive(&p_full[b]);
-      }
       const float alpha = exp2f((m_run - m_use) * L2E); // first tile: exp2(-inf) = 0
-      l_run = l_run * alpha + sum;
+      l_run = l_run * alpha + (sum0 + sum1);
       m_run = m_use;
       if (j > 0) {
         if (!consume_o(j - 1, alpha_pending)) {
@@ -377,7 +417,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       // full row sum = the pair's partial sums (every P·V has completed: xchg is idle)
       xl[half * BQ + row] = l_run;
       ok = pair_sync(&xend[q * 2 + 0], 0);
-      const float l_all = ok ? l_run + xl[(half ^ 1) * BQ + row] : 1.f;
+      float l_all = 0.f;
+#pragma unroll
+      for (int pt = 0; pt < ATT_PARTS; ++pt)
+        l_all += xl[pt * BQ + row];
+      if (!ok)
+        l_all = 1.f;
       // normalise and stage this thread's D/2 columns in the (now idle) P buffer
       const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
       uint8_t *orow = sP + row * 128;
