@@ -6,8 +6,11 @@
 // reference runs as five full passes over a [B·H·T, B·H·T] matrix (two of them
 // on the host). Only the row's own head block is ever touched here.
 //
-// One CTA = one (head, 128-query tile); 320 threads:
-//   warp 0    TMA producer: Q once, then K/V tiles of 128 keys through a ring.
+// Persistent: one CTA per SM walks (head, 128-query tile) works, heavy and light query
+// tiles paired so that every CTA sees the same number of key tiles; the rings run on
+// across works, so the next work's loads and first Q·K' overlap this work's epilogue.
+// 320 threads:
+//   warp 0    TMA producer: Q per work, K and V tiles of 128 keys through two rings.
 //   warp 1    tcgen05.mma issuer: S_j = Q·K_j' (M=128,N=128) into a double-
 //             buffered TMEM S tile, O_j = P_j·V_j (M=128,N=D) into a double-
 //             buffered TMEM O tile.
@@ -89,18 +92,38 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
   uint64_t *o_empty = o_full + 2;
   uint64_t *xbar = o_empty + 2; // [quarter][tile parity]: paired softmax warps
   uint64_t *xend = xbar + 8;    // [quarter][0: row sums, 1: output staged]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(xend + 8);
+  uint64_t *q_empty = xend + 8;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(q_empty + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh = blockIdx.y;
-  // heavy (late) query tiles first: under the causal mask tile i has i+1 key tiles
-  const int qt = prm.n_qtiles - 1 - static_cast<int>(blockIdx.x);
-  const int q0 = qt * BQ;
-  const int kv_len = prm.causal ? min(prm.T, q0 + BQ) : prm.T;
-  const int nk = (kv_len + BKV - 1) / BKV;
+  // Persistent CTA: it walks "items" blockIdx.x, blockIdx.x + gridDim.x, ...; an item is one
+  // head with a PAIR of query tiles (p-th from the end, then p-th from the start), so that under
+  // the causal mask every item has the same number of key tiles (n_qtiles + 1) and the CTAs stay
+  // balanced. Consecutive items are the pairs of one head: CTAs running side by side share its
+  // K/V through L2. All three roles enumerate the same sequence with this helper; pipeline
+  // counters (key tiles, works) run on across works so loads and Q·K' of the next work overlap
+  // the epilogue of the current one.
+  const int n_pairs = (prm.n_qtiles + 1) / 2;
+  const long long n_items = 1ll * prm.BH * n_pairs;
+  struct Work {
+    int bh, q0, nk;
+  };
+  auto get_work = [&](long long item, int second, Work &wk) -> bool {
+    const int pr = static_cast<int>(item % n_pairs);
+    const int heavy = prm.n_qtiles - 1 - pr;
+    if (second && pr == heavy)
+      return false; // middle tile of an odd count: it has no partner
+    const int qt = second ? pr : heavy;
+    wk.bh = static_cast<int>(item / n_pairs);
+    wk.q0 = qt * BQ;
+    const int kv_len = prm.causal ? min(prm.T, wk.q0 + BQ) : prm.T;
+    wk.nk = (kv_len + BKV - 1) / BKV;
+    return true;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
@@ -137,49 +160,64 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
-#pragma unroll
-      for (int db = 0; db < DB; ++db)
-        tma_load_3d(sQ + db * (BQ * 128), &tmQ, q_full, db * 64, q0, bh);
       bool ok = true;
-      for (int j = 0; j < nk && ok; ++j) {
-        const int stage = j % STAGES;
-        if (!mbar_wait(&k_empty[stage], ((j / STAGES) & 1) ^ 1)) {
-          atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
-          ok = false;
-          break;
-        }
-        uint8_t *sK = sKV + stage * Cfg::KV_STAGE;
-        uint8_t *sV = sK + Cfg::K_BYTES;
-        mbar_arrive_expect_tx(&k_full[stage], Cfg::K_BYTES);
-        const int k0 = j * BKV;
-        if (LITERAL) {
-          // K' tile = rows d, columns bh*T + k0.. of the [D, N] view: [dbox][nbox][64 x 128 B]
+      uint32_t kt = 0, w = 0; // key tiles and works issued so far
+      for (long long item = blockIdx.x; item < n_items && ok; item += gridDim.x)
+        for (int second = 0; second < 2 && ok; ++second) {
+          Work wk;
+          if (!get_work(item, second, wk))
+            continue;
+          // Q is single-buffered: the last Q·K' of the previous work must have read it
+          if (!mbar_wait(q_empty, (w & 1) ^ 1)) {
+            atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
 #pragma unroll
           for (int db = 0; db < DB; ++db)
+            tma_load_3d(sQ + db * (BQ * 128), &tmQ, q_full, db * 64, wk.q0, wk.bh);
+          ++w;
+          for (int j = 0; j < wk.nk; ++j, ++kt) {
+            const int stage = kt % STAGES;
+            const uint32_t par = ((kt / STAGES) & 1) ^ 1;
+            if (!mbar_wait(&k_empty[stage], par)) {
+              atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
+              ok = false;
+              break;
+            }
+            uint8_t *sK = sKV + stage * Cfg::KV_STAGE;
+            uint8_t *sV = sK + Cfg::K_BYTES;
+            mbar_arrive_expect_tx(&k_full[stage], Cfg::K_BYTES);
+            const int k0 = j * BKV;
+            if (LITERAL) {
+              // K' tile = rows d, columns bh*T + k0.. of the [D, N] view: [dbox][nbox][64 x 128 B]
 #pragma unroll
-            for (int nb = 0; nb < 2; ++nb)
-              tma_load_3d(sK + (db * 2 + nb) * 8192, &tmK, &k_full[stage],
-                          bh * prm.T + k0 + nb * 64, db * 64, 0);
-        } else {
+              for (int db = 0; db < DB; ++db)
 #pragma unroll
-          for (int db = 0; db < DB; ++db)
-            tma_load_3d(sK + db * (BKV * 128), &tmK, &k_full[stage], db * 64, k0, bh);
+                for (int nb = 0; nb < 2; ++nb)
+                  tma_load_3d(sK + (db * 2 + nb) * 8192, &tmK, &k_full[stage],
+                              wk.bh * prm.T + k0 + nb * 64, db * 64, 0);
+            } else {
+#pragma unroll
+              for (int db = 0; db < DB; ++db)
+                tma_load_3d(sK + db * (BKV * 128), &tmK, &k_full[stage], db * 64, k0, wk.bh);
+            }
+            if (!mbar_wait(&v_empty[stage], par)) {
+              atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
+              ok = false;
+              break;
+            }
+            mbar_arrive_expect_tx(&v_full[stage], Cfg::V_BYTES);
+            // V tile as MN-major B operand: [keybox][dbox][64 keys x 128 B]
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+              for (int db = 0; db < DB; ++db)
+                tma_load_3d(sV + (kb * DB + db) * 8192, &tmV, &v_full[stage], db * 64,
+                            k0 + kb * 64, wk.bh);
+          }
         }
-        if (!mbar_wait(&v_empty[stage], ((j / STAGES) & 1) ^ 1)) {
-          atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
-          ok = false;
-          break;
-        }
-        mbar_arrive_expect_tx(&v_full[stage], Cfg::V_BYTES);
-        // V tile as MN-major B operand: [keybox][dbox][64 keys x 128 B]
-#pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-          for (int db = 0; db < DB; ++db)
-            tma_load_3d(sV + (kb * DB + db) * 8192, &tmV, &v_full[stage], db * 64,
-                        k0 + kb * 64, bh);
-      }
       if (!ok)
         for (int i = 0; i < 64; ++i)
           __nanosleep(1000);
@@ -190,13 +228,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(1u, 0u, LITERAL ? 1u : 0u, BQ, BKV);
       constexpr uint32_t idesc_pv = make_idesc(1u, 0u, 1u, BQ, D);
-      bool ok = mbar_wait(q_full, 0);
-      if (!ok)
-        atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
       const uint32_t q_addr = smem_u32(sQ);
-      auto issue_pv = [&](int i) -> bool {
+      bool ok = true;
+      uint32_t t = 0, w = 0; // key tiles and works issued so far (they index every ring)
+      // P·V of tile number i (global count): needs its V tile, the probabilities and a free O buffer
+      auto issue_pv = [&](uint32_t i) -> bool {
         const int b = i & 1;
-        const uint32_t par = static_cast<uint32_t>(i >> 1) & 1;
+        const uint32_t par = (i >> 1) & 1;
         if (!mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1) || !mbar_wait(&p_full[b], par) ||
             !mbar_wait(&o_empty[b], par ^ 1))
           return false;
@@ -213,33 +251,49 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         umma_commit(&v_empty[i % STAGES]);
         return true;
       };
-      for (int j = 0; j < nk && ok; ++j) {
-        const int stage = j % STAGES, b = j & 1;
-        if (!mbar_wait(&k_full[stage], (j / STAGES) & 1) ||
-            !mbar_wait(&s_empty[b], ((j >> 1) & 1) ^ 1)) {
-          atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(sKV + stage * Cfg::KV_STAGE);
+      for (long long item = blockIdx.x; item < n_items && ok; item += gridDim.x)
+        for (int second = 0; second < 2 && ok; ++second) {
+          Work wk;
+          if (!get_work(item, second, wk))
+            continue;
+          if (!mbar_wait(q_full, w & 1)) {
+            atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          ++w;
+          for (int j = 0; j < wk.nk && ok; ++j, ++t) {
+            const int stage = t % STAGES, b = t & 1;
+            if (!mbar_wait(&k_full[stage], (t / STAGES) & 1) ||
+                !mbar_wait(&s_empty[b], ((t >> 1) & 1) ^ 1)) {
+              atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t k_addr = smem_u32(sKV + stage * Cfg::KV_STAGE);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t ad = make_smem_desc(q_addr + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
-          const uint64_t bd =
-              LITERAL ? make_smem_desc(k_addr + (k / 4) * (2 * 8192) + (k % 4) * 2048, 8192, 1024)
-                      : make_smem_desc(k_addr + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
-          umma_f16(tmem_S + b * BKV, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
+            for (int k = 0; k < D / 16; ++k) {
+              const uint64_t ad = make_smem_desc(q_addr + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
+              const uint64_t bd =
+                  LITERAL ? make_smem_desc(k_addr + (k / 4) * (2 * 8192) + (k % 4) * 2048, 8192, 1024)
+                          : make_smem_desc(k_addr + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
+              umma_f16(tmem_S + b * BKV, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
+            }
+            umma_commit(&s_full[b]);
+            umma_commit(&k_empty[stage]);
+            if (j == wk.nk - 1)
+              umma_commit(q_empty); // the producer may fetch the next work's Q
+            if (j > 0 && !issue_pv(t - 1)) {
+              atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+              ok = false;
+            }
+          }
+          if (ok && !issue_pv(t - 1)) {
+            atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+            ok = false;
+          }
         }
-        umma_commit(&s_full[b]);
-        umma_commit(&k_empty[stage]);
-        if (j > 0 && !issue_pv(j - 1)) {
-          atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
-          ok = false;
-        }
-      }
-      if (ok && nk > 0 && !issue_pv(nk - 1))
-        atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
     }
     __syncwarp();
   } else {
@@ -251,7 +305,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
     const int q = warp & 3;
     const int half = (warp - 2) >> 2; // which 1/PARTS of the columns
     const int row = q * 32 + lane;       // row inside the query tile = TMEM lane
-    const int qrow = q0 + row;           // position in the sequence
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     const float scale_b = bf16_round(prm.scale);
     constexpr float L2E = 1.4426950408889634f;
@@ -259,12 +312,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
     constexpr int DH = D / ATT_PARTS;   // output columns per thread
     uint16_t *xm = reinterpret_cast<uint16_t *>(xchg); // [tile parity][half][row] partial maxima (bf16)
     float *xl = reinterpret_cast<float *>(xchg);       // [half][row] partial row sums (end only)
-    float m_run = -INFINITY, l_run = 0.f, alpha_pending = 1.f;
     float o_acc[DH];
-#pragma unroll
-    for (int i = 0; i < DH; ++i)
-      o_acc[i] = 0.f;
     bool ok = true;
+    bool store_pending = false; // this thread issued the previous work's output store
+    uint32_t t = 0, w = 0;      // key tiles and works consumed so far
 
     auto pair_sync = [&](uint64_t *bar, uint32_t parity) -> bool {
       __syncwarp();
@@ -273,9 +324,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       return mbar_wait(bar, parity);
     };
 
-    auto consume_o = [&](int i, float a) -> bool {
+    auto consume_o = [&](uint32_t i, float a) -> bool {
       const int b = i & 1;
-      if (!mbar_wait(&o_full[b], static_cast<uint32_t>(i >> 1) & 1))
+      if (!mbar_wait(&o_full[b], (i >> 1) & 1))
         return false;
       tc_fence_after();
       if constexpr (DH % 32 == 0) {
@@ -304,9 +355,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       return true;
     };
 
-    for (int j = 0; j < nk && ok; ++j) {
-      const int b = j & 1;
-      if (!mbar_wait(&s_full[b], static_cast<uint32_t>(j >> 1) & 1)) {
+    for (long long item = blockIdx.x; item < n_items && ok; item += gridDim.x)
+    for (int second = 0; second < 2 && ok; ++second) {
+    Work wk;
+    if (!get_work(item, second, wk))
+      continue;
+    const int q0 = wk.q0, nk = wk.nk, bh = wk.bh;
+    const int qrow = q0 + row; // position in the sequence
+    float m_run = -INFINITY, l_run = 0.f, alpha_pending = 1.f;
+#pragma unroll
+    for (int i = 0; i < DH; ++i)
+      o_acc[i] = 0.f;
+    for (int j = 0; j < nk && ok; ++j, ++t) {
+      const int b = t & 1;
+      if (!mbar_wait(&s_full[b], (t >> 1) & 1)) {
         atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
         ok = false;
         break;
@@ -354,7 +416,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       const float raw_mx = fmaxf(bf16_lo(mx2), bf16_hi(mx2));
       const float mine = bf16_round(raw_mx * scale_b); // exactly a bf16 value (or -inf)
       xm[(b * ATT_PARTS + half) * BQ + row] = static_cast<uint16_t>(__float_as_uint(mine) >> 16);
-      if (!pair_sync(&xbar[q * 2 + b], static_cast<uint32_t>(j >> 1) & 1)) {
+      if (store_pending) {
+        // The previous work's output was staged in the P buffers; its store must have read them
+        // before anyone of this row quarter (all behind the barrier below) writes P again.
+        bulk_wait_read<0>();
+        store_pending = false;
+      }
+      if (!pair_sync(&xbar[q * 2 + b], (t >> 1) & 1)) {
         atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
         ok = false;
         break;
@@ -401,7 +469,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       l_run = l_run * alpha + (sum0 + sum1);
       m_run = m_use;
       if (j > 0) {
-        if (!consume_o(j - 1, alpha_pending)) {
+        if (!consume_o(t - 1, alpha_pending)) {
           atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
           ok = false;
           break;
@@ -409,14 +477,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       }
       alpha_pending = alpha;
     }
-    if (ok && nk > 0 && !consume_o(nk - 1, alpha_pending)) {
+    if (ok && !consume_o(t - 1, alpha_pending)) {
       atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
       ok = false;
     }
     if (ok) {
       // full row sum = the pair's partial sums (every P·V has completed: xchg is idle)
       xl[half * BQ + row] = l_run;
-      ok = pair_sync(&xend[q * 2 + 0], 0);
+      ok = pair_sync(&xend[q * 2 + 0], w & 1);
       float l_all = 0.f;
 #pragma unroll
       for (int pt = 0; pt < ATT_PARTS; ++pt)
@@ -430,16 +498,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       for (int i = 0; i < DH / 8; ++i) {
         const int gc = (half * DH) / 8 + i;
         const int box = gc >> 3, cc = gc & 7;
-        uint32_t w[4];
+        uint32_t ow[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          w[k] = pack_bf16x2(o_acc[i * 8 + 2 * k] * inv, o_acc[i * 8 + 2 * k + 1] * inv);
+          ow[k] = pack_bf16x2(o_acc[i * 8 + 2 * k] * inv, o_acc[i * 8 + 2 * k + 1] * inv);
         *reinterpret_cast<uint4 *>(orow + box * (BQ * 128) + ((cc ^ (lane & 7)) << 4)) =
-            make_uint4(w[0], w[1], w[2], w[3]);
+            make_uint4(ow[0], ow[1], ow[2], ow[3]);
       }
       fence_proxy_async();
       if (ok)
-        ok = pair_sync(&xend[q * 2 + 1], 0);
+        ok = pair_sync(&xend[q * 2 + 1], w & 1);
       if (!ok)
         atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
       if (ok && half == 0 && lane == 0 && q0 + q * 32 < prm.T) {
@@ -448,9 +516,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         for (int db = 0; db < DB; ++db)
           tma_store_5d(&tmO, sP + db * (BQ * 128) + q * 32 * 128, db * 64, hh, q0 + q * 32, bb, 0);
         bulk_commit();
-        bulk_wait<0>();
+        store_pending = true;
       }
     }
+    ++w;
+    } // works
+    if (store_pending)
+      bulk_wait<0>(); // shared memory must outlive the last store
   }
 
   tc_fence_before();
@@ -510,7 +582,7 @@ int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *
   if (literal && (T % 8))
     return 1; // column offset bh*T must stay 16-byte aligned
   const unsigned long long BH = 1ull * B * H, uT = T, uD = D, Ntot = BH * uT, E = 1ull * H * D;
-  if (BH > 65535 || Ntot > 0x7fffffffull)
+  if (Ntot > 0x7fffffffull)
     return 1;
   CUtensorMap tmQ, tmK, tmV, tmO;
   {
@@ -543,7 +615,13 @@ int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *
   prm.T = T, prm.H = H, prm.BH = static_cast<int>(BH), prm.causal = causal;
   prm.scale = 1.0f / sqrtf(static_cast<float>(D));
   prm.n_qtiles = (T + BQ - 1) / BQ;
-  dim3 grid(prm.n_qtiles, static_cast<unsigned>(BH));
+  // one persistent CTA per SM (the kernel's shared memory allows no more), fewer for small jobs
+  int dev = 0, num_sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
+    return 2;
+  const unsigned long long n_items = BH * ((prm.n_qtiles + 1) / 2);
+  dim3 grid(static_cast<unsigned>(n_items < static_cast<unsigned long long>(num_sms) ? n_items : num_sms));
 
 #define MU_ATT_LAUNCH(D_, L_)                                                                    \
   do {                                                                                           \
