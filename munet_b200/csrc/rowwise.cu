@@ -410,6 +410,64 @@ argmax_kernel(const T *__restrict__ x, int *__restrict__ idx, long long rows, in
     idx[row] = bi;
 }
 
+// bf16 rows whose length is a multiple of 8: 16-byte streaming loads, four in flight per lane,
+// and a packed maximum (one instruction per two values). The index is only searched for when a
+// lane's chunk beats its running maximum, which happens O(log n) times per lane. Same answer as
+// argmax_kernel: the smallest index of the maximum.
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+argmax_bf16_vec_kernel(const __nv_bfloat16 *__restrict__ x, int *__restrict__ idx, long long rows,
+                       int cols) {
+  const int lane = threadIdx.x & 31;
+  const long long row = 1ll * blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  if (row >= rows)
+    return;
+  const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * cols);
+  const int nvec = cols / 8;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int v0 = lane; v0 < nvec; v0 += 128) {
+    uint4 qv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int vi = v0 + 32 * u;
+      qv[u] = vi < nvec ? __ldcs(xr + vi) : make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);
+    }
+    uint32_t m2 = 0xFF80FF80u;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      m2 = bf16x2_max(m2, bf16x2_max(bf16x2_max(qv[u].x, qv[u].y), bf16x2_max(qv[u].z, qv[u].w)));
+    const float cm = fmaxf(bf16_lo(m2), bf16_hi(m2));
+    if (cm > best) {
+      best = cm;
+      int found = 0x7fffffff;
+#pragma unroll
+      for (int u = 3; u >= 0; --u) { // descending, so the smallest index is written last
+        const uint32_t w[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
+#pragma unroll
+        for (int k = 3; k >= 0; --k) {
+          const int base = (v0 + 32 * u) * 8 + 2 * k;
+          if (bf16_hi(w[k]) == cm)
+            found = base + 1;
+          if (bf16_lo(w[k]) == cm)
+            found = base;
+        }
+      }
+      bi = found;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (lane == 0)
+    idx[row] = bi == 0x7fffffff ? 0 : bi; // every value was -inf (or NaN): the first index
+}
+
 // ---------------------------------------------------------------------------
 // Host launchers
 // ---------------------------------------------------------------------------
@@ -528,6 +586,9 @@ int launch_argmax(const void *x, int *idx, long long rows, int cols, int dtype, 
     return 0;
   if (dtype == F32)
     argmax_kernel<float><<<row_blocks(rows), ROW_WARPS * 32, 0, st>>>((const float *)x, idx, rows, cols);
+  else if (dtype == BF16 && cols % 8 == 0 && al16(x))
+    argmax_bf16_vec_kernel<<<row_blocks(rows), ROW_WARPS * 32, 0, st>>>((const __nv_bfloat16 *)x, idx,
+                                                                      rows, cols);
   else if (dtype == BF16)
     argmax_kernel<__nv_bfloat16><<<row_blocks(rows), ROW_WARPS * 32, 0, st>>>(
         (const __nv_bfloat16 *)x, idx, rows, cols);

@@ -5,6 +5,8 @@ the command to put under a profiler.
     python -m munet_b200.kernel_case attention B H T D [--kmode 0|1] [--non-causal] [--reps 5]
     python -m munet_b200.kernel_case layer_norm ROWS COLS [--reps 5]
     python -m munet_b200.kernel_case softmax ROWS COLS [--reps 5]
+    python -m munet_b200.kernel_case argmax ROWS COLS [--reps 5]
+    python -m munet_b200.kernel_case eltwise ROWS COLS [--act gelu] [--residual] [--reps 5]
 
 Operands are random bf16 tensors (torch is used for allocation and CUDA events only).
 Prints mean milliseconds over ``--reps`` launches after two warm-up launches, with the
@@ -34,7 +36,7 @@ def timed(fn, reps):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["linear", "attention", "layer_norm", "softmax"])
+    ap.add_argument("kernel", choices=["linear", "attention", "layer_norm", "softmax", "argmax", "eltwise"])
     ap.add_argument("dims", type=int, nargs="+")
     ap.add_argument("--act", default="none")
     ap.add_argument("--no-bias", action="store_true")
@@ -67,6 +69,22 @@ def main():
         fl = (2.0 if causal else 4.0) * B * H * T * T * D
         print(f"attention B{B} H{H} T{T} D{D} kmode={a.kmode} causal={causal}: {ms:.4f} ms  "
               f"{fl / ms / 1e9:.1f} TFLOP/s ({'causal-useful' if causal else 'full'})")
+    elif a.kernel == "argmax":
+        rows, cols = a.dims
+        x = torch.randn(rows, cols, device="cuda").bfloat16()
+        idx = torch.empty(rows, dtype=torch.int32, device="cuda")
+        ms = timed(lambda: ctx.argmax(x, idx, rows, cols, mb.BF16), a.reps)
+        print(f"argmax {rows}x{cols}: {ms:.4f} ms  {(rows * cols * 2 + rows * 4) / ms / 1e6:.0f} GB/s")
+    elif a.kernel == "eltwise":
+        rows, cols = a.dims
+        x = torch.randn(rows, cols, device="cuda").bfloat16()
+        y = torch.empty_like(x)
+        bias = torch.zeros(cols, **bf)
+        res = torch.randn(rows, cols, device="cuda").bfloat16() if a.residual else None
+        ms = timed(lambda: ctx.eltwise(x, y, rows * cols, mb.BF16, act=a.act, bias=bias, cols=cols,
+                                       residual=res), a.reps)
+        nb = (3 if a.residual else 2) * rows * cols * 2
+        print(f"eltwise {rows}x{cols} act={a.act} residual={a.residual}: {ms:.4f} ms  {nb / ms / 1e6:.0f} GB/s")
     else:
         rows, cols = a.dims
         x = torch.randn(rows, cols, device="cuda").bfloat16()

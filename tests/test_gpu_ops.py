@@ -196,6 +196,26 @@ def test_argmax_first_max(ctx, dtype):
     assert np.array_equal(to_host(idx), want) and want[3] == 10
 
 
+@pytest.mark.parametrize("rows,cols", [(37, 32000), (5, 8), (9, 1000), (300, 1032), (4, 1001)])
+def test_argmax_bf16_ties(ctx, rows, cols):
+    """bf16 logits quantised coarsely: most rows hold their maximum several times, and the
+    smallest index must win on every one of them (vector path for widths divisible by 8)."""
+    rng = np.random.default_rng(rows * 7 + cols)
+    xf = np.round(rng.standard_normal((rows, cols)) * 4).astype(np.float32) / 4
+    xf[0, :] = -np.inf          # nothing beats -inf: index 0
+    if rows > 2:
+        xf[1, :] = 0.0
+        xf[1, cols // 2] = -0.0  # signed zeros compare equal
+        xf[2, cols - 1] = 1000.0
+    x = oracle.to_bf16(xf)
+    idx = empty_dev((rows,), I32)
+    ctx.argmax(to_dev(x, BF16), idx, rows, cols, BF16)
+    ctx.check()
+    want = np.argmax(oracle.as_float(x, BF16), axis=-1).astype(np.int32)
+    assert np.array_equal(oracle.port().argmax(x, BF16), want)
+    assert np.array_equal(to_host(idx), want)
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("kmode", [oracle.K_LITERAL, oracle.K_MATH])
 @pytest.mark.parametrize("causal", [True, False])
