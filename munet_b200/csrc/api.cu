@@ -16,6 +16,8 @@ int launch_gemm_simt(const SimtArgs &, cudaStream_t);
 int launch_layer_norm(const void *, const void *, const void *, void *, long long, int, float, int, int *, int,
                       cudaStream_t);
 int launch_softmax(const void *, void *, long long, int, float, int, int, int, cudaStream_t);
+int launch_softmax_bf16_rows(const void *, void *, long long, int, float, int, int, int *, int,
+                             cudaStream_t);
 int launch_embedding(const int *, const void *, const void *, void *, long long, int, int, int, int,
                      int *, cudaStream_t);
 int launch_eltwise(const void *, const void *, const void *, void *, long long, int, int, int, int,
@@ -464,7 +466,12 @@ int mu_softmax(mu_ctx *ctx, const void *x, void *y, long long rows, int cols, in
   MU_REQUIRE(x && y, "Softmax: null pointer");
   if (!set_device(ctx))
     return fail(ctx, MU_ERR_CUDA, "Softmax: cannot select device");
-  int rc = mu::launch_softmax(x, y, rows, cols, 1.0f, 0, 0, dtype, static_cast<cudaStream_t>(stream));
+  int rc = 1;
+  if (dtype == MU_BF16) // model widths: persistent kernel on a shared-memory ring
+    rc = mu::launch_softmax_bf16_rows(x, y, rows, cols, 1.0f, 0, 0, ctx->d_status, ctx->num_sms,
+                                      static_cast<cudaStream_t>(stream));
+  if (rc == 1)
+    rc = mu::launch_softmax(x, y, rows, cols, 1.0f, 0, 0, dtype, static_cast<cudaStream_t>(stream));
   if (rc == 1)
     return fail(ctx, MU_ERR_UNSUPPORTED, "Softmax: dtype %d not implemented", dtype);
   return rc ? cuda_fail(ctx, "Softmax", cudaGetLastError()) : MU_OK;

@@ -9,6 +9,7 @@
 // gamma and beta sit in shared memory once per block.
 #include "common.h"
 #include "ptx.cuh"
+#include <cfloat>
 
 namespace mu {
 
@@ -139,6 +140,155 @@ layer_norm_bf16_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bflo
       stage = 0;
       parity ^= 1u;
     }
+  }
+}
+
+// Row softmax on the same ring (arithmetic of softmax_kernel in rowwise.cu: scale first, optional
+// bf16 rounding of the scaled value, maximum, exp, sum, divide; causal_T > 0 limits row r to its
+// first r % causal_T + 1 columns and writes exact zeros behind them).
+template <int VPL>
+__global__ void __launch_bounds__(LN_WARPS * 32, 1)
+softmax_bf16_rows_kernel(const __nv_bfloat16 *__restrict__ x, __nv_bfloat16 *__restrict__ y,
+                         long long rows, float scale, int causal_T, int round_scaled, int *status) {
+  using Cfg = LnCfg<VPL>;
+  constexpr int COLS = Cfg::COLS, ROW_BYTES = Cfg::ROW_BYTES, STAGES = Cfg::STAGES;
+  extern __shared__ __align__(128) unsigned char ln_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned char *ring = ln_smem + 2 * ROW_BYTES + warp * STAGES * ROW_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(ln_smem + 2 * ROW_BYTES + LN_WARPS * STAGES * ROW_BYTES) +
+                   warp * STAGES;
+  if (lane == 0) {
+    for (int s = 0; s < STAGES; ++s)
+      mbar_init(&bars[s], 1);
+    fence_barrier_init();
+  }
+  __syncwarp();
+  const long long stride = 1ll * gridDim.x * LN_WARPS;
+  const long long first = 1ll * blockIdx.x * LN_WARPS + warp;
+  if (lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      const long long r = first + s * stride;
+      if (r < rows) {
+        mbar_arrive_expect_tx(&bars[s], ROW_BYTES);
+        bulk_load(ring + s * ROW_BYTES, x + r * COLS, ROW_BYTES, &bars[s]);
+      }
+    }
+  }
+  int stage = 0;
+  uint32_t parity = 0;
+  for (long long row = first; row < rows; row += stride) {
+    if (!mbar_wait(&bars[stage], parity)) {
+      if (lane == 0)
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_OTHER);
+      for (int k = 1; k < STAGES; ++k) {
+        if (row + k * stride >= rows)
+          break;
+        if (++stage == STAGES) {
+          stage = 0;
+          parity ^= 1u;
+        }
+        if (!mbar_wait(&bars[stage], parity))
+          break;
+      }
+      return;
+    }
+    const uint4 *buf = reinterpret_cast<const uint4 *>(ring + stage * ROW_BYTES);
+    uint4 cur[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+      cur[i] = buf[lane + i * 32];
+    __syncwarp();
+    if (lane == 0) {
+      const long long r = row + STAGES * stride;
+      if (r < rows) {
+        mbar_arrive_expect_tx(&bars[stage], ROW_BYTES);
+        bulk_load(ring + stage * ROW_BYTES, x + r * COLS, ROW_BYTES, &bars[stage]);
+      }
+    }
+    const int valid = causal_T > 0 ? static_cast<int>(row % causal_T) + 1 : COLS;
+    float p[VPL * 8];
+    float mx = -FLT_MAX;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const uint32_t w[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+      const int c0 = (lane + i * 32) * 8;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float t0 = bf16_lo(w[k]) * scale, t1 = bf16_hi(w[k]) * scale;
+        if (round_scaled) {
+          const uint32_t u = pack_bf16x2(t0, t1);
+          t0 = bf16_lo(u), t1 = bf16_hi(u);
+        }
+        p[i * 8 + 2 * k] = t0, p[i * 8 + 2 * k + 1] = t1;
+        if (c0 + 2 * k < valid)
+          mx = fmaxf(mx, t0);
+        if (c0 + 2 * k + 1 < valid)
+          mx = fmaxf(mx, t1);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c0 = (lane + i * 32) * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float v = (c0 + e < valid) ? __expf(p[i * 8 + e] - mx) : 0.f;
+        p[i * 8 + e] = v;
+        s += v;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float inv = 1.0f / s;
+    uint4 *yr = reinterpret_cast<uint4 *>(y + row * COLS);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        o[k] = pack_bf16x2(p[i * 8 + 2 * k] * inv, p[i * 8 + 2 * k + 1] * inv);
+      __stcs(&yr[lane + i * 32], make_uint4(o[0], o[1], o[2], o[3]));
+    }
+    if (++stage == STAGES) {
+      stage = 0;
+      parity ^= 1u;
+    }
+  }
+}
+
+template <int VPL>
+static int sm_launch(const __nv_bfloat16 *x, __nv_bfloat16 *y, long long rows, float scale, int causal_T,
+                     int round_scaled, int *status, unsigned blocks, cudaStream_t st) {
+  auto kern = softmax_bf16_rows_kernel<VPL>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LnCfg<VPL>::SMEM) !=
+      cudaSuccess)
+    return 2;
+  kern<<<blocks, LN_WARPS * 32, LnCfg<VPL>::SMEM, st>>>(x, y, rows, scale, causal_T, round_scaled, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// Returns 0 launched, 1 shape not covered here (caller uses the generic kernel), 2 failure.
+int launch_softmax_bf16_rows(const void *x, void *y, long long rows, int cols, float scale, int causal_T,
+                             int round_scaled, int *status, int num_sms, cudaStream_t st) {
+  auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!al(x) || !al(y) || rows <= 0 || num_sms <= 0 || status == nullptr)
+    return 1;
+  long long blocks = (rows + LN_WARPS - 1) / LN_WARPS;
+  if (blocks > num_sms)
+    blocks = num_sms;
+  const auto *xp = static_cast<const __nv_bfloat16 *>(x);
+  auto *yp = static_cast<__nv_bfloat16 *>(y);
+  const unsigned nb = static_cast<unsigned>(blocks);
+  switch (cols) {
+  case 256: return sm_launch<1>(xp, yp, rows, scale, causal_T, round_scaled, status, nb, st);
+  case 512: return sm_launch<2>(xp, yp, rows, scale, causal_T, round_scaled, status, nb, st);
+  case 1024: return sm_launch<4>(xp, yp, rows, scale, causal_T, round_scaled, status, nb, st);
+  case 2048: return sm_launch<8>(xp, yp, rows, scale, causal_T, round_scaled, status, nb, st);
+  default: return 1;
   }
 }
 

@@ -12,6 +12,7 @@
 //   GELU/Tanh  src/nn/activations.hpp:20-38 (compositions of mul/sigmoid)
 #include "common.h"
 #include "ptx.cuh"
+#include "epilogue_math.cuh"
 #include <cfloat>
 
 namespace mu {
@@ -377,6 +378,40 @@ eltwise_kernel(const T *__restrict__ x, const T *__restrict__ bias, const T *__r
   }
 }
 
+// bf16 fast path of the chain above: activation fixed at compile time, pair arithmetic with
+// packed converts (epilogue_math.cuh, the same code the GEMM epilogue runs), two 16-byte
+// vectors per thread in flight.
+template <int ACT>
+__global__ void __launch_bounds__(256)
+eltwise_bf16_vec_kernel(const uint4 *__restrict__ x, const __nv_bfloat16 *__restrict__ bias,
+                        const uint4 *__restrict__ res, uint4 *__restrict__ y, long long nv, int cols) {
+  const long long stride = 1ll * gridDim.x * blockDim.x;
+  const bool hb = bias != nullptr, hr = res != nullptr;
+  auto one = [&](long long i, uint4 xv, uint4 rv) {
+    uint4 bv = make_uint4(0, 0, 0, 0);
+    if (hb)
+      bv = __ldg(reinterpret_cast<const uint4 *>(bias + (i * 8) % cols));
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w},
+                   rw[4] = {rv.x, rv.y, rv.z, rv.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      ow[k] = epi_pair<ACT, false>(bf16_lo(xw[k]), bf16_hi(xw[k]), bf16_lo(bw[k]), bf16_hi(bw[k]),
+                                   bf16_lo(rw[k]), bf16_hi(rw[k]), 1.0f, false, hb, hr, true);
+    __stcs(y + i, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+  };
+  for (long long i = 1ll * blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += 2 * stride) {
+    const long long i2 = i + stride;
+    const bool two = i2 < nv;
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    const uint4 xa = __ldcs(x + i), xb = two ? __ldcs(x + i2) : z;
+    const uint4 ra = hr ? __ldcs(res + i) : z, rb = (hr && two) ? __ldcs(res + i2) : z;
+    one(i, xa, ra);
+    if (two)
+      one(i2, xb, rb);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // argmax over the last dim, first maximum wins (np.argmax rule). Warp per row.
 // ---------------------------------------------------------------------------
@@ -555,6 +590,30 @@ static int elt_t(const void *x, const void *bias, const void *res, void *y, long
                  int act, int num_sms, cudaStream_t st) {
   const bool vec = (n % Vec<T>::N == 0) && (cols % Vec<T>::N == 0) && al16(x) && al16(y) &&
                    (!bias || al16(bias)) && (!res || al16(res));
+  if constexpr (sizeof(T) == 2) {
+    if (vec) {
+      const long long nv = n / 8;
+      long long nb = (nv + 511) / 512; // two vectors per thread and pass
+      const long long capb = 1ll * num_sms * 8;
+      if (nb > capb)
+        nb = capb;
+      if (nb < 1)
+        nb = 1;
+#define MU_ELT(A)                                                                                  \
+  eltwise_bf16_vec_kernel<A><<<(unsigned)nb, 256, 0, st>>>((const uint4 *)x, (const __nv_bfloat16 *)bias, \
+                                                           (const uint4 *)res, (uint4 *)y, nv, cols)
+      switch (act) {
+      case ACT_NONE: MU_ELT(ACT_NONE); break;
+      case ACT_RELU: MU_ELT(ACT_RELU); break;
+      case ACT_GELU: MU_ELT(ACT_GELU); break;
+      case ACT_SIGMOID: MU_ELT(ACT_SIGMOID); break;
+      case ACT_TANH: MU_ELT(ACT_TANH); break;
+      default: return 1;
+      }
+#undef MU_ELT
+      return cudaGetLastError() == cudaSuccess ? 0 : 2;
+    }
+  }
   const long long work = vec ? n / Vec<T>::N : n;
   long long blocks = (work + 255) / 256;
   const long long cap = 1ll * num_sms * 16;

@@ -125,7 +125,8 @@ def test_layer_norm(ctx, dtype, rows, cols):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("rows,cols", [(64, 256), (100, 1024), (9, 33), (4, 5000)])
+@pytest.mark.parametrize("rows,cols", [(64, 256), (100, 1024), (9, 33), (4, 5000), (3, 512),
+                                       (20011, 2048), (40001, 256)])
 def test_softmax(ctx, dtype, rows, cols):
     rng = np.random.default_rng(rows * cols)
     x = rnd(rng, (rows, cols), dtype, 3.0)
@@ -159,6 +160,26 @@ def test_embedding(ctx, dtype):
     with pytest.raises(mb.MuNetError, match="out of range"):
         ctx.check()
     ctx.check()  # status is cleared after being reported
+
+
+@pytest.mark.parametrize("act", ["none", "relu", "gelu", "sigmoid", "tanh"])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (333, 512), (70001, 64)])
+def test_eltwise_bf16_chain(ctx, act, rows, cols):
+    """bias + activation + residual in one pass (vector path), against the same three ops of the
+    CPU checker applied one after another with its per-op rounding."""
+    rng = np.random.default_rng(rows + cols)
+    x, r = rnd(rng, (rows, cols), BF16, 2.0), rnd(rng, (rows, cols), BF16)
+    b = rnd(rng, (cols,), BF16)
+    y = empty_dev((rows, cols), BF16)
+    ctx.eltwise(to_dev(x, BF16), y, rows * cols, BF16, act=act, bias=to_dev(b, BF16), cols=cols,
+                residual=to_dev(r, BF16))
+    ctx.check()
+    o = oracle.port()
+    want = o.add(x, np.broadcast_to(b, x.shape).copy(), BF16)
+    if act != "none":
+        want = o.activation(want, BF16, act)
+    want = o.add(want, r, BF16)
+    assert_close(to_host(y), want, BF16, what=f"bias+{act}+residual")
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
