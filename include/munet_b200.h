@@ -183,6 +183,64 @@ int mu_binary_broadcast(mu_ctx *ctx, int op, const void *a, const void *b, void 
                         const int *out_shape, const long long *strides_a,
                         const long long *strides_b, int dtype, void *stream);
 
+/* ---- remaining forward entry points of the Backend surface --------------------
+ * float32 and bfloat16 (bfloat16 evaluates in fp32 and rounds once). Shapes of extent 0 are
+ * accepted and do nothing. */
+
+/* BackendElementwiseCapability::exp / log / sqrt / rsqrt / sin / cos
+ * (src/core/backend.hpp:228-233; CPU kernels src/backend/cpu_backend.hpp:533-586). */
+enum mu_unary_op { MU_UN_EXP = 0, MU_UN_LOG = 1, MU_UN_SQRT = 2, MU_UN_RSQRT = 3, MU_UN_SIN = 4,
+                   MU_UN_COS = 5 };
+int mu_unary(mu_ctx *ctx, int op, const void *x, void *y, long long n, int dtype, void *stream);
+
+/* nn::LeakyReLU (src/nn/activations.hpp:76-88): relu(x) + (x - relu(x)) * slope, one pass. */
+int mu_leaky_relu(mu_ctx *ctx, const void *x, void *y, long long n, float slope, int dtype,
+                  void *stream);
+
+/* BackendElementwiseCapability::broadcast_row (src/core/backend.hpp:217-218;
+ * cpu_backend.hpp:1051-1060): out[r, :] = row for r in [0, rows). */
+int mu_broadcast_row(mu_ctx *ctx, const void *row, void *out, long long rows, int cols, int dtype,
+                     void *stream);
+
+/* BackendShapeCapability::concat (src/core/backend.hpp:257-258; cpu_backend.hpp:416-452).
+ * `outer` = product of the dimensions before the concatenation axis, `inner` = product of
+ * those after it, dim_sizes[j] = extent of input j along the axis. At most 8 inputs. */
+int mu_concat(mu_ctx *ctx, const void *const *inputs, const int *dim_sizes, int n_inputs, void *out,
+              long long outer, long long inner, int dtype, void *stream);
+
+/* BackendSpatialCapability::upsample2d (src/core/backend.hpp:300-301; cpu_backend.hpp:889-902):
+ * nearest neighbour, integer scale, NCHW. */
+int mu_upsample2d(mu_ctx *ctx, const void *x, void *y, int B, int C, int H, int W, int scale,
+                  int dtype, void *stream);
+
+/* BackendNormalizationCapability::batch_norm with training=false (src/core/backend.hpp:308-312;
+ * cpu_backend.hpp:957-967): y = gamma[c]*(x - mean[c])*(1/sqrt(var[c] + eps)) + beta[c].
+ * The running statistics are float32 whatever `dtype` is (the reference keeps them in the
+ * accumulation type, src/nn/normalization.hpp:84-98). The training branch is not built. */
+int mu_batch_norm_eval(mu_ctx *ctx, const void *x, const void *gamma, const void *beta,
+                       const float *running_mean, const float *running_var, void *y, int B, int C,
+                       int H, int W, float eps, int dtype, void *stream);
+
+/* nn::RMSNorm (src/nn/normalization.hpp:39-67): x * rsqrt(mean(x*x, last dim) + eps) * weight. */
+int mu_rms_norm(mu_ctx *ctx, const void *x, const void *weight, void *y, long long rows, int cols,
+                float eps, int dtype, void *stream);
+
+/* BackendReductionCapability (src/core/backend.hpp:239-247; cpu_backend.hpp:1040-1049,
+ * 1124-1137, 1084-1122): sum of every element into out[0]; mean over the last dimension;
+ * sum onto a broadcast-compatible smaller shape (output extents are 1 or the input's, aligned
+ * at the trailing dimensions). Accumulation is in double. */
+int mu_sum(mu_ctx *ctx, const void *x, void *out, long long n, int dtype, void *stream);
+int mu_mean_last_dim(mu_ctx *ctx, const void *x, void *out, long long outer, int dim, int dtype,
+                     void *stream);
+int mu_sum_to_shape(mu_ctx *ctx, const void *x, void *out, const int *in_shape, int in_ndim,
+                    const int *out_shape, int out_ndim, int dtype, void *stream);
+
+/* BackendRandomCapability::fill_uniform (src/core/backend.hpp:341-344). The reference's CPU
+ * fill depends on the host's thread count (cpu_backend.hpp:1021-1038), so there are no bits to
+ * match: values are a pure function of (seed, index), uniform in [low, high). */
+int mu_fill_uniform(mu_ctx *ctx, void *out, long long n, float low, float high,
+                    unsigned long long seed, int dtype, void *stream);
+
 /* ---- argmax ---------------------------------------------------------------
  * The reference has no argmax op; its demos take np.argmax of the logits
  * (demos/transformers/decoder_block_demo.py:112). First maximum wins. */

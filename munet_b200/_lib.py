@@ -63,6 +63,17 @@ SIGNATURES = {
     "mu_embedding": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "mu_eltwise": (_i, [_vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp]),
     "mu_argmax": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
+    "mu_unary": (_i, [_vp, _i, _vp, _vp, _ll, _i, _vp]),
+    "mu_leaky_relu": (_i, [_vp, _vp, _vp, _ll, C.c_float, _i, _vp]),
+    "mu_broadcast_row": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
+    "mu_concat": (_i, [_vp, C.POINTER(_vp), C.POINTER(_i), _i, _vp, _ll, _ll, _i, _vp]),
+    "mu_upsample2d": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "mu_batch_norm_eval": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, C.c_float, _i, _vp]),
+    "mu_rms_norm": (_i, [_vp, _vp, _vp, _vp, _ll, _i, C.c_float, _i, _vp]),
+    "mu_sum": (_i, [_vp, _vp, _vp, _ll, _i, _vp]),
+    "mu_mean_last_dim": (_i, [_vp, _vp, _vp, _ll, _i, _i, _vp]),
+    "mu_sum_to_shape": (_i, [_vp, _vp, _vp, C.POINTER(_i), _i, C.POINTER(_i), _i, _i, _vp]),
+    "mu_fill_uniform": (_i, [_vp, _vp, _ll, C.c_float, C.c_float, C.c_ulonglong, _i, _vp]),
     "mu_binary_broadcast": (_i, [_vp, _i, _vp, _vp, _vp, _i, C.POINTER(_i), C.POINTER(_ll),
                                  C.POINTER(_ll), _i, _vp]),
     "mu_comm_unique_id": (_i, [_vp, _sz]),
@@ -237,6 +248,55 @@ class Context:
             self._h, code, _ptr(a), _ptr(b), _ptr(out), n, (C.c_int * max(n, 1))(*out_shape),
             (C.c_longlong * max(n, 1))(*strides_a), (C.c_longlong * max(n, 1))(*strides_b), dtype,
             _stream(stream)))
+
+    # -- remaining forward entry points ---------------------------------------------
+    UNARY = {"exp": 0, "log": 1, "sqrt": 2, "rsqrt": 3, "sin": 4, "cos": 5}
+
+    def unary(self, op, x, y, n, dtype, stream=None):
+        self._rc(self._lib.mu_unary(self._h, self.UNARY[op], _ptr(x), _ptr(y), n, dtype, _stream(stream)))
+
+    def leaky_relu(self, x, y, n, slope, dtype, stream=None):
+        self._rc(self._lib.mu_leaky_relu(self._h, _ptr(x), _ptr(y), n, slope, dtype, _stream(stream)))
+
+    def broadcast_row(self, row, out, rows, cols, dtype, stream=None):
+        self._rc(self._lib.mu_broadcast_row(self._h, _ptr(row), _ptr(out), rows, cols, dtype,
+                                            _stream(stream)))
+
+    def concat(self, inputs, dim_sizes, out, outer, inner, dtype, stream=None):
+        n = len(inputs)
+        ptrs = (_vp * max(n, 1))(*[_ptr(t) for t in inputs])
+        self._rc(self._lib.mu_concat(self._h, ptrs, (C.c_int * max(n, 1))(*dim_sizes), n, _ptr(out),
+                                     outer, inner, dtype, _stream(stream)))
+
+    def upsample2d(self, x, y, B, Cc, H, W, scale, dtype, stream=None):
+        self._rc(self._lib.mu_upsample2d(self._h, _ptr(x), _ptr(y), B, Cc, H, W, scale, dtype,
+                                         _stream(stream)))
+
+    def batch_norm_eval(self, x, gamma, beta, mean, var, y, B, Cc, H, W, eps, dtype, stream=None):
+        self._rc(self._lib.mu_batch_norm_eval(self._h, _ptr(x), _ptr(gamma), _ptr(beta), _ptr(mean),
+                                              _ptr(var), _ptr(y), B, Cc, H, W, eps, dtype,
+                                              _stream(stream)))
+
+    def rms_norm(self, x, w, y, rows, cols, dtype, eps=1e-5, stream=None):
+        self._rc(self._lib.mu_rms_norm(self._h, _ptr(x), _ptr(w), _ptr(y), rows, cols, eps, dtype,
+                                       _stream(stream)))
+
+    def sum(self, x, out, n, dtype, stream=None):
+        self._rc(self._lib.mu_sum(self._h, _ptr(x), _ptr(out), n, dtype, _stream(stream)))
+
+    def mean_last_dim(self, x, out, outer, dim, dtype, stream=None):
+        self._rc(self._lib.mu_mean_last_dim(self._h, _ptr(x), _ptr(out), outer, dim, dtype,
+                                            _stream(stream)))
+
+    def sum_to_shape(self, x, out, in_shape, out_shape, dtype, stream=None):
+        ni, no = len(in_shape), len(out_shape)
+        self._rc(self._lib.mu_sum_to_shape(self._h, _ptr(x), _ptr(out), (C.c_int * max(ni, 1))(*in_shape),
+                                           ni, (C.c_int * max(no, 1))(*out_shape), no, dtype,
+                                           _stream(stream)))
+
+    def fill_uniform(self, out, n, low, high, seed, dtype, stream=None):
+        self._rc(self._lib.mu_fill_uniform(self._h, _ptr(out), n, low, high, seed, dtype,
+                                           _stream(stream)))
 
     def argmax(self, x, idx, rows, cols, dtype, stream=None):
         self._rc(self._lib.mu_argmax(self._h, _ptr(x), _ptr(idx), rows, cols, dtype, _stream(stream)))

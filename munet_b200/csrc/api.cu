@@ -161,6 +161,7 @@ const char *mu_last_error(const mu_ctx *ctx) { return ctx ? ctx->err : "null con
 // used by the entry points that live in other translation units
 int mu_set_error(mu_ctx *ctx, int code, const char *msg) { return fail(ctx, code, "%s", msg); }
 int mu_ctx_num_sms(const mu_ctx *ctx) { return ctx ? ctx->num_sms : 0; }
+int mu_ctx_select_device(mu_ctx *ctx) { return (ctx && set_device(ctx)) ? MU_OK : MU_ERR_CUDA; }
 int mu_ctx_force_simt(mu_ctx *ctx, int on) {
   if (!ctx)
     return MU_ERR_INVALID;

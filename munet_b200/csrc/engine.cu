@@ -35,7 +35,7 @@ namespace {
 
 enum OpKind {
   OP_EMBED, OP_LN, OP_LINEAR, OP_QKV, OP_ATTN, OP_ELTWISE, OP_ARGMAX, OP_CONV, OP_MAXPOOL, OP_GAP,
-  OP_ALLREDUCE
+  OP_ALLREDUCE, OP_BATCHNORM, OP_UPSAMPLE, OP_LEAKY, OP_RMSNORM
 };
 
 struct Tensor {
@@ -497,6 +497,67 @@ int mu_engine::lower(const Json &node, const std::string &prefix, Val &v, const 
     v.tid = op.out;
     return MU_OK;
   }
+  if (type == "LeakyReLU") { // src/nn/activations.hpp:76-88
+    const Json *sl = node.get("negative_slope");
+    if (!sl || !sl->is_number()) return fail(MU_ERR_INVALID, "LeakyReLU: missing negative_slope");
+    Op op;
+    op.kind = OP_LEAKY, op.eps = static_cast<float>(sl->num), op.n = v.numel();
+    op.in = v.tid, op.out = new_tensor(static_cast<size_t>(op.n) * esize(dtype));
+    push(op);
+    v.tid = op.out;
+    return MU_OK;
+  }
+  if (type == "RMSNorm") { // src/nn/normalization.hpp:39-67
+    int d;
+    const Json *eps = node.get("eps");
+    if (!req_int("normalized_shape", &d) || !eps || !eps->is_number())
+      return fail(MU_ERR_INVALID, "RMSNorm: missing normalized_shape/eps");
+    if (d <= 0) return fail(MU_ERR_INVALID, "RMSNorm expects normalized_shape > 0");
+    if (v.shape.empty() || v.shape.back() != d)
+      return fail(MU_ERR_INVALID, "RMSNorm expects last dim to match normalized_shape");
+    Op n;
+    n.kind = OP_RMSNORM, n.eps = static_cast<float>(eps->num);
+    n.w = stage_weight({prefix + "weight"}, &why);
+    if (n.w < 0) return fail(MU_ERR_INVALID, "RMSNorm: %s", why.c_str());
+    n.M = static_cast<int>(v.numel() / d), n.N = d, n.in = v.tid;
+    n.out = new_tensor(static_cast<size_t>(v.numel()) * esize(dtype));
+    push(n);
+    v.tid = n.out;
+    return MU_OK;
+  }
+  if (type == "BatchNorm2d") { // src/nn/normalization.hpp:69-108, eval: running statistics
+    int c;
+    const Json *eps = node.get("eps");
+    if (!req_int("num_features", &c) || !eps || !eps->is_number())
+      return fail(MU_ERR_INVALID, "BatchNorm2d: missing num_features/eps");
+    if (v.shape.size() != 4 || v.shape[1] != c)
+      return fail(MU_ERR_INVALID, "BatchNorm2d expects NCHW input with C == num_features");
+    if (dtype != MU_F32) return fail(MU_ERR_UNSUPPORTED, "BatchNorm2d: only float32 is implemented");
+    Op n;
+    n.kind = OP_BATCHNORM, n.eps = static_cast<float>(eps->num);
+    n.w = stage_weight({prefix + "weight"}, &why);
+    if (n.w >= 0) n.b = stage_weight({prefix + "bias"}, &why);
+    if (n.b >= 0) n.w2 = stage_weight({prefix + "running_mean"}, &why);
+    if (n.w2 >= 0) n.b2 = stage_weight({prefix + "running_var"}, &why);
+    if (n.w < 0 || n.b < 0 || n.w2 < 0 || n.b2 < 0) return fail(MU_ERR_INVALID, "BatchNorm2d: %s", why.c_str());
+    n.B = v.shape[0], n.iC = c, n.iH = v.shape[2], n.iW = v.shape[3], n.in = v.tid;
+    n.out = new_tensor(static_cast<size_t>(v.numel()) * 4);
+    push(n);
+    v.tid = n.out;
+    return MU_OK;
+  }
+  if (type == "Upsample") { // src/nn/pooling.hpp:37-43, nearest neighbour
+    int sc;
+    if (!req_int("scale_factor", &sc) || sc <= 0) return fail(MU_ERR_INVALID, "Upsample: missing scale_factor");
+    if (v.shape.size() != 4) return fail(MU_ERR_INVALID, "Upsample expects NCHW input");
+    Op u;
+    u.kind = OP_UPSAMPLE, u.B = v.shape[0], u.iC = v.shape[1], u.iH = v.shape[2], u.iW = v.shape[3];
+    u.stride = sc, u.in = v.tid;
+    u.out = new_tensor(static_cast<size_t>(v.numel()) * sc * sc * esize(dtype));
+    push(u);
+    v.tid = u.out, v.shape = {u.B, u.iC, u.iH * sc, u.iW * sc};
+    return MU_OK;
+  }
   if (type == "Conv2d") { // src/nn/linear.hpp:39-64; ReLU and MaxPool2d(2,2,0) that follow are fused
     int iC, oC, k, s, p;
     if (!req_int("in_channels", &iC) || !req_int("out_channels", &oC) || !req_int("kernel_size", &k) ||
@@ -794,6 +855,24 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       rc = mu_global_avg_pool(ctx, tptr(op.in), tptr(op.out), op.B, op.iC, op.iH, op.iW, dtype, st);
       n_launches += 1;
       break;
+    case OP_LEAKY:
+      rc = mu_leaky_relu(ctx, tptr(op.in), tptr(op.out), op.n, op.eps, dtype, st);
+      n_launches += 1;
+      break;
+    case OP_RMSNORM:
+      rc = mu_rms_norm(ctx, tptr(op.in), wptr(op.w), tptr(op.out), op.M, op.N, op.eps, dtype, st);
+      n_launches += 1;
+      break;
+    case OP_BATCHNORM:
+      rc = mu_batch_norm_eval(ctx, tptr(op.in), wptr(op.w), wptr(op.b), static_cast<const float *>(wptr(op.w2)),
+                              static_cast<const float *>(wptr(op.b2)), tptr(op.out), op.B, op.iC, op.iH,
+                              op.iW, op.eps, dtype, st);
+      n_launches += 1;
+      break;
+    case OP_UPSAMPLE:
+      rc = mu_upsample2d(ctx, tptr(op.in), tptr(op.out), op.B, op.iC, op.iH, op.iW, op.stride, dtype, st);
+      n_launches += 1;
+      break;
     default:
       rc = MU_ERR_UNSUPPORTED;
     }
@@ -848,6 +927,18 @@ void mu_engine::op_work(const Op &op, double *flops, double *bytes) const {
   case OP_MAXPOOL:
   case OP_GAP:
     *bytes = 4.0 * op.B * op.iC * op.iH * op.iW;
+    break;
+  case OP_LEAKY:
+    *bytes = es * 2.0 * op.n;
+    break;
+  case OP_RMSNORM:
+    *bytes = es * 2.0 * op.M * op.N;
+    break;
+  case OP_BATCHNORM:
+    *bytes = es * 2.0 * op.B * op.iC * op.iH * op.iW;
+    break;
+  case OP_UPSAMPLE:
+    *bytes = es * (1.0 + op.stride * op.stride) * op.B * op.iC * op.iH * op.iW;
     break;
   default:
     break;

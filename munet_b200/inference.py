@@ -230,7 +230,8 @@ class Engine:
         return out
 
     OP_KINDS = ["embed", "layer_norm", "linear", "qkv_linear", "attention", "eltwise", "argmax",
-                "conv2d", "max_pool2d", "global_avg_pool", "all_reduce"]
+                "conv2d", "max_pool2d", "global_avg_pool", "all_reduce", "batch_norm", "upsample",
+                "leaky_relu", "rms_norm"]
 
     def profile(self, reps: int = 1, stream=None) -> list[dict]:
         """Eager forward with CUDA events around every op: per-op ms + algorithmic work."""

@@ -182,6 +182,68 @@ class _Lib:
         self._call("global_avg_pool", _p(x), _p(y), B, Cc, H, W, *extra)
         return y
 
+    # -- remaining forward entry points ------------------------------------------
+    UNARY = {"exp": 0, "log": 1, "sqrt": 2, "rsqrt": 3, "sin": 4, "cos": 5}
+
+    def unary(self, x, dtype, op):
+        x = _c(x, dtype)
+        y = np.empty_like(x)
+        self._call("unary", _p(x), _p(y), C.c_long(x.size), dtype, self.UNARY[op])
+        return y
+
+    def leaky_relu(self, x, slope, dtype):
+        x = _c(x, dtype)
+        y = np.empty_like(x)
+        self._call("leaky_relu", _p(x), _p(y), C.c_long(x.size), C.c_float(slope), dtype)
+        return y
+
+    def rms_norm(self, x, w, dtype, eps=1e-5):
+        x, w = _c(x, dtype), _c(w, dtype)
+        cols = x.shape[-1]
+        y = np.empty_like(x)
+        self._call("rms_norm", _p(x), _p(w), _p(y), x.size // cols, cols, C.c_float(eps), dtype)
+        return y
+
+    def batch_norm_eval(self, x, g, b, mean, var, dtype, eps=1e-5):
+        x, g, b = _c(x, dtype), _c(g, dtype), _c(b, dtype)
+        mean, var = _c(mean, F32), _c(var, F32)
+        B, Cc, H, W = x.shape
+        y = np.empty_like(x)
+        self._call("batch_norm_eval", _p(x), _p(g), _p(b), _p(mean), _p(var), _p(y), B, Cc, H, W,
+                   C.c_float(eps), dtype)
+        return y
+
+    def sum(self, x, dtype):
+        x = _c(x, dtype)
+        y = np.empty((1,), np_dtype(dtype))
+        self._call("sum", _p(x), _p(y), C.c_long(x.size), dtype)
+        return y
+
+    def mean_last_dim(self, x, dtype):
+        x = _c(x, dtype)
+        dim = x.shape[-1]
+        y = np.empty(x.shape[:-1], np_dtype(dtype))
+        self._call("mean_last_dim", _p(x), _p(y), x.size // dim, dim, dtype)
+        return y
+
+    def upsample2d(self, x, scale, dtype):
+        """Reference only (data movement: numpy's repeat is the CPU checker)."""
+        x = _c(x, dtype)
+        B, Cc, H, W = x.shape
+        y = np.empty((B, Cc, H * scale, W * scale), np_dtype(dtype))
+        self._call("upsample2d", _p(x), _p(y), B, Cc, H, W, scale, dtype)
+        return y
+
+    def concat(self, xs, dtype):
+        """Reference only: inputs shaped [outer, dim_j, inner], joined along axis 1."""
+        xs = [_c(x, dtype) for x in xs]
+        outer, _, inner = xs[0].shape
+        dims = [x.shape[1] for x in xs]
+        y = np.empty((outer, sum(dims), inner), np_dtype(dtype))
+        arr = (C.c_void_p * len(xs))(*[x.ctypes.data for x in xs])
+        self._call("concat", arr, (C.c_int * len(xs))(*dims), len(xs), _p(y), outer, inner, dtype)
+        return y
+
     def gpt_forward(self, ids, params, V, d, H, L, dtype, stop_after_layers=-1, kmode=K_LITERAL):
         ids = _c(ids, I32)
         B, T = ids.shape

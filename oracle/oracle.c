@@ -635,3 +635,169 @@ int orc_gpt_forward(const int32_t *ids, const void *const *params, void *out,
   free(h); free(t1); free(t2); free(f);
   return 0;
 }
+
+/* ------------------------------------------------------------------------
+ * Remaining forward entry points (UNet-style and RMSNorm models).
+ * float32 follows the CPU backend's float kernels, bfloat16 the typed fallback
+ * (evaluate in double, round double -> float -> bf16 after EVERY op).
+ * ---------------------------------------------------------------------- */
+
+/* op: 0 exp, 1 log, 2 sqrt, 3 rsqrt, 4 sin, 5 cos.
+ * float32: src/backend/cpu_backend.hpp:533-586; typed: src/core/ops/activations.cpp:66-190. */
+int orc_unary(const void *x, void *y, long n, int dtype, int op) {
+  if (dtype == DT_F32) {
+    const float *a = x;
+    float *o = y;
+    for (long i = 0; i < n; ++i) {
+      float v = a[i];
+      o[i] = op == 0 ? expf(v) : op == 1 ? logf(v) : op == 2 ? sqrtf(v)
+           : op == 3 ? 1.0f / sqrtf(v) : op == 4 ? sinf(v) : cosf(v);
+    }
+    return 0;
+  }
+  if (dtype != DT_BF16)
+    return 1;
+  const uint16_t *a = x;
+  uint16_t *o = y;
+  for (long i = 0; i < n; ++i) {
+    double v = bf2d(a[i]);
+    o[i] = d2bf(op == 0 ? exp(v) : op == 1 ? log(v) : op == 2 ? sqrt(v)
+              : op == 3 ? 1.0 / sqrt(v) : op == 4 ? sin(v) : cos(v));
+  }
+  return 0;
+}
+
+/* nn::LeakyReLU, src/nn/activations.hpp:76-88: relu(x) + (x - relu(x)) * slope, the slope
+ * held in a one-element tensor of the activation's dtype. */
+int orc_leaky_relu(const void *x, void *y, long n, float slope, int dtype) {
+  if (dtype == DT_F32) {
+    const float *a = x;
+    float *o = y;
+    for (long i = 0; i < n; ++i) {
+      float r = a[i] > 0 ? a[i] : 0;
+      float d = a[i] - r;
+      float m = d * slope;
+      o[i] = r + m;
+    }
+    return 0;
+  }
+  if (dtype != DT_BF16)
+    return 1;
+  const uint16_t *a = x, sl = f2bf(slope);
+  uint16_t *o = y;
+  for (long i = 0; i < n; ++i) {
+    double v = bf2d(a[i]);
+    uint16_t r = d2bf(v > 0.0 ? v : 0.0);
+    o[i] = add_bf16(r, mul_bf16(sub_bf16(a[i], r), sl));
+  }
+  return 0;
+}
+
+/* nn::RMSNorm, src/nn/normalization.hpp:53-62:
+ * variance = mean(x*x, -1); normed = x * rsqrt(variance + eps); out = normed * weight.
+ * mean accumulates in double (src/backend/cpu_backend.hpp:1124-1137; typed path
+ * src/core/ops/shape.cpp:112-150). */
+int orc_rms_norm(const void *x, const void *w, void *y, int rows, int cols, float eps, int dtype) {
+  if (dtype == DT_F32) {
+    const float *a = x, *g = w;
+    float *o = y;
+    for (int r = 0; r < rows; ++r) {
+      double tot = 0.0;
+      for (int c = 0; c < cols; ++c) {
+        float sq = a[(size_t)r * cols + c] * a[(size_t)r * cols + c];
+        tot += sq;
+      }
+      float var = (float)(tot / (double)cols);
+      float ve = var + eps;
+      float rs = 1.0f / sqrtf(ve);
+      for (int c = 0; c < cols; ++c) {
+        float nm = a[(size_t)r * cols + c] * rs;
+        o[(size_t)r * cols + c] = nm * g[c];
+      }
+    }
+    return 0;
+  }
+  if (dtype != DT_BF16)
+    return 1;
+  const uint16_t *a = x, *g = w, e = f2bf(eps);
+  uint16_t *o = y;
+  for (int r = 0; r < rows; ++r) {
+    double tot = 0.0;
+    for (int c = 0; c < cols; ++c)
+      tot += bf2d(mul_bf16(a[(size_t)r * cols + c], a[(size_t)r * cols + c]));
+    uint16_t var = d2bf(tot * (1.0 / (double)cols));
+    uint16_t ve = add_bf16(var, e);
+    uint16_t rs = d2bf(1.0 / sqrt(bf2d(ve)));
+    for (int c = 0; c < cols; ++c)
+      o[(size_t)r * cols + c] = mul_bf16(mul_bf16(a[(size_t)r * cols + c], rs), g[c]);
+  }
+  return 0;
+}
+
+/* batch_norm, eval branch (src/backend/cpu_backend.hpp:957-967): float arithmetic
+ * y = g*(x-mean)*(1/sqrt(var+eps)) + b; bf16 inputs are widened to float and the result is
+ * rounded once (src/core/ops/normalization.cpp:32-60). Statistics are float32. */
+int orc_batch_norm_eval(const void *x, const void *g, const void *b, const float *mean,
+                        const float *var, void *y, int B, int C, int H, int W, float eps,
+                        int dtype) {
+  if (dtype != DT_F32 && dtype != DT_BF16)
+    return 1;
+  const size_t spatial = (size_t)H * W, n = (size_t)B * C * spatial;
+  for (size_t i = 0; i < n; ++i) {
+    int c = (int)((i / spatial) % C);
+    float xv, gv, bv;
+    if (dtype == DT_F32) {
+      xv = ((const float *)x)[i], gv = ((const float *)g)[c], bv = ((const float *)b)[c];
+    } else {
+      xv = bf2f(((const uint16_t *)x)[i]), gv = bf2f(((const uint16_t *)g)[c]),
+      bv = bf2f(((const uint16_t *)b)[c]);
+    }
+    float inv_std = 1.0f / sqrtf(var[c] + eps);
+    float d = xv - mean[c];
+    float t = gv * d;
+    float u = t * inv_std;
+    float r = u + bv;
+    if (dtype == DT_F32)
+      ((float *)y)[i] = r;
+    else
+      ((uint16_t *)y)[i] = f2bf(r);
+  }
+  return 0;
+}
+
+/* sum of every element: float32 adds sequentially in float (src/backend/cpu_backend.hpp:1040-1049),
+ * the typed path accumulates in double (src/core/ops/shape.cpp:56-66). */
+int orc_sum(const void *x, void *out, long n, int dtype) {
+  if (dtype == DT_F32) {
+    float tot = 0.0f;
+    for (long i = 0; i < n; ++i)
+      tot += ((const float *)x)[i];
+    *(float *)out = tot;
+    return 0;
+  }
+  if (dtype != DT_BF16)
+    return 1;
+  double tot = 0.0;
+  for (long i = 0; i < n; ++i)
+    tot += bf2d(((const uint16_t *)x)[i]);
+  *(uint16_t *)out = d2bf(tot);
+  return 0;
+}
+
+/* mean over the last dimension, double accumulation in both paths
+ * (src/backend/cpu_backend.hpp:1124-1137; src/core/ops/shape.cpp:112-155). */
+int orc_mean_last_dim(const void *x, void *out, int outer, int dim, int dtype) {
+  if (dtype != DT_F32 && dtype != DT_BF16)
+    return 1;
+  for (int r = 0; r < outer; ++r) {
+    double tot = 0.0;
+    for (int c = 0; c < dim; ++c)
+      tot += dtype == DT_F32 ? (double)((const float *)x)[(size_t)r * dim + c]
+                             : bf2d(((const uint16_t *)x)[(size_t)r * dim + c]);
+    if (dtype == DT_F32)
+      ((float *)out)[r] = (float)(tot / (double)dim);
+    else
+      ((uint16_t *)out)[r] = d2bf(tot * (1.0 / (double)dim));
+  }
+  return 0;
+}

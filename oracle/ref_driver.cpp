@@ -192,6 +192,73 @@ int ref_mha(const void *x, const void *const *params, void *y, int B, int T,
   });
 }
 
+// Unary math through the Tensor API (op: 0 exp, 1 log, 2 sqrt, 3 rsqrt, 4 sin, 5 cos).
+int ref_unary(const void *x, void *y, long n, int dtype, int op) {
+  return guarded([&] {
+    Tensor t = from_host(x, {static_cast<int>(n)}, dtype);
+    Tensor out = op == 0 ? t.exp() : op == 1 ? t.log() : op == 2 ? t.sqrt()
+               : op == 3 ? t.rsqrt() : op == 4 ? t.sin() : t.cos();
+    to_host(out, y);
+  });
+}
+
+int ref_leaky_relu(const void *x, void *y, long n, float slope, int dtype) {
+  return guarded([&] {
+    to_host(nn::LeakyReLU(slope).forward(from_host(x, {static_cast<int>(n)}, dtype)), y);
+  });
+}
+
+int ref_rms_norm(const void *x, const void *w, void *y, int rows, int cols, float eps, int dtype) {
+  return guarded([&] {
+    TensorOptions opt(kCpu, dt(dtype), false);
+    nn::RMSNorm m(cols, eps, opt);
+    set_param(m.weight, w);
+    m.eval();
+    to_host(m.forward(from_host(x, {rows, cols}, dtype)), y);
+  });
+}
+
+// nn::BatchNorm2d in eval mode with the given running statistics (float32).
+int ref_batch_norm_eval(const void *x, const void *g, const void *b, const float *mean,
+                        const float *var, void *y, int B, int C, int H, int W, float eps,
+                        int dtype) {
+  return guarded([&] {
+    TensorOptions opt(kCpu, dt(dtype), false);
+    nn::BatchNorm2d m(C, eps, 0.1f, opt);
+    set_param(m.weight, g);
+    set_param(m.bias, b);
+    if (m.running_mean.dtype() != DataType::Float32 || m.running_var.dtype() != DataType::Float32)
+      throw std::runtime_error("driver expects float32 running statistics");
+    std::memcpy(m.running_mean.data(), mean, sizeof(float) * C);
+    std::memcpy(m.running_var.data(), var, sizeof(float) * C);
+    m.eval();
+    to_host(m.forward(from_host(x, {B, C, H, W}, dtype)), y);
+  });
+}
+
+int ref_upsample2d(const void *x, void *y, int B, int C, int H, int W, int scale, int dtype) {
+  return guarded([&] { to_host(from_host(x, {B, C, H, W}, dtype).upsample2d(scale), y); });
+}
+
+// Tensor::cat of n inputs shaped [outer, dim_j, inner] along dimension 1.
+int ref_concat(const void *const *inputs, const int *dims, int n, void *out, int outer, int inner,
+               int dtype) {
+  return guarded([&] {
+    std::vector<Tensor> ts;
+    for (int j = 0; j < n; ++j)
+      ts.push_back(from_host(inputs[j], {outer, dims[j], inner}, dtype));
+    to_host(Tensor::cat(ts, 1), out);
+  });
+}
+
+int ref_sum(const void *x, void *out, long n, int dtype) {
+  return guarded([&] { to_host(from_host(x, {static_cast<int>(n)}, dtype).sum(), out); });
+}
+
+int ref_mean_last_dim(const void *x, void *out, int outer, int dim, int dtype) {
+  return guarded([&] { to_host(from_host(x, {outer, dim}, dtype).mean(-1, false), out); });
+}
+
 // nn::Embedding index path: ids[B,T] int32 → out[B,T,D] in the table's dtype.
 int ref_embedding(const int32_t *ids, const void *table, void *out, int B,
                   int T, int V, int D, int dtype) {

@@ -137,3 +137,60 @@ def test_all_reduce_sum(dtype, world):
     rng = np.random.default_rng(9)
     bufs = [rnd(rng, (257,), dtype) for _ in range(world)]
     same(oracle.port().all_reduce_sum(bufs, dtype), oracle.ref().all_reduce_sum(bufs, dtype))
+
+
+# ---- remaining forward entry points -------------------------------------------------------
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("op", ["exp", "log", "sqrt", "rsqrt", "sin", "cos"])
+def test_unary(dtype, op):
+    rng = np.random.default_rng(11)
+    x = rnd(rng, (777,), dtype, 2.0)
+    if op in ("log", "sqrt", "rsqrt"):  # the reference throws outside the domain
+        xf = np.abs(oracle.as_float(x, dtype)) + 0.01
+        x = xf.astype(np.float32) if dtype == F32 else oracle.to_bf16(xf)
+    same(oracle.port().unary(x, dtype, op), oracle.ref().unary(x, dtype, op))
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_leaky_relu_rms_norm(dtype):
+    rng = np.random.default_rng(12)
+    x = rnd(rng, (500,), dtype, 3.0)
+    for slope in (0.01, 0.2):
+        same(oracle.port().leaky_relu(x, slope, dtype), oracle.ref().leaky_relu(x, slope, dtype))
+    x, w = rnd(rng, (19, 96), dtype, 2.0), rnd(rng, (96,), dtype)
+    same(oracle.port().rms_norm(x, w, dtype), oracle.ref().rms_norm(x, w, dtype))
+    same(oracle.port().rms_norm(x, w, dtype, eps=1e-3), oracle.ref().rms_norm(x, w, dtype, eps=1e-3))
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_batch_norm_eval(dtype):
+    rng = np.random.default_rng(13)
+    x = rnd(rng, (3, 5, 4, 6), dtype, 2.0)
+    g, b = rnd(rng, (5,), dtype), rnd(rng, (5,), dtype)
+    mean = rng.standard_normal(5).astype(np.float32)
+    var = (rng.random(5) + 0.1).astype(np.float32)
+    same(oracle.port().batch_norm_eval(x, g, b, mean, var, dtype),
+         oracle.ref().batch_norm_eval(x, g, b, mean, var, dtype))
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_reductions(dtype):
+    rng = np.random.default_rng(14)
+    x = rnd(rng, (23, 130), dtype)
+    same(oracle.port().mean_last_dim(x, dtype), oracle.ref().mean_last_dim(x, dtype))
+    same(oracle.port().sum(x.reshape(-1), dtype), oracle.ref().sum(x.reshape(-1), dtype))
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_data_movement_is_what_numpy_does(dtype):
+    """upsample2d and concat move values without arithmetic: numpy is the CPU checker the GPU
+    tests use, pinned here against the reference."""
+    rng = np.random.default_rng(15)
+    x = rnd(rng, (2, 3, 4, 5), dtype)
+    same(np.repeat(np.repeat(x, 3, axis=2), 3, axis=3), oracle.ref().upsample2d(x, 3, dtype))
+    xs = [rnd(rng, (4, d, 6), dtype) for d in (3, 1, 5)]
+    if dtype == F32:
+        same(np.concatenate(xs, axis=1), oracle.ref().concat(xs, dtype))
+    else:  # the reference's CPU backend has no bfloat16 concat (explicit_unsupported)
+        with pytest.raises(RuntimeError, match="does not support feature 'concat'"):
+            oracle.ref().concat(xs, dtype)
