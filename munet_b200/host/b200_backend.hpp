@@ -3,11 +3,12 @@
 // MuNet headers (include path = its `src/`); it contains no kernels.
 //
 // Advertised (query_support): Matmul, ElementwiseBinary (add/sub/mul/div with
-// broadcasting), UnaryActivation (relu, sigmoid), Softmax for float32 and bfloat16;
-// Convolution and Pooling for float32. Row broadcast, reductions, concat, batch-norm and random fill are not advertised, so MuNet's
-// dispatcher routes them to its CPU fallback exactly as it does for any partial
-// backend (src/core/op_dispatch.cpp:670-718). Backward/optimizer entry points are
-// training-only and throw.
+// broadcasting), BroadcastRow, UnaryActivation (relu, sigmoid, exp, log, sqrt, rsqrt, sin,
+// cos), Softmax, Concat, Reduction, RandomFill for float32 and bfloat16; Convolution,
+// Pooling (max-pool, nearest upsample) and BatchNorm (inference branch) for float32.
+// Loss and OptimizerStep are not advertised, so MuNet's dispatcher keeps them on its CPU
+// path exactly as it does for any partial backend (src/core/op_dispatch.cpp:670-718).
+// Backward entry points and batch_norm(training=true) are training-only and throw.
 //
 // Errors follow the reference convention: std::runtime_error with the C ABI's
 // message (src/backend/cuda_backend.cu:15-31). copy() is complete on return
@@ -18,8 +19,10 @@
 #include "munet_b200.h"
 #include "storage.hpp"
 
+#include <cstring>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 namespace munet {
 
@@ -27,7 +30,11 @@ class B200Backend : public Backend,
                     public BackendAllocationTransferCapability,
                     public BackendElementwiseCapability,
                     public BackendBlasCapability,
-                    public BackendSpatialCapability {
+                    public BackendSpatialCapability,
+                    public BackendReductionCapability,
+                    public BackendShapeCapability,
+                    public BackendNormalizationCapability,
+                    public BackendRandomCapability {
 public:
   explicit B200Backend(int index) {
     const int rc = mu_ctx_create(index, &ctx_);
@@ -46,6 +53,14 @@ public:
   const BackendBlasCapability *blas_capability() const override { return this; }
   BackendSpatialCapability *spatial_capability() override { return this; }
   const BackendSpatialCapability *spatial_capability() const override { return this; }
+  BackendReductionCapability *reduction_capability() override { return this; }
+  const BackendReductionCapability *reduction_capability() const override { return this; }
+  BackendShapeCapability *shape_capability() override { return this; }
+  const BackendShapeCapability *shape_capability() const override { return this; }
+  BackendNormalizationCapability *normalization_capability() override { return this; }
+  const BackendNormalizationCapability *normalization_capability() const override { return this; }
+  BackendRandomCapability *random_capability() override { return this; }
+  const BackendRandomCapability *random_capability() const override { return this; }
 
   BackendSupport query_support(BackendFeature feature, DataType dtype,
                                const Shape *shape) const override {
@@ -56,10 +71,15 @@ public:
     case BackendFeature::UnaryActivation:
     case BackendFeature::Softmax:
     case BackendFeature::ElementwiseBinary:
+    case BackendFeature::BroadcastRow:
+    case BackendFeature::Concat:
+    case BackendFeature::Reduction:
+    case BackendFeature::RandomFill:
       s.available = f32 || bf16;
       break;
     case BackendFeature::Convolution:
     case BackendFeature::Pooling:
+    case BackendFeature::BatchNorm:
       s.available = f32;
       break;
     default:
@@ -134,13 +154,15 @@ public:
   void sub(const Storage &a, const Storage &b, Storage &o, const BroadcastInfo &i) override { binary(MU_OP_SUB, a, b, o, i); }
   void mul(const Storage &a, const Storage &b, Storage &o, const BroadcastInfo &i) override { binary(MU_OP_MUL, a, b, o, i); }
   void div(const Storage &a, const Storage &b, Storage &o, const BroadcastInfo &i) override { binary(MU_OP_DIV, a, b, o, i); }
-  void broadcast_row(const Storage &, Storage &, int, int) override { not_advertised("broadcast_row"); }
-  void exp(const Storage &, Storage &, size_t) override { not_advertised("exp"); }
-  void log(const Storage &, Storage &, size_t) override { not_advertised("log"); }
-  void sqrt(const Storage &, Storage &, size_t) override { not_advertised("sqrt"); }
-  void rsqrt(const Storage &, Storage &, size_t) override { not_advertised("rsqrt"); }
-  void sin(const Storage &, Storage &, size_t) override { not_advertised("sin"); }
-  void cos(const Storage &, Storage &, size_t) override { not_advertised("cos"); }
+  void broadcast_row(const Storage &src, Storage &dst, int rows, int cols) override {
+    check(mu_broadcast_row(ctx_, src.data(), dst.data(), rows, cols, code(src), nullptr));
+  }
+  void exp(const Storage &in, Storage &out, size_t n) override { math(MU_UN_EXP, in, out, n); }
+  void log(const Storage &in, Storage &out, size_t n) override { math(MU_UN_LOG, in, out, n); }
+  void sqrt(const Storage &in, Storage &out, size_t n) override { math(MU_UN_SQRT, in, out, n); }
+  void rsqrt(const Storage &in, Storage &out, size_t n) override { math(MU_UN_RSQRT, in, out, n); }
+  void sin(const Storage &in, Storage &out, size_t n) override { math(MU_UN_SIN, in, out, n); }
+  void cos(const Storage &in, Storage &out, size_t n) override { math(MU_UN_COS, in, out, n); }
   void relu_backward(const Storage &, const Storage &, Storage &, size_t) override { training_only("relu_backward"); }
   void sigmoid_backward(const Storage &, const Storage &, Storage &, size_t) override { training_only("sigmoid_backward"); }
   void softmax_backward(const Storage &, const Storage &, Storage &, int, int) override { training_only("softmax_backward"); }
@@ -156,15 +178,76 @@ public:
                   int p) override {
     check(mu_max_pool2d(ctx_, in.data(), out.data(), B, C, iH, iW, k, s, p, code(in), nullptr));
   }
-  void upsample2d(const Storage &, Storage &, int, int, int, int, int) override { not_advertised("upsample2d"); }
+  void upsample2d(const Storage &in, Storage &out, int B, int C, int iH, int iW, int scale) override {
+    check(mu_upsample2d(ctx_, in.data(), out.data(), B, C, iH, iW, scale, code(in), nullptr));
+  }
   void conv2d_backward(const Storage &, const Storage &, const Storage &, Storage &, Storage &,
                        Storage *, int, int, int, int, int, int, int, int, int) override { training_only("conv2d_backward"); }
   void max_pool2d_backward(const Storage &, const Storage &, Storage &, int, int, int, int, int, int,
                            int) override { training_only("max_pool2d_backward"); }
   void upsample2d_backward(const Storage &, Storage &, int, int, int, int, int) override { training_only("upsample2d_backward"); }
 
+  // ---- reductions -------------------------------------------------------------------
+  void sum_to_shape(const Storage &in, Storage &out, const Shape &in_shape, const Shape &out_shape) override {
+    check(mu_sum_to_shape(ctx_, in.data(), out.data(), in_shape.data(), static_cast<int>(in_shape.size()),
+                          out_shape.data(), static_cast<int>(out_shape.size()), code(in), nullptr));
+  }
+  void sum(const Storage &in, Storage &out, size_t n) override {
+    check(mu_sum(ctx_, in.data(), out.data(), static_cast<long long>(n), code(in), nullptr));
+  }
+  void mean_last_dim(const Storage &in, Storage &out, int outer, int dim) override {
+    check(mu_mean_last_dim(ctx_, in.data(), out.data(), outer, dim, code(in), nullptr));
+  }
+
+  // ---- shape ------------------------------------------------------------------------
+  void concat(const std::vector<Storage *> &inputs, Storage &out, int dim,
+              const std::vector<Shape> &shapes) override {
+    if (inputs.empty() || shapes.size() != inputs.size())
+      throw std::runtime_error("B200Backend: concat expects one shape per input");
+    long long outer = 1, inner = 1;
+    for (int i = 0; i < dim; ++i) outer *= shapes[0][i];
+    for (size_t i = dim + 1; i < shapes[0].size(); ++i) inner *= shapes[0][i];
+    std::vector<const void *> ptrs;
+    std::vector<int> dims;
+    for (size_t j = 0; j < inputs.size(); ++j) {
+      ptrs.push_back(inputs[j]->data());
+      dims.push_back(shapes[j][dim]);
+    }
+    check(mu_concat(ctx_, ptrs.data(), dims.data(), static_cast<int>(ptrs.size()), out.data(), outer,
+                    inner, code(out), nullptr));
+  }
+  void concat_backward(const Storage &, std::vector<Storage *> &, int, const std::vector<Shape> &) override {
+    training_only("concat_backward");
+  }
+
+  // ---- normalization ------------------------------------------------------------------
+  void batch_norm(const Storage &in, const Storage &scale, const Storage &bias, Storage &running_mean,
+                  Storage &running_var, Storage &, Storage &, Storage &out, int B, int C, int H, int W,
+                  float, float eps, bool training) override {
+    if (training) training_only("batch_norm(training=true)");
+    if (running_mean.dtype() != DataType::Float32 || running_var.dtype() != DataType::Float32)
+      throw std::runtime_error("B200Backend: batch_norm expects float32 running statistics");
+    check(mu_batch_norm_eval(ctx_, in.data(), scale.data(), bias.data(),
+                             static_cast<const float *>(running_mean.data()),
+                             static_cast<const float *>(running_var.data()), out.data(), B, C, H, W, eps,
+                             code(in), nullptr));
+  }
+  void batch_norm_backward(const Storage &, const Storage &, const Storage &, const Storage &,
+                           const Storage &, Storage &, Storage &, Storage &, int, int, int, int,
+                           float) override { training_only("batch_norm_backward"); }
+
+  // ---- random -------------------------------------------------------------------------
+  void fill_uniform(Storage &out, float low, float high, size_t n) override {
+    check(mu_fill_uniform(ctx_, out.data(), static_cast<long long>(n), low, high, ++fill_calls_ * 0x9E3779B9ull,
+                          code(out), nullptr));
+  }
+
 private:
   mu_ctx *ctx_ = nullptr;
+  unsigned long long fill_calls_ = 41; // seeds successive fills differently, reproducibly per process
+  void math(int op, const Storage &in, Storage &out, size_t n) {
+    check(mu_unary(ctx_, op, in.data(), out.data(), static_cast<long long>(n), code(in), nullptr));
+  }
   static int code(const Storage &s) { return static_cast<int>(s.dtype()); } // same enum order
   void check(int rc) const {
     if (rc != MU_OK) throw std::runtime_error(std::string("B200Backend: ") + mu_last_error(ctx_));
@@ -185,10 +268,6 @@ private:
     }
     check(mu_binary_broadcast(ctx_, op, a.data(), b.data(), out.data(), nd, shape, sa, sb, code(a),
                               nullptr));
-  }
-  [[noreturn]] static void not_advertised(const char *op) {
-    throw std::runtime_error(std::string("B200Backend: '") + op +
-                             "' is not advertised by query_support and must not be dispatched here");
   }
   [[noreturn]] static void training_only(const char *op) {
     throw std::runtime_error(std::string("B200Backend: '") + op + "' is a training-only entry point");

@@ -49,3 +49,46 @@ def test_reference_engine_runs_mlp_on_b200_backend_bf16(ref_b200, tmp_path):
     h = oracle.port().linear(oracle.to_bf16(x), bt["0.weight"], bt["0.bias"], BF16, "gelu")
     want = oracle.from_bf16(oracle.port().linear(h, bt["2.weight"], bt["2.bias"], BF16))
     assert_close(got, want, F32, rtol=2e-2, what="reference Engine on B200Backend, bf16")
+
+
+def test_reference_engine_runs_unet_style_block_on_b200_backend(ref_b200, tmp_path):
+    """Conv2d → BatchNorm2d → LeakyReLU → Upsample → Conv2d → GlobalAvgPool2d → Flatten → RMSNorm
+    through MuNet's own Engine with every op dispatched to the B200 backend (conv, batch-norm
+    inference branch, relu/sub/mul/add of LeakyReLU, nearest upsample, the GAP matmul, mean,
+    rsqrt): float32, compared with the same modules of the CPU checker."""
+    from munet_b200.inference import save_deploy
+    rng = np.random.default_rng(41)
+    t = {
+        "0.weight": (rng.standard_normal((8, 3, 3, 3)) * 0.3).astype(np.float32),
+        "0.bias": (rng.standard_normal(8) * 0.1).astype(np.float32),
+        "1.weight": rng.standard_normal(8).astype(np.float32),
+        "1.bias": rng.standard_normal(8).astype(np.float32),
+        "1.running_mean": (rng.standard_normal(8) * 0.2).astype(np.float32),
+        "1.running_var": (rng.random(8) + 0.5).astype(np.float32),
+        "4.weight": (rng.standard_normal((4, 8, 3, 3)) * 0.2).astype(np.float32),
+        "4.bias": np.zeros(4, np.float32),
+        "7.weight": rng.standard_normal(4).astype(np.float32),
+    }
+    cfg = {"type": "Sequential", "layers": [
+        {"type": "Conv2d", "in_channels": 3, "out_channels": 8, "kernel_size": 3, "stride": 1, "padding": 1},
+        {"type": "BatchNorm2d", "num_features": 8, "eps": 1e-5, "momentum": 0.1},
+        {"type": "LeakyReLU", "negative_slope": 0.2},
+        {"type": "Upsample", "scale_factor": 2},
+        {"type": "Conv2d", "in_channels": 8, "out_channels": 4, "kernel_size": 3, "stride": 1, "padding": 1},
+        {"type": "GlobalAvgPool2d"},
+        {"type": "Flatten"},
+        {"type": "RMSNorm", "normalized_shape": 4, "eps": 1e-5}]}
+    path = str(tmp_path / "unet_block.npz")
+    save_deploy(path, cfg, t)
+    x = rng.random((2, 3, 10, 12), dtype=np.float32)
+    P = oracle.port()
+    h = P.conv2d(x, t["0.weight"], t["0.bias"], 1, 1)
+    h = P.batch_norm_eval(h, t["1.weight"], t["1.bias"], t["1.running_mean"], t["1.running_var"], F32)
+    h = P.leaky_relu(h, 0.2, F32).reshape(h.shape)
+    h = np.repeat(np.repeat(h, 2, axis=2), 2, axis=3)
+    h = P.conv2d(h, t["4.weight"], t["4.bias"], 1, 1)
+    h = P.global_avg_pool(h).reshape(2, 4)
+    want = P.rms_norm(h, t["7.weight"], F32)
+    got = ref_b200.engine_run_npz(path, x, F32)
+    assert got.shape == want.shape
+    assert_close(got, want, F32, what="reference Engine on B200Backend, UNet-style block")
