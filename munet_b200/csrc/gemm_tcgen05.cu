@@ -21,6 +21,7 @@
 #include "ptx.cuh"
 #include "epilogue_math.cuh"
 #include <cuda.h>
+#include <cstdlib>
 
 namespace mu {
 
@@ -28,11 +29,14 @@ constexpr int BM = 128;
 constexpr int BK = 64; // 64 bf16 = 128 bytes = one swizzle row
 constexpr int GEMM_THREADS = 320; // TMA warp, MMA warp, 8 epilogue warps
 
-template <int BN> struct GemmCfg {
+// CTAS = 2: a cluster of two CTAs shares one 256 x BN tile (tcgen05 cta_group::2). Each CTA
+// stages its own 128 rows of A and its own BN/2 columns of B, so a CTA moves a third less
+// shared-memory traffic per FLOP and the ring is deeper.
+template <int BN, int CTAS = 1> struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = (BN / CTAS) * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = CTAS == 2 ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int TMEM_COLS = 2 * BN;
   // epilogue staging: one [32 rows x 64 cols] bf16 box (128-byte rows) per epilogue warp
   static constexpr int OUT_BOX_BYTES = 32 * 128;
@@ -119,15 +123,16 @@ __device__ __forceinline__ void epi_half(const uint32_t (&r)[32], uint8_t *row, 
   }
 }
 
-template <int BN, bool B_KMAJOR>
+template <int BN, bool B_KMAJOR, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmC,
                          const __grid_constant__ CUtensorMap tmR, GemmShape sh, Epilogue ep,
                          int *status) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, CTAS>;
   constexpr int STAGES = Cfg::STAGES;
+  static_assert(CTAS == 1 || (CTAS == 2 && BN == 256), "CTA pairs are built for 256-column tiles");
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atoms.
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -143,10 +148,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int tiles_m = (sh.M + BM - 1) / BM;
+  // rank of this CTA inside its pair; the leader (rank 0) owns the full/tempty barriers and
+  // issues the MMAs. With CTAS == 1 every CTA is its own leader.
+  const int rank = CTAS == 2 ? static_cast<int>(cluster_ctarank()) : 0;
+  const bool leader = rank == 0;
+  const int tiles_m = (sh.M + BM * CTAS - 1) / (BM * CTAS);
   const int tiles_n = (sh.N + BN - 1) / BN;
   const int num_kb = (sh.K + BK - 1) / BK;
   const long long total_tiles = 1ll * tiles_m * tiles_n * sh.batch;
+  const long long tile0 = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -155,7 +165,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], 8);
+      mbar_init(&tempty_bar[b], 8 * CTAS);
     }
     for (int b = 0; b < 8; ++b)
       mbar_init(&res_bar[b], 1);
@@ -169,11 +179,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-    tmem_relinquish();
+    tmem_alloc_g<CTAS>(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish_g<CTAS>();
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (CTAS == 2)
+    cluster_sync_all(); // the peer's barriers are initialised before anything signals them
+  else
+    __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -183,7 +196,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (long long tile = tile0; tile < total_tiles && ok; tile += tile_step) {
         const int nt = static_cast<int>(tile % tiles_n);
         const int mt = static_cast<int>((tile / tiles_n) % tiles_m);
         const int bt = static_cast<int>(tile / (1ll * tiles_n * tiles_m));
@@ -195,16 +208,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           uint8_t *sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t *sb = sa + Cfg::A_BYTES;
-          mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          // the leader's barrier counts the bytes of both CTAs of a pair
+          if (leader)
+            mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES * CTAS);
           const int bta = sh.a_batched ? bt : 0, btb = sh.b_batched ? bt : 0;
-          tma_load_3d(sa, &tmA, &full_bar[stage], kb * BK, mt * BM, bta);
+          tma_load_3d_g<CTAS>(sa, &tmA, &full_bar[stage], kb * BK, (mt * CTAS + rank) * BM, bta);
           if (B_KMAJOR) {
-            tma_load_3d(sb, &tmB, &full_bar[stage], kb * BK, nt * BN, btb);
+            tma_load_3d_g<CTAS>(sb, &tmB, &full_bar[stage], kb * BK, nt * BN + rank * (BN / CTAS), btb);
           } else {
-            const int c0 = nt * BN + bt * sh.b_col_per_batch;
+            const int c0 = nt * BN + rank * (BN / CTAS) + bt * sh.b_col_per_batch;
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sb + j * 8192, &tmB, &full_bar[stage], c0 + j * 64, kb * BK, btb);
+            for (int j = 0; j < BN / CTAS / 64; ++j)
+              tma_load_3d_g<CTAS>(sb + j * 8192, &tmB, &full_bar[stage], c0 + j * 64, kb * BK, btb);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -221,13 +236,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(1u, 0u, B_KMAJOR ? 0u : 1u, BM, BN);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc(1u, 0u, B_KMAJOR ? 0u : 1u, BM * CTAS, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      for (long long tile = tile0; tile < total_tiles && ok; tile += tile_step, ++it) {
         const int buf = it & 1;
         const uint32_t use = static_cast<uint32_t>(it >> 1);
         if (!mbar_wait(&tempty_bar[buf], (use & 1) ^ 1)) {
@@ -251,16 +266,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             const uint64_t adesc = make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t bdesc = B_KMAJOR ? make_smem_desc(sb + k * 32, 16, 1024)
                                             : make_smem_desc(sb + k * 2048, 8192, 1024);
-            umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_g<CTAS>(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]); // smem slot reusable once these MMAs retire
+          umma_commit_g<CTAS>(&empty_bar[stage]); // smem slot reusable once these MMAs retire
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (ok)
-          umma_commit(&tfull_bar[buf]); // accumulator complete
+          umma_commit_g<CTAS>(&tfull_bar[buf]); // accumulator complete (both CTAs of a pair)
       }
     }
     __syncwarp();
@@ -280,9 +295,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int it = 0;
     int gcount = 0; // staged 64-column groups issued by this warp (phase of its residual barrier)
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+    auto release_accumulator = [&](int b) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (CTAS == 2 && !leader)
+          mbar_arrive_cluster(&tempty_bar[b], 0);
+        else
+          mbar_arrive(&tempty_bar[b]);
+      }
+    };
+    for (long long tile = tile0; tile < total_tiles && ok; tile += tile_step, ++it) {
       const int nt = static_cast<int>(tile % tiles_n);
-      const int mt = static_cast<int>((tile / tiles_n) % tiles_m);
+      const int mt = static_cast<int>((tile / tiles_n) % tiles_m) * CTAS + rank; // 128-row tile index
       const int bt = static_cast<int>(tile / (1ll * tiles_n * tiles_m));
       const int buf_idx = it & 1;
       const uint32_t use = static_cast<uint32_t>(it >> 1);
@@ -368,10 +393,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             ++gcount;
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0)
-          mbar_arrive(&tempty_bar[buf_idx]);
+        release_accumulator(buf_idx);
         continue;
       }
       const int m = mt * BM + q * 32 + lane;
@@ -465,19 +487,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive(&tempty_bar[buf_idx]);
+      release_accumulator(buf_idx);
     }
     if (lane == 0)
       bulk_wait<0>(); // every TMA store of this warp has completed before the CTA exits
   }
 
   tc_fence_before();
-  __syncthreads();
+  // A pair leaves together: the leader's MMAs read the peer's shared memory and the peer signals
+  // the leader's barriers, so neither may exit (or free TMEM) while the other still runs.
+  if constexpr (CTAS == 2)
+    cluster_sync_all();
+  else
+    __syncthreads();
   if (warp == 1)
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    tmem_dealloc_g<CTAS>(tmem_base, Cfg::TMEM_COLS);
 }
 
 // ---------------------------------------------------------------------------
@@ -606,13 +630,22 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
   const unsigned long long b_nb = s2.b_batched ? sh.batch : 1;
   const unsigned long long a_bs = s2.a_batched ? op.a_batch : 1ull * op.lda * sh.M;
   const int BN = sh.N > 128 ? 256 : (sh.N > 64 ? 128 : 64);
+  // CTA pairs (256 x 256 tiles) for the large, tile-rich problems; MU_GEMM_CTAS=1 in the
+  // environment keeps every problem on single CTAs (for A/B timing).
+  static const bool pairs_enabled = [] {
+    const char *e = getenv("MU_GEMM_CTAS");
+    return !(e && e[0] == '1');
+  }();
+  const long long pair_tiles = 1ll * ((sh.M + 2 * BM - 1) / (2 * BM)) * ((sh.N + BN - 1) / BN) * sh.batch;
+  const bool pairs = pairs_enabled && BN == 256 && sh.M >= 1024 && num_sms >= 2 && pair_tiles >= num_sms / 2;
+  const int CT = pairs ? 2 : 1;
   CUtensorMap tmA, tmB;
   if (!encode_map3(&tmA, op.a, sh.K, sh.M, a_nb, op.lda, a_bs, BK, BM))
     return 2;
   bool okb;
   if (op.b_kmajor) {
     const unsigned long long b_bs = s2.b_batched ? op.b_batch : 1ull * op.ldb * sh.N;
-    okb = encode_map3(&tmB, op.b, sh.K, sh.N, b_nb, op.ldb, b_bs, BK, BN);
+    okb = encode_map3(&tmB, op.b, sh.K, sh.N, b_nb, op.ldb, b_bs, BK, BN / CT);
   } else {
     const unsigned long long cols = b_slab ? 1ull * op.b_col_per_batch * sh.batch : sh.N;
     const unsigned long long b_bs = s2.b_batched ? op.b_batch : 1ull * op.ldb * sh.K;
@@ -632,7 +665,7 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
 
 #define MU_LAUNCH(BN_, KM_)                                                                      \
   do {                                                                                           \
-    auto kern = gemm_bf16_tcgen05_kernel<BN_, KM_>;                                              \
+    auto kern = gemm_bf16_tcgen05_kernel<BN_, KM_, 1>;                                           \
     static bool attr_set = false;                                                                \
     if (!attr_set) {                                                                             \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
@@ -643,6 +676,42 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
     kern<<<grid, GEMM_THREADS, GemmCfg<BN_>::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, s2, ep2,     \
                                                                    status);                       \
   } while (0)
+
+  // CTA pairs: clusters of two, as many as the device can hold at once (persistent).
+#define MU_LAUNCH_PAIR(KM_)                                                                      \
+  do {                                                                                           \
+    auto kern = gemm_bf16_tcgen05_kernel<256, KM_, 2>;                                           \
+    constexpr int smem = GemmCfg<256, 2>::SMEM_BYTES;                                            \
+    static int max_clusters = -1;                                                                \
+    cudaLaunchConfig_t cfg = {};                                                                 \
+    cudaLaunchAttribute at[1];                                                                   \
+    at[0].id = cudaLaunchAttributeClusterDimension;                                              \
+    at[0].val.clusterDim.x = 2, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;          \
+    cfg.blockDim = dim3(GEMM_THREADS), cfg.dynamicSmemBytes = smem, cfg.stream = stream;         \
+    cfg.attrs = at, cfg.numAttrs = 1;                                                            \
+    if (max_clusters < 0) {                                                                      \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=       \
+          cudaSuccess)                                                                           \
+        return 2;                                                                                \
+      cfg.gridDim = dim3(num_sms & ~1);                                                          \
+      int n = 0;                                                                                 \
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0)               \
+        return 2;                                                                                \
+      max_clusters = n;                                                                          \
+    }                                                                                            \
+    const long long nc = pair_tiles < max_clusters ? pair_tiles : max_clusters;                  \
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * nc));                                           \
+    if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmR, s2, ep2, status) != cudaSuccess)      \
+      return 2;                                                                                  \
+  } while (0)
+
+  if (pairs) {
+    if (op.b_kmajor)
+      MU_LAUNCH_PAIR(true);
+    else
+      MU_LAUNCH_PAIR(false);
+    return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  }
 
   if (op.b_kmajor) {
     if (BN == 256)
@@ -660,6 +729,7 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
       MU_LAUNCH(64, false);
   }
 #undef MU_LAUNCH
+#undef MU_LAUNCH_PAIR
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
 }
 

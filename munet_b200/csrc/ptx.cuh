@@ -188,6 +188,85 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
                    smem_u32(bar))
                : "memory");
 }
+// ---- CTA-pair forms (cta_group::2): the two CTAs of a cluster of 2 work on one 256-row tile.
+// Every tcgen05 instruction of a kernel uses one group, hence the template parameter G
+// (1 = the single-CTA forms above). Both CTAs allocate and free their own TMEM; only the
+// even-ranked ("leader") CTA issues MMAs and commits.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() { // every thread of every CTA of the cluster
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the mbarrier at the same shared-memory offset in CTA `cta` of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t *bar, uint32_t cta) {
+  asm volatile("{\n\t.reg .b32 ra;\n\t"
+               "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+               "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}" ::"r"(smem_u32(bar)),
+               "r"(cta)
+               : "memory");
+}
+template <int G> __device__ __forceinline__ void tmem_alloc_g(uint32_t *smem_out, uint32_t ncols) {
+  if constexpr (G == 1)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)), "r"(ncols) : "memory");
+  else
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)), "r"(ncols) : "memory");
+}
+template <int G> __device__ __forceinline__ void tmem_relinquish_g() {
+  if constexpr (G == 1)
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  else
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+template <int G> __device__ __forceinline__ void tmem_dealloc_g(uint32_t taddr, uint32_t ncols) {
+  if constexpr (G == 1)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  else
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// G == 2: M = 256 rows, A rows 0-127 and B columns 0-N/2 from the leader's shared memory, the
+// rest from the peer's (same offsets); each CTA's TMEM receives its 128 rows of D.
+template <int G>
+__device__ __forceinline__ void umma_f16_g(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                           uint32_t idesc, uint32_t accumulate) {
+  if constexpr (G == 1)
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+                 "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+  else
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+                 "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// G == 2: the arrival is delivered to the barrier at this offset in BOTH CTAs of the pair.
+template <int G> __device__ __forceinline__ void umma_commit_g(uint64_t *bar) {
+  if constexpr (G == 1)
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+  else
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+// G == 2: the tile lands in THIS CTA's shared memory, the byte count is reported to the
+// barrier at the same offset in the leader CTA (bit 24 of a shared::cluster address is the
+// low bit of the CTA rank). One data copy per CTA: no multicast.
+template <int G>
+__device__ __forceinline__ void tma_load_3d_g(void *smem_dst, const void *tmap, uint64_t *bar, int c0,
+                                              int c1, int c2) {
+  if constexpr (G == 1)
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+  else
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0),
+                 "r"(c1), "r"(c2)
+                 : "memory");
+}
 // 32 lanes × 32 consecutive fp32 columns: thread i of the warp gets lane
 // (base_lane + i), registers r[0..31] = columns col..col+31.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {

@@ -46,6 +46,26 @@ def test_linear_bf16_tcgen05(ctx, M, K, N, act):
     assert_close(got_simt, want, BF16, what="linear bf16 (cuda-core kernel)")
 
 
+@pytest.mark.parametrize("M,K,N", [(1152, 256, 3840), (1100, 200, 3800), (2560, 128, 2048)])
+@pytest.mark.parametrize("transB", [False, True])
+def test_linear_bf16_cta_pairs(ctx, M, K, N, transB):
+    """Shapes large enough for the CTA-pair (256 x 256 tile) kernel, ragged in M, N and K, with
+    bias + GELU + residual; weights as [K,N] (Linear) and as [N,K] (matmul with transB)."""
+    rng = np.random.default_rng(M + K + N)
+    x = rnd(rng, (M, K), BF16)
+    w = rnd(rng, (K, N), BF16, 1.0 / np.sqrt(K))
+    b, r = rnd(rng, (N,), BF16, 0.05), rnd(rng, (M, N), BF16)
+    P = oracle.port()
+    if not transB:
+        want = P.add(P.linear(x, w, b, BF16, "gelu"), r, BF16)
+        assert_close(dev_linear(ctx, x, w, b, BF16, "gelu", res=r), want, BF16, what="pair linear")
+    else:
+        c = empty_dev((M, N), BF16)
+        ctx.matmul(to_dev(x, BF16), to_dev(np.ascontiguousarray(w.T), BF16), c, M, K, N, BF16, transB=True)
+        ctx.check()
+        assert_close(to_host(c), P.matmul(x, w, BF16), BF16, what="pair matmul transB")
+
+
 @pytest.mark.parametrize("act", ["none", "relu", "gelu", "sigmoid", "tanh"])
 def test_linear_bf16_acts_residual(ctx, act):
     rng = np.random.default_rng(5)
