@@ -23,6 +23,10 @@ int launch_embedding(const int *, const void *, const void *, void *, long long,
 int launch_eltwise(const void *, const void *, const void *, void *, long long, int, int, int, int,
                    cudaStream_t);
 int launch_argmax(const void *, int *, long long, int, int, cudaStream_t);
+size_t gemm_tf32x3_scratch_bytes(int, int, int);
+int launch_gemm_tf32x3(const float *, long long, const float *, long long, int, float *, long long,
+                       const float *, const float *, float, int, int, int, int, void *, int *, int,
+                       cudaStream_t);
 int launch_attention_tcgen05(const void *, const void *, const void *, void *, int, int, int, int,
                              int, int, int *, cudaStream_t);
 } // namespace mu
@@ -32,6 +36,8 @@ struct mu_ctx {
   int num_sms = 0;
   int force_simt = 0;
   int *d_status = nullptr;
+  void *scratch = nullptr; // grow-only device buffer for the split operands of the 3xTF32 GEMM
+  size_t scratch_bytes = 0;
   char err[512] = {0};
 };
 
@@ -89,6 +95,42 @@ int run_gemm(mu_ctx *ctx, const mu::GemmOperands &op, const mu::GemmShape &sh, m
     if (rc == 2)
       return cuda_fail(ctx, who, cudaGetLastError());
     // rc == 1: shape or alignment outside the TMA kernel's envelope
+  }
+  // Large float32 products: tensor cores with every operand split in two TF32 parts (float32-class
+  // accuracy, not the reference's accumulation order). Below 2^31 multiply-adds the CUDA-core
+  // kernel keeps the reference's result bit for bit.
+  if (dtype == MU_F32 && !ctx->force_simt && sh.batch == 1 && ep.split_T == 0 && ep.batch_div <= 1 &&
+      1.0 * sh.M * sh.N * sh.K >= 2147483648.0 && sh.K % 4 == 0 && ep.ldc % 4 == 0) {
+    const size_t need = mu::gemm_tf32x3_scratch_bytes(sh.M, sh.N, sh.K);
+    bool have = ctx->scratch_bytes >= need;
+    if (!have) {
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      cudaStreamIsCapturing(st, &cap);
+      if (cap == cudaStreamCaptureStatusNone) { // never allocate inside a capture
+        cudaStreamSynchronize(st);
+        if (ctx->scratch)
+          cudaFree(ctx->scratch);
+        ctx->scratch = nullptr, ctx->scratch_bytes = 0;
+        if (cudaMalloc(&ctx->scratch, need) == cudaSuccess) {
+          ctx->scratch_bytes = need;
+          have = true;
+        } else {
+          cudaGetLastError(); // out of memory: the CUDA-core kernel needs no scratch
+        }
+      }
+    }
+    if (have) {
+      int rc = mu::launch_gemm_tf32x3(static_cast<const float *>(op.a), op.lda,
+                                      static_cast<const float *>(op.b), op.ldb, op.b_kmajor,
+                                      static_cast<float *>(ep.c), ep.ldc,
+                                      static_cast<const float *>(ep.bias),
+                                      static_cast<const float *>(ep.residual), ep.alpha, ep.act, sh.M,
+                                      sh.N, sh.K, ctx->scratch, ctx->d_status, ctx->num_sms, st);
+      if (rc == 0)
+        return MU_OK;
+      if (rc == 2)
+        return cuda_fail(ctx, who, cudaGetLastError());
+    }
   }
   mu::SimtArgs g;
   g.a = op.a, g.b = op.b, g.lda = op.lda, g.ldb = op.ldb;
@@ -154,6 +196,8 @@ void mu_ctx_destroy(mu_ctx *ctx) {
     return;
   if (ctx->d_status)
     cudaFree(ctx->d_status);
+  if (ctx->scratch)
+    cudaFree(ctx->scratch);
   delete ctx;
 }
 

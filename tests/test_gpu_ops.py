@@ -91,6 +91,37 @@ def test_linear_f32_bit_exact(ctx, M, K, N, act):
         f"max diff {np.abs(got - want).max()}"
 
 
+@pytest.mark.parametrize("M,K,N,act,res", [(2048, 1024, 1024, "none", False), (1300, 1284, 1300, "gelu", True),
+                                           (4100, 516, 1028, "relu", False)])
+def test_linear_f32_tensor_core_split(ctx, M, K, N, act, res):
+    """float32 products of 2^31 multiply-adds and more run on the tensor cores with every operand
+    split into two TF32 parts. Both that result and the CUDA-core kernel's (the reference's float
+    accumulation order) are compared with a float64 evaluation: the split product must be
+    float32-class — within 3e-5 of the truth (the config tolerance is 1e-4). The tensor core adds
+    into its accumulator with truncation, so the split product carries a small bias toward zero
+    that the sequential float sum does not have; summing K in chunks keeps it below 1e-5 of the
+    result's RMS whatever K is."""
+    rng = np.random.default_rng(M + N)
+    x = rnd(rng, (M, K), F32)
+    w = rnd(rng, (K, N), F32, 1.0 / np.sqrt(K))
+    b = rnd(rng, (N,), F32, 0.1)
+    r = rnd(rng, (M, N), F32) if res else None
+    t = x.astype(np.float64) @ w.astype(np.float64) + b
+    if act == "gelu":
+        t = t / (1.0 + np.exp(-1.702 * t))
+    elif act == "relu":
+        t = np.maximum(t, 0.0)
+    if res:
+        t = t + r
+    simt = dev_linear(ctx, x, w, b, F32, act, res=r, simt=True)
+    got = dev_linear(ctx, x, w, b, F32, act, res=r)
+    assert not np.array_equal(got, simt), "expected the tensor-core path, got the CUDA-core bits"
+    assert_close(got, t.astype(np.float32), F32, rtol=3e-5, what="3xTF32 linear vs float64")
+    assert_close(simt, t.astype(np.float32), F32, rtol=3e-5, what="CUDA-core linear vs float64")
+    rms = float(np.sqrt((t * t).mean()))
+    assert abs(float(((got - t) * np.sign(t)).mean())) < 1e-5 * rms
+
+
 @pytest.mark.parametrize("act", ["gelu", "sigmoid", "tanh"])
 def test_linear_f32_acts(ctx, act):
     rng = np.random.default_rng(9)
