@@ -38,6 +38,9 @@ struct GemmShape {
   int a_batched = 1;        // third TMA coordinate of A = batch index (else 0)
   int b_batched = 1;        // third TMA coordinate of B = batch index (else 0)
   int b_col_per_batch = 0;  // added to B's N coordinate per batch (B = column slab of a wide matrix)
+  // Tile order: panels of `panel_n` column tiles are swept over all row tiles before the next
+  // panel starts, so a panel of B stays in L2 while A streams past it (0 = one panel).
+  int panel_n = 0;
 };
 
 // Operand addressing in elements. A is row-major [M,K]. B is row-major [K,N]

@@ -66,6 +66,21 @@ def test_linear_bf16_cta_pairs(ctx, M, K, N, transB):
         assert_close(to_host(c), P.matmul(x, w, BF16), BF16, what="pair matmul transB")
 
 
+def test_linear_bf16_wide_weights_use_column_panels(ctx):
+    """A weight matrix wider than the L2 budget (here 49 MB) is swept in panels of column tiles,
+    the last one narrower. Every output tile must still be produced exactly once: compared with
+    the CUDA-core kernel on the whole output and with the CPU checker on a few rows."""
+    rng = np.random.default_rng(77)
+    M, K, N = 1100, 2048, 12032
+    x = rnd(rng, (M, K), BF16)
+    w = rnd(rng, (K, N), BF16, 1.0 / np.sqrt(K))
+    b = rnd(rng, (N,), BF16, 0.05)
+    got = dev_linear(ctx, x, w, b, BF16)
+    assert_close(got, dev_linear(ctx, x, w, b, BF16, simt=True), BF16, what="panels vs cuda-core kernel")
+    rows = [0, 127, 128, 255, 256, 700, 1023, 1024, 1099]
+    assert_close(got[rows], oracle.port().linear(x[rows], w, b, BF16), BF16, what="panels vs checker")
+
+
 @pytest.mark.parametrize("act", ["none", "relu", "gelu", "sigmoid", "tanh"])
 def test_linear_bf16_acts_residual(ctx, act):
     rng = np.random.default_rng(5)
