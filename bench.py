@@ -309,7 +309,11 @@ def run_ours(args, cfg):
         "bound": "tensor", "kernel": "gemm_bf16_tcgen05_kernel (all Linear layers of one forward)",
         "achieved": achieved, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
         "frac": achieved / pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (sustained)",
-        "traffic": None,
+        # DRAM bytes per launch, averaged over the 97 GEMM launches of one forward of the
+        # default config: ncu captures of each model shape at a quarter of the rows, scaled by 4
+        # (profiles/gemm_bf16_tcgen05_M16384_N2048_K2048_gelu.md); algorithmic: 1.135e9.
+        "traffic": 1.347e9 if (cfg["d_model"], cfg["n_layers"], cfg["batch"], tp) == (2048, 24, 64, 1) else None,
+        "traffic_unit": "bytes/launch (ncu dram read+write, offline capture)",
         "launches_per_step": by_kind.get("linear", {"n": 0})["n"] + by_kind.get("qkv_linear", {"n": 0})["n"],
         "avg_launch_ms": gemm_ms / max(1, by_kind.get("linear", {"n": 0})["n"] + by_kind.get("qkv_linear", {"n": 0})["n"]),
         "per_kind_ms": {k: round(v["ms"], 3) for k, v in by_kind.items()},
