@@ -297,7 +297,9 @@ int mu_engine_load_memory(mu_engine *engine, const char *config_json, int n_tens
 /* Tensor parallelism (no counterpart in the reference, which has none): options "tp_size" and
  * "tp_rank" plus a communicator of that size shard every decoder block Megatron-style —
  * q/k/v and fc1 by output columns (heads), out_proj and fc2 by input rows with an all-reduce
- * of the partial sums, the LM head by vocabulary columns (output = this rank's slab). */
+ * of the partial sums, the LM head by vocabulary columns (output = this rank's slab).
+ * Option "tp_overlap" (default 1) cuts the row-parallel layers into four row chunks and runs
+ * the all-reduce of one chunk on a second stream under the GEMM of the next. */
 int mu_engine_set_comm(mu_engine *engine, mu_comm *comm);
 int mu_engine_compile(mu_engine *engine, const int *input_shape, int ndim, int input_dtype);
 int mu_engine_output_shape(const mu_engine *engine, int *shape, int *ndim, int *dtype);

@@ -36,8 +36,6 @@ struct mu_ctx {
   int num_sms = 0;
   int force_simt = 0;
   int *d_status = nullptr;
-  void *scratch = nullptr; // grow-only device buffer for the split operands of the 3xTF32 GEMM
-  size_t scratch_bytes = 0;
   char err[512] = {0};
 };
 
@@ -101,35 +99,24 @@ int run_gemm(mu_ctx *ctx, const mu::GemmOperands &op, const mu::GemmShape &sh, m
   // kernel keeps the reference's result bit for bit.
   if (dtype == MU_F32 && !ctx->force_simt && sh.batch == 1 && ep.split_T == 0 && ep.batch_div <= 1 &&
       1.0 * sh.M * sh.N * sh.K >= 2147483648.0 && sh.K % 4 == 0 && ep.ldc % 4 == 0) {
+    // The split copies live in a stream-ordered allocation (pool-backed, legal inside a stream
+    // capture): concurrent calls on different streams never share scratch.
     const size_t need = mu::gemm_tf32x3_scratch_bytes(sh.M, sh.N, sh.K);
-    bool have = ctx->scratch_bytes >= need;
-    if (!have) {
-      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-      cudaStreamIsCapturing(st, &cap);
-      if (cap == cudaStreamCaptureStatusNone) { // never allocate inside a capture
-        cudaStreamSynchronize(st);
-        if (ctx->scratch)
-          cudaFree(ctx->scratch);
-        ctx->scratch = nullptr, ctx->scratch_bytes = 0;
-        if (cudaMalloc(&ctx->scratch, need) == cudaSuccess) {
-          ctx->scratch_bytes = need;
-          have = true;
-        } else {
-          cudaGetLastError(); // out of memory: the CUDA-core kernel needs no scratch
-        }
-      }
-    }
-    if (have) {
+    void *scratch = nullptr;
+    if (cudaMallocAsync(&scratch, need, st) == cudaSuccess) {
       int rc = mu::launch_gemm_tf32x3(static_cast<const float *>(op.a), op.lda,
                                       static_cast<const float *>(op.b), op.ldb, op.b_kmajor,
                                       static_cast<float *>(ep.c), ep.ldc,
                                       static_cast<const float *>(ep.bias),
                                       static_cast<const float *>(ep.residual), ep.alpha, ep.act, sh.M,
-                                      sh.N, sh.K, ctx->scratch, ctx->d_status, ctx->num_sms, st);
+                                      sh.N, sh.K, scratch, ctx->d_status, ctx->num_sms, st);
+      cudaFreeAsync(scratch, st);
       if (rc == 0)
         return MU_OK;
       if (rc == 2)
         return cuda_fail(ctx, who, cudaGetLastError());
+    } else {
+      cudaGetLastError(); // out of memory: the CUDA-core kernel needs no scratch
     }
   }
   mu::SimtArgs g;
@@ -187,6 +174,16 @@ int mu_ctx_create(int device, mu_ctx **out) {
     return MU_ERR_CUDA;
   }
   ctx->num_sms = prop.multiProcessorCount;
+  {
+    // Stream-ordered scratch (3xTF32 operand copies) is reused from the device's default pool:
+    // keep freed blocks cached instead of returning them to the driver at every synchronisation.
+    cudaMemPool_t pool = nullptr;
+    if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess && pool) {
+      unsigned long long keep = ~0ull;
+      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    cudaGetLastError();
+  }
   *out = ctx;
   return MU_OK;
 }
@@ -196,8 +193,6 @@ void mu_ctx_destroy(mu_ctx *ctx) {
     return;
   if (ctx->d_status)
     cudaFree(ctx->d_status);
-  if (ctx->scratch)
-    cudaFree(ctx->scratch);
   delete ctx;
 }
 

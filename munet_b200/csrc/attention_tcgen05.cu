@@ -626,12 +626,12 @@ int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *
 #define MU_ATT_LAUNCH(D_, L_)                                                                    \
   do {                                                                                           \
     auto kern = attention_tcgen05_kernel<D_, L_>;                                                \
-    static bool attr_set = false;                                                                \
-    if (!attr_set) {                                                                             \
+    static PerDeviceOnce attr_set;                                                               \
+    if (attr_set.get() < 0) {                                                                             \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
                                AttCfg<D_>::SMEM_BYTES) != cudaSuccess)                           \
         return 2;                                                                                \
-      attr_set = true;                                                                           \
+      attr_set.set(1);                                                                           \
     }                                                                                            \
     kern<<<grid, ATT_THREADS, AttCfg<D_>::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, prm, status); \
   } while (0)

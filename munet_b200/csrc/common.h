@@ -1,5 +1,6 @@
 // Internal shared definitions for the kernels and their host launchers.
 #pragma once
+#include <atomic>
 #include <cstdint>
 #include <cuda_runtime.h>
 
@@ -72,6 +73,29 @@ struct ConvArgs {
   float *y;
   int B, iC, iH, iW, oC, oH, oW, k, s, p;
   int relu, pool; // pool: 0 none, 2 = MaxPool2d(2,2,0) fused after the activation
+};
+
+// Per-device, thread-safe "done once" flags for settings that CUDA keeps per device (a kernel's
+// dynamic shared-memory limit, the number of co-resident clusters). Index = current device.
+struct PerDeviceOnce {
+  static constexpr int MAX_DEV = 64;
+  std::atomic<int> v[MAX_DEV];
+  PerDeviceOnce() {
+    for (auto &x : v)
+      x.store(-1);
+  }
+  // value cached for the current device, or -1
+  int get() const {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= MAX_DEV)
+      return -1;
+    return v[d].load(std::memory_order_acquire);
+  }
+  void set(int value) {
+    int d = 0;
+    if (cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < MAX_DEV)
+      v[d].store(value, std::memory_order_release);
+  }
 };
 
 } // namespace mu

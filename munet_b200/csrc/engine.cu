@@ -24,6 +24,7 @@
 #include <cstring>
 #include <cuda_runtime.h>
 #include <map>
+#include <set>
 #include <memory>
 #include <string>
 #include <vector>
@@ -56,6 +57,11 @@ struct Op {
   float eps = 1e-5f;
   long long n = 0;
   size_t ws_bytes = 0;
+  // Row chunk of a tensor-parallel row-parallel layer: the op works on rows [row0, row0 + M) of
+  // its tensors. `side` ops run on the engine's second stream (the all-reduce of one chunk under
+  // the GEMM of the next); `rec_ev` is recorded after the op, `wait_ev` awaited before it.
+  long long row0 = 0;
+  int side = 0, wait_ev = -1, rec_ev = -1;
 };
 
 struct Weight {
@@ -137,6 +143,9 @@ struct mu_engine {
     if (gexec) cudaGraphExecDestroy(gexec), gexec = nullptr;
     if (graph) cudaGraphDestroy(graph), graph = nullptr;
     if (cap_stream) cudaStreamDestroy(cap_stream), cap_stream = nullptr;
+    for (auto &ev : events) cudaEventDestroy(ev);
+    events.clear(), n_events = 0;
+    if (side_stream) cudaStreamDestroy(side_stream), side_stream = nullptr;
     if (weight_slab) mu_free(ctx, weight_slab), weight_slab = nullptr;
     if (arena) mu_free(ctx, arena), arena = nullptr;
     if (input_buf) mu_free(ctx, input_buf), input_buf = nullptr;
@@ -171,9 +180,13 @@ struct mu_engine {
     return idx;
   }
 
+  // Looks a tensor up by its dotted path and remembers that the module tree asked for it.
+  mutable std::set<std::string> used_params;
   const NamedTensor *find_param(const std::string &name) const {
     auto it = params.find(name);
-    return it == params.end() ? nullptr : &it->second;
+    if (it == params.end()) return nullptr;
+    used_params.insert(name);
+    return &it->second;
   }
 
   // Stage a parameter (converted to the compute dtype) into the weight slab.
@@ -274,6 +287,14 @@ struct mu_engine {
   int lower_block(const std::string &prefix, int d, int H, Val &v);
   int plan_and_allocate();
   int launch_all(cudaStream_t st);
+  int n_events = 0, tp_overlap = 1;
+  std::vector<cudaEvent_t> events;
+  cudaStream_t side_stream = nullptr;
+  // rows [row0, ...) of a [rows, cols] tensor (nullptr stays nullptr)
+  void *rows(int tid, long long row0, int cols) const {
+    void *p = tptr(tid);
+    return p ? static_cast<char *>(p) + static_cast<size_t>(row0) * cols * esize(dtype) : nullptr;
+  }
   int launch_op(const Op &op, cudaStream_t st);
   void op_work(const Op &op, double *flops, double *bytes) const;
   void *tptr(int tid) const {
@@ -330,20 +351,43 @@ int mu_engine::lower_linear(const std::string &prefix, int K, int N, bool bias, 
     // residual, like the unsharded layer
     if (act != MU_ACT_NONE) return fail(MU_ERR_INVALID, "row-parallel Linear cannot carry an activation");
     op.out = new_tensor(static_cast<size_t>(op.M) * Nl * esize(dtype));
-    push(op);
-    Op ar;
-    ar.kind = OP_ALLREDUCE, ar.in = op.out, ar.out = op.out, ar.n = 1ll * op.M * Nl;
-    push(ar);
-    Op e;
-    e.kind = OP_ELTWISE, e.in = op.out, e.b = bias_id, e.N = Nl, e.n = 1ll * op.M * Nl, e.res = res_tid;
+    int e_out;
     if (res_tid >= 0) {
-      e.out = new_tensor(0);
-      tensors[e.out].alias_of = root(res_tid);
+      e_out = new_tensor(0);
+      tensors[e_out].alias_of = root(res_tid);
     } else {
-      e.out = op.out;
+      e_out = op.out;
     }
-    push(e);
-    v.tid = e.out;
+    // Rows are cut into chunks so that the all-reduce of chunk i (second stream) runs under the
+    // GEMM of chunk i+1; the bias/residual pass of a chunk waits for its all-reduce.
+    const int Mtot = op.M;
+    int chunks = (tp_overlap && Mtot >= 4096) ? 4 : 1;
+    const int rows_per = ((Mtot + chunks - 1) / chunks + 255) / 256 * 256;
+    chunks = (Mtot + rows_per - 1) / rows_per;
+    std::vector<int> done_ev(chunks, -1);
+    for (int c = 0; c < chunks; ++c) {
+      Op g = op;
+      g.row0 = 1ll * c * rows_per, g.M = std::min(rows_per, Mtot - c * rows_per);
+      Op ar;
+      ar.kind = OP_ALLREDUCE, ar.in = op.out, ar.out = op.out, ar.row0 = g.row0, ar.N = Nl;
+      ar.n = 1ll * g.M * Nl;
+      if (chunks > 1) {
+        g.rec_ev = n_events++;
+        ar.side = 1, ar.wait_ev = g.rec_ev, ar.rec_ev = n_events++;
+        done_ev[c] = ar.rec_ev;
+      }
+      push(g);
+      push(ar);
+    }
+    for (int c = 0; c < chunks; ++c) {
+      Op e;
+      e.kind = OP_ELTWISE, e.in = op.out, e.b = bias_id, e.N = Nl, e.res = res_tid, e.out = e_out;
+      e.row0 = 1ll * c * rows_per;
+      e.n = 1ll * std::min(rows_per, Mtot - c * rows_per) * Nl;
+      e.wait_ev = done_ev[c];
+      push(e);
+    }
+    v.tid = e_out;
     v.shape.back() = Nl;
     return MU_OK;
   }
@@ -786,9 +830,24 @@ int mu_engine::plan_and_allocate() {
 
 int mu_engine::launch_all(cudaStream_t st) {
   n_launches = 0;
+  if (n_events > 0 && events.empty()) {
+    events.resize(n_events);
+    for (auto &ev : events)
+      if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess)
+        return fail(MU_ERR_CUDA, "event creation failed");
+    if (cudaStreamCreateWithFlags(&side_stream, cudaStreamNonBlocking) != cudaSuccess)
+      return fail(MU_ERR_CUDA, "stream creation failed");
+  }
   for (const Op &op : ops) {
-    int rc = launch_op(op, st);
+    // the second stream only ever runs work that waits on an event of `st`, and `st` waits on
+    // every event the second stream records: both a plain run and a stream capture stay joined
+    cudaStream_t s = op.side ? side_stream : st;
+    if (op.wait_ev >= 0 && cudaStreamWaitEvent(s, events[op.wait_ev], 0) != cudaSuccess)
+      return fail(MU_ERR_CUDA, "stream wait failed");
+    int rc = launch_op(op, s);
     if (rc) return rc;
+    if (op.rec_ev >= 0 && cudaEventRecord(events[op.rec_ev], s) != cudaSuccess)
+      return fail(MU_ERR_CUDA, "event record failed");
   }
   return MU_OK;
 }
@@ -808,8 +867,8 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       n_launches += 1;
       break;
     case OP_LINEAR:
-      rc = mu_linear(ctx, tptr(op.in), wptr(op.w), wptr(op.b), tptr(op.res), tptr(op.out), op.M, op.K,
-                     op.N, op.act, dtype, st);
+      rc = mu_linear(ctx, rows(op.in, op.row0, op.K), wptr(op.w), wptr(op.b), rows(op.res, op.row0, op.N),
+                     rows(op.out, op.row0, op.N), op.M, op.K, op.N, op.act, dtype, st);
       n_launches += 1;
       break;
     case OP_QKV: {
@@ -829,12 +888,12 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       break;
     }
     case OP_ELTWISE:
-      rc = mu_eltwise(ctx, tptr(op.in), wptr(op.b), tptr(op.res), tptr(op.out), op.n,
-                      op.b >= 0 ? op.N : 1, op.act, dtype, st);
+      rc = mu_eltwise(ctx, rows(op.in, op.row0, op.N), wptr(op.b), rows(op.res, op.row0, op.N),
+                      rows(op.out, op.row0, op.N), op.n, op.b >= 0 ? op.N : 1, op.act, dtype, st);
       n_launches += 1;
       break;
     case OP_ALLREDUCE:
-      rc = mu_all_reduce_sum(ctx, comm, tptr(op.in), op.n, dtype, st);
+      rc = mu_all_reduce_sum(ctx, comm, rows(op.in, op.row0, op.N), op.n, dtype, st);
       n_launches += 1;
       break;
     case OP_ARGMAX:
@@ -1014,6 +1073,7 @@ int mu_engine_set_option(mu_engine *e, const char *name, int value) {
   else if (n == "argmax") e->want_argmax = value;
   else if (n == "tp_rank") e->tp_rank = value;
   else if (n == "tp_size") e->tp_size = value;
+  else if (n == "tp_overlap") e->tp_overlap = value;
   else return e->fail(MU_ERR_INVALID, "unknown option '%s'", name);
   return MU_OK;
 }
@@ -1095,8 +1155,17 @@ int mu_engine_compile(mu_engine *e, const int *input_shape, int ndim, int input_
   e->input_bytes = static_cast<size_t>(v.numel()) * esize(input_dtype);
   v.tid = e->new_tensor(e->input_bytes);
   e->tensors[v.tid].external = true;
+  e->used_params.clear();
   int rc = e->lower(e->config, "", v, nullptr, nullptr);
   if (rc) return rc;
+  // Every serialized tensor must belong to a module of the tree, as in the reference's loader
+  // (src/inference_serialization.cpp:1043-1051). BatchNorm2d's momentum-only state and Dropout
+  // have no tensors, so anything left over is a mismatch between config and payload.
+  for (const auto &kv : e->params)
+    if (!e->used_params.count(kv.first))
+      return e->fail(MU_ERR_INVALID,
+                     "Serialized tensor '%s' does not match any named parameter/buffer in the "
+                     "reconstructed module", kv.first.c_str());
   e->out_tid = v.tid, e->out_shape = v.shape, e->out_dtype = v.dtype;
   if (e->want_argmax) {
     Op a;

@@ -691,12 +691,12 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
 #define MU_LAUNCH(BN_, KM_)                                                                      \
   do {                                                                                           \
     auto kern = gemm_bf16_tcgen05_kernel<BN_, KM_, 1>;                                           \
-    static bool attr_set = false;                                                                \
-    if (!attr_set) {                                                                             \
+    static PerDeviceOnce attr_set;                                                               \
+    if (attr_set.get() < 0) {                                                                             \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
                                GemmCfg<BN_>::SMEM_BYTES) != cudaSuccess)                         \
         return 2;                                                                                \
-      attr_set = true;                                                                           \
+      attr_set.set(1);                                                                           \
     }                                                                                            \
     kern<<<grid, GEMM_THREADS, GemmCfg<BN_>::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmR, s2, ep2,     \
                                                                    status);                       \
@@ -707,7 +707,8 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
   do {                                                                                           \
     auto kern = gemm_bf16_tcgen05_kernel<256, KM_, 2>;                                           \
     constexpr int smem = GemmCfg<256, 2>::SMEM_BYTES;                                            \
-    static int max_clusters = -1;                                                                \
+    static PerDeviceOnce cluster_cache;                                                          \
+    int max_clusters = cluster_cache.get();                                                      \
     cudaLaunchConfig_t cfg = {};                                                                 \
     cudaLaunchAttribute at[1];                                                                   \
     at[0].id = cudaLaunchAttributeClusterDimension;                                              \
@@ -723,6 +724,7 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
       if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0)               \
         return 2;                                                                                \
       max_clusters = n;                                                                          \
+      cluster_cache.set(n);                                                                      \
     }                                                                                            \
     const long long nc = pair_tiles < max_clusters ? pair_tiles : max_clusters;                  \
     cfg.gridDim = dim3(static_cast<unsigned>(2 * nc));                                           \

@@ -424,12 +424,12 @@ int launch_gemm_tf32x3(const float *a, long long lda, const float *b, long long 
   T3Args g;
   g.M = M, g.N = N, g.K = K, g.act = act, g.has_bias = bias != nullptr, g.has_res = residual != nullptr;
   g.alpha = alpha, g.bias = bias;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_set;
+  if (attr_set.get() < 0) {
     if (cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T3_SMEM) !=
         cudaSuccess)
       return 2;
-    attr_set = true;
+    attr_set.set(1);
   }
   const long long tiles = 1ll * ((M + T3_BM - 1) / T3_BM) * ((N + T3_BN - 1) / T3_BN);
   const unsigned grid = static_cast<unsigned>(tiles < num_sms ? tiles : num_sms);

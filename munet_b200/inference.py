@@ -101,11 +101,69 @@ def inspect_artifact(path: str) -> dict:
     return json.loads(out.value.decode())
 
 
+class PreparedInputCache:
+    """Device copies of host inputs, keyed by the identity and version of the host object:
+    the reference's ``detail::PreparedInputCache`` (src/inference.hpp:186-289). Same policy:
+    at most ``max_entries`` entries and ``max_bytes`` bytes, a value larger than ``max_bytes`` is
+    not cached, storing under an identity that is already present replaces it, and room is made
+    by evicting the oldest entries first. ``store`` returns the number of evictions."""
+
+    def __init__(self, max_entries: int = 8, max_bytes: int = 64 * 1024 * 1024):
+        self.configure(max_entries, max_bytes)
+
+    def configure(self, max_entries: int, max_bytes: int):
+        self.max_entries, self.max_bytes = int(max_entries), int(max_bytes)
+        self.reset()
+
+    def reset(self):
+        self._entries = []  # [identity, version, value, nbytes], oldest first
+        self.current_bytes = 0
+
+    def find(self, identity, version):
+        for ident, ver, value, _ in self._entries:
+            if ident == identity and ver == version:
+                return value
+        return None
+
+    def store(self, identity, version, value, nbytes: int) -> int:
+        if value is None or self.max_entries == 0 or self.max_bytes == 0 or nbytes > self.max_bytes:
+            return 0
+        for i, e in enumerate(self._entries):
+            if e[0] == identity:
+                self.current_bytes -= e[3]
+                del self._entries[i]
+                break
+        evictions = 0
+        while self._entries and (len(self._entries) >= self.max_entries
+                                 or self.current_bytes + nbytes > self.max_bytes):
+            self.current_bytes -= self._entries[0][3]
+            del self._entries[0]
+            evictions += 1
+        self._entries.append([identity, version, value, nbytes])
+        self.current_bytes += nbytes
+        return evictions
+
+    def __len__(self):
+        return len(self._entries)
+
+
+def _input_identity(x):
+    """(identity, version) of a host input, or None when changes to it cannot be noticed.
+    torch CPU tensors carry a version counter (bumped by in-place ops, like the reference's
+    ``Tensor::version``); a numpy array only qualifies when it is read-only."""
+    if hasattr(x, "_version") and hasattr(x, "data_ptr"):
+        return (id(x), x.data_ptr()), int(x._version)
+    if isinstance(x, np.ndarray) and not x.flags.writeable:
+        return (id(x), x.ctypes.data), 0
+    return None
+
+
 class Engine:
     """``load`` → ``compile`` → ``run``; one instance per device context."""
 
     def __init__(self, ctx: Context | None = None, device: int = 0, compute_dtype: int = F32,
-                 kmode: int = 0, use_graph: bool = True, argmax: bool = False, comm=None):
+                 kmode: int = 0, use_graph: bool = True, argmax: bool = False, comm=None,
+                 tp_overlap: bool = True):
         self._lib = lib()
         self.ctx = ctx or Context(device)
         self.compute_dtype = compute_dtype
@@ -123,9 +181,75 @@ class Engine:
         if comm is not None and comm.world > 1:  # tensor-parallel shard of the decoder blocks
             self._opt("tp_size", comm.world)
             self._opt("tp_rank", comm.rank)
+            self._opt("tp_overlap", int(tp_overlap))
             self._rc(self._lib.mu_engine_set_comm(self._h, comm._h))
         self.input_shape = None
         self.output_shape = None
+        # host-side bookkeeping with the reference's names (EngineStats, src/inference.hpp:43-68)
+        self._cache = PreparedInputCache()
+        self._estats = {"runs": 0, "load_to_device_ms": 0.0, "compile_ms": 0.0, "last_run_ms": 0.0,
+                        "last_prepare_input_ms": 0.0, "last_forward_ms": 0.0,
+                        "compiled_input_shape": [], "compiled_output_shape": [],
+                        "prepared_input_cache_hits": 0, "prepared_input_cache_misses": 0,
+                        "prepared_input_cache_evictions": 0}
+        self._observer = None
+
+    # -- reference-style configuration and bookkeeping ------------------------------
+    def set_observer(self, observer):
+        """``observer(event: dict)`` is called for load/compile/run completion and errors
+        (EngineEvent, src/inference.hpp:70-92)."""
+        self._observer = observer
+
+    def _emit(self, kind, duration_ms=0.0, message=""):
+        if self._observer is not None:
+            self._observer({"type": kind, "device": ("cuda", self.ctx.device), "run_index": self._estats["runs"],
+                            "duration_ms": duration_ms, "input_shape": list(self.input_shape or ()),
+                            "output_shape": list(self.output_shape or ()), "message": message})
+
+    def set_prepared_input_cache_entries(self, entries: int):
+        self._cache.configure(entries, self._cache.max_bytes)
+
+    def set_prepared_input_cache_max_bytes(self, nbytes: int):
+        self._cache.configure(self._cache.max_entries, nbytes)
+
+    def clear_prepared_input_cache(self):
+        self._cache.reset()
+
+    @property
+    def engine_stats(self) -> dict:
+        """EngineStats of the reference plus the executor's plan figures (``stats()``)."""
+        d = dict(self._estats)
+        d["prepared_input_cache_entries"] = len(self._cache)
+        d["prepared_input_cache_bytes"] = self._cache.current_bytes
+        return d
+
+    def _prepared(self, x):
+        """Device copy of a host input through the cache; None when the input cannot be keyed."""
+        key = _input_identity(x)
+        if key is None:
+            return None
+        hit = self._cache.find(*key)
+        if hit is not None:
+            self._estats["prepared_input_cache_hits"] += 1
+            return hit
+        self._estats["prepared_input_cache_misses"] += 1
+        import torch
+        t = x if hasattr(x, "data_ptr") else torch.from_numpy(x)
+        if tuple(t.shape) != self.input_shape:
+            raise MuNetError(1, f"Engine: input shape {tuple(t.shape)} does not match compiled "
+                                f"contract {self.input_shape}")
+        dev = t.contiguous().to(torch.device("cuda", self.ctx.device))
+        self._estats["prepared_input_cache_evictions"] += self._cache.store(
+            key[0], key[1], dev, dev.numel() * dev.element_size())
+        return dev
+
+    def prepare_batch(self, inputs):
+        """Engine::prepare_batch (src/inference.hpp:368-382): move the inputs to the device ahead
+        of the runs; ``run`` on the same (unchanged) host object then skips the copy."""
+        if self.input_shape is None:
+            raise MuNetError(1, "Engine: prepare_batch() called before compile()")
+        for x in inputs:
+            self._prepared(x)
 
     def _rc(self, rc):
         if rc:
@@ -149,8 +273,16 @@ class Engine:
     def load(self, source, tensors=None, tensor_dtype: int | None = None):
         """``load(path)`` reads a deploy artifact; ``load(config_dict, tensors)`` takes the
         module tree and named tensors (numpy float32 / uint16-bf16, or torch CUDA tensors)."""
+        import time
+        t0 = time.perf_counter()
         if isinstance(source, str):
-            self._rc(self._lib.mu_engine_load(self._h, source.encode(), self.compute_dtype))
+            try:
+                self._rc(self._lib.mu_engine_load(self._h, source.encode(), self.compute_dtype))
+            except MuNetError as e:
+                self._emit("error", message=f"load failed: {e}")
+                raise
+            self._estats["load_to_device_ms"] = (time.perf_counter() - t0) * 1e3
+            self._emit("load_completed", self._estats["load_to_device_ms"])
             return self
         names = list(tensors)
         n = len(names)
@@ -182,13 +314,21 @@ class Engine:
             (C.c_char_p * n)(*[k.encode() for k in names]), (C.c_void_p * n)(*ptrs),
             (C.c_int * n)(*dts), (C.c_int * n)(*nds), (C.c_longlong * max(len(shp), 1))(*shp),
             int(on_device), self.compute_dtype))
+        self._estats["load_to_device_ms"] = (time.perf_counter() - t0) * 1e3
+        self._emit("load_completed", self._estats["load_to_device_ms"])
         return self
 
     # -- compile ---------------------------------------------------------------
     def compile(self, input_shape, input_dtype: int | None = None):
+        import time
+        t0 = time.perf_counter()
         shape = tuple(int(s) for s in input_shape)
         dt = self.compute_dtype if input_dtype is None else input_dtype
-        self._rc(self._lib.mu_engine_compile(self._h, (C.c_int * len(shape))(*shape), len(shape), dt))
+        try:
+            self._rc(self._lib.mu_engine_compile(self._h, (C.c_int * len(shape))(*shape), len(shape), dt))
+        except MuNetError as e:
+            self._emit("error", message=f"compile failed: {e}")
+            raise
         self._keep = None  # weights now live in the engine's slab
         self.input_shape, self.input_dtype = shape, dt
         out = (C.c_int * 8)()
@@ -196,6 +336,10 @@ class Engine:
         self._rc(self._lib.mu_engine_output_shape(self._h, out, C.byref(nd), C.byref(odt)))
         self.output_shape = tuple(out[i] for i in range(nd.value))
         self.output_dtype = odt.value
+        self._cache.reset()
+        self._estats.update(compile_ms=(time.perf_counter() - t0) * 1e3,
+                            compiled_input_shape=list(shape), compiled_output_shape=list(self.output_shape))
+        self._emit("compile_completed", self._estats["compile_ms"])
         return self
 
     def stats(self) -> dict:
@@ -210,10 +354,27 @@ class Engine:
         the engine's arena (returned as raw device pointer via ``output_ptr``) unless ``out``."""
         if self.input_shape is None:
             raise MuNetError(1, "Engine: run() called before compile()")
-        host_in = isinstance(x, np.ndarray)
+        import time
+        t0 = time.perf_counter()
+        self._estats["last_prepare_input_ms"] = 0.0
+        host_in = isinstance(x, np.ndarray) or (hasattr(x, "is_cuda") and not x.is_cuda)
         if tuple(x.shape) != self.input_shape:
+            self._emit("error", message="run failed: shape contract")
             raise MuNetError(1, f"Engine: input shape {tuple(x.shape)} does not match compiled "
                                 f"contract {self.input_shape}")
+        if host_in and len(self._cache) and _input_identity(x) is not None \
+                and self._cache.find(*_input_identity(x)) is not None:
+            dev = self._prepared(x)  # prepared earlier and unchanged since: no host copy
+            self._estats["last_prepare_input_ms"] = (time.perf_counter() - t0) * 1e3
+            if out is None:
+                out = np.empty(self.output_shape, _NP[self.output_dtype])
+            am = np.empty(self.output_shape[:-1], np.int32) if self.argmax else None
+            self._rc(self._lib.mu_engine_run(self._h, dev.data_ptr(), 0, out.ctypes.data, 1,
+                                             None if am is None else am.ctypes.data, 1, _stream(stream)))
+            self._ran(t0)
+            return (out, am) if self.argmax else out
+        if host_in and not isinstance(x, np.ndarray):
+            x = x.numpy()
         if host_in:
             x = np.ascontiguousarray(x, dtype=_NP[self.input_dtype])
             xin = x.ctypes.data
@@ -223,11 +384,21 @@ class Engine:
             self._rc(self._lib.mu_engine_run(self._h, xin, 1, out.ctypes.data, 1,
                                              None if am is None else am.ctypes.data, 1,
                                              _stream(stream)))
+            self._ran(t0)
             return (out, am) if self.argmax else out
         self._rc(self._lib.mu_engine_run(self._h, x.data_ptr(), 0,
                                          None if out is None else out.data_ptr(), 0, None, 0,
                                          _stream(stream)))
+        self._ran(t0)
         return out
+
+    def _ran(self, t0):
+        import time
+        ms = (time.perf_counter() - t0) * 1e3
+        self._estats["runs"] += 1
+        self._estats["last_run_ms"] = ms
+        self._estats["last_forward_ms"] = ms - self._estats["last_prepare_input_ms"]
+        self._emit("run_completed", ms)
 
     OP_KINDS = ["embed", "layer_norm", "linear", "qkv_linear", "attention", "eltwise", "argmax",
                 "conv2d", "max_pool2d", "global_avg_pool", "all_reduce", "batch_norm", "upsample",
@@ -248,7 +419,15 @@ class Engine:
 
     def run_batch(self, inputs, stream=None):
         """Engine::run_batch (src/inference.hpp:612-627): independent inputs, one run each."""
-        return [self.run(x, stream=stream) for x in inputs]
+        outputs = []
+        self.run_batch_into(inputs, outputs, stream=stream)
+        return outputs
+
+    def run_batch_into(self, inputs, outputs: list, stream=None):
+        """Engine::run_batch_into: ``outputs`` is cleared and receives one result per input."""
+        outputs.clear()
+        for x in inputs:
+            outputs.append(self.run(x, stream=stream))
 
     @property
     def output_ptr(self) -> int:

@@ -140,3 +140,51 @@ def test_contract_and_errors(ctx, tmp_path):
     eng.close()
     with pytest.raises(mb.MuNetError, match="Unable to open"):
         make_engine(ctx, F32).load(str(tmp_path / "missing.npz"))
+    # a payload tensor no module of the tree claims (src/inference_serialization.cpp:1043-1051)
+    extra = str(tmp_path / "extra.npz")
+    save_deploy(extra, {"type": "Linear", "in_features": 2, "out_features": 2, "bias": False},
+                {"weight": np.eye(2, dtype=np.float32), "bias": np.zeros(2, np.float32)})
+    eng = make_engine(ctx, F32).load(extra)
+    with pytest.raises(mb.MuNetError, match="'bias' does not match any named parameter"):
+        eng.compile((1, 2))
+    eng.close()
+
+
+def test_prepared_inputs_stats_and_observer(ctx, tmp_path):
+    """Engine::prepare_batch / run_batch_into / EngineStats / observer (src/inference.hpp:43-92,
+    368-382, 612-637): a prepared, unchanged host input is served from its device copy, an input
+    changed in place is not, and the counters and events say so."""
+    import torch
+    import munet_b200 as mb
+    rng = np.random.default_rng(3)
+    path, tensors = mlp_artifact(tmp_path, rng, [8, 16, 4], ["ReLU"])
+    events = []
+    eng = make_engine(ctx, F32)
+    eng.set_observer(events.append)
+    eng.load(path).compile((5, 8))
+    xs = [torch.from_numpy(rng.standard_normal((5, 8)).astype(np.float32)) for _ in range(3)]
+    want = [mlp_oracle(x.numpy(), tensors, ["ReLU"]) for x in xs]
+    eng.prepare_batch(xs)
+    st = eng.engine_stats
+    assert st["prepared_input_cache_entries"] == 3 and st["prepared_input_cache_misses"] == 3
+    assert st["prepared_input_cache_bytes"] == 3 * 5 * 8 * 4
+    outs = []
+    eng.run_batch_into(xs, outs)
+    for o, w in zip(outs, want):
+        assert np.array_equal(o, w)
+    st = eng.engine_stats
+    assert st["prepared_input_cache_hits"] == 3 and st["runs"] == 3
+    assert st["compiled_input_shape"] == [5, 8] and st["compiled_output_shape"] == [5, 4]
+    xs[0].mul_(2.0)  # in-place change: the cached copy is stale and must not be used
+    assert np.array_equal(eng.run(xs[0]), mlp_oracle(xs[0].numpy(), tensors, ["ReLU"]))
+    assert eng.engine_stats["prepared_input_cache_hits"] == 3
+    eng.set_prepared_input_cache_entries(1)  # reconfiguring drops the entries
+    eng.prepare_batch(xs)
+    st = eng.engine_stats
+    assert st["prepared_input_cache_entries"] == 1 and st["prepared_input_cache_evictions"] == 2
+    kinds = [e["type"] for e in events]
+    assert kinds[:2] == ["load_completed", "compile_completed"] and kinds.count("run_completed") == 4
+    with pytest.raises(mb.MuNetError):
+        eng.run(np.zeros((4, 8), np.float32))
+    assert events[-1]["type"] == "error"
+    eng.close()

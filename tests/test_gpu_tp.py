@@ -23,7 +23,7 @@ def _n_gpus():
         return 0
 
 
-def _worker(rank, world, port, dtype, uid_q, res_q):
+def _worker(rank, world, port, dtype, uid_q, res_q, B=2, T=64):
     import torch
     import munet_b200 as mb
     from munet_b200.inference import Engine, gpt_decoder_config, gpt_param_names
@@ -47,23 +47,29 @@ def _worker(rank, world, port, dtype, uid_q, res_q):
     comm.check()
     red = buf.view(torch.int16).cpu().numpy().view(np.uint16) if dtype == BF16 else buf.cpu().numpy()
     # decoder forward, sharded over the two ranks
-    B, T, V, d, H, L = 2, 64, 128, 256, 4, 2
+    V, d, H, L = 128, 256, 4, 2
     prng = np.random.default_rng(5)
     ps = gpt_params(prng, V, T, d, L, dtype, std=0.05)
     ids = prng.integers(0, V, (B, T)).astype(np.int32)
-    eng = Engine(ctx=ctx, compute_dtype=dtype, comm=comm, kmode=mb.K_MATH)
-    eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)), tensor_dtype=dtype)
-    eng.compile((B, T), I32)
-    slab = eng.run(ids)  # [B, T, V / world]: this rank's vocabulary columns
-    res_q.put((rank, red, slab))
-    eng.close()
+    slabs = []
+    for overlap in (True, False):  # row chunks + all-reduce on a second stream, then the plain order
+        eng = Engine(ctx=ctx, compute_dtype=dtype, comm=comm, kmode=mb.K_MATH, tp_overlap=overlap)
+        eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)), tensor_dtype=dtype)
+        eng.compile((B, T), I32)
+        slabs.append(eng.run(ids))  # [B, T, V / world]: this rank's vocabulary columns
+        slabs.append(eng.run(ids))  # graph replay gives the same bits
+        eng.close()
+    assert np.array_equal(slabs[0], slabs[1]) and np.array_equal(slabs[0], slabs[2])
+    res_q.put((rank, red, slabs[0]))
     comm.close()
     ctx.close()
 
 
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("dtype", [BF16, F32])
-def test_tensor_parallel_decoder_and_all_reduce(dtype):
+@pytest.mark.parametrize("dtype,B,T", [(BF16, 2, 64), (F32, 2, 64), (BF16, 8, 512)])
+def test_tensor_parallel_decoder_and_all_reduce(dtype, B, T):
+    """The last case has 4096 token rows: the row-parallel layers run as four row chunks with
+    the all-reduce of each on a second stream."""
     import torch.multiprocessing as mp
     world = 2
     s = socket.socket()
@@ -72,7 +78,7 @@ def test_tensor_parallel_decoder_and_all_reduce(dtype):
     s.close()
     mpc = mp.get_context("spawn")
     uid_q, res_q = mpc.Queue(), mpc.Queue()
-    procs = [mpc.Process(target=_worker, args=(r, world, port, dtype, uid_q, res_q)) for r in range(world)]
+    procs = [mpc.Process(target=_worker, args=(r, world, port, dtype, uid_q, res_q, B, T)) for r in range(world)]
     for p in procs:
         p.start()
     results = dict()
@@ -90,7 +96,7 @@ def test_tensor_parallel_decoder_and_all_reduce(dtype):
     for r in range(world):
         assert np.array_equal(results[r][0], want_sum)
     # sharded forward == unsharded checker (logits slabs concatenated along the vocabulary)
-    B, T, V, d, H, L = 2, 64, 128, 256, 4, 2
+    V, d, H, L = 128, 256, 4, 2
     prng = np.random.default_rng(5)
     ps = gpt_params(prng, V, T, d, L, dtype, std=0.05)
     ids = prng.integers(0, V, (B, T)).astype(np.int32)
