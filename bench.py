@@ -219,7 +219,7 @@ def run_ours(args, cfg):
             raise SystemExit("--tp N runs one tensor-parallel group: launch exactly N ranks")
         comm = mb.Comm.from_torch_distributed(ctx)
     eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_MATH if tp > 1 else mb.K_LITERAL,
-                 argmax=tp == 1, comm=comm)
+                 argmax=tp == 1, comm=comm, tp_overlap=bool(args.tp_overlap))
     eng.load(gpt_decoder_config(V, T, d, H, L), tensors)
     eng.compile((B, T), mb.I32)
     del tensors
@@ -360,6 +360,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (variant run)")
+    ap.add_argument("--tp-overlap", type=int, default=1,
+                    help="1: all-reduce of a row chunk under the GEMM of the next (default); 0: in order")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.batch:

@@ -65,6 +65,9 @@ const char *mu_last_error(const mu_ctx *ctx);
 int mu_ctx_num_sms(const mu_ctx *ctx);
 /* force every matmul onto the CUDA-core kernel (debug / A-B checks); 0 restores */
 int mu_ctx_force_simt(mu_ctx *ctx, int on);
+/* Persistent GEMM kernels launch one CTA per SM; n > 0 limits them to n SMs so that a kernel
+ * running beside them (a collective on another stream) finds free SMs. 0 = all SMs. */
+int mu_ctx_set_sm_budget(mu_ctx *ctx, int n);
 int mu_alloc(mu_ctx *ctx, size_t bytes, void **ptr);
 int mu_free(mu_ctx *ctx, void *ptr);
 int mu_copy(mu_ctx *ctx, void *dst, const void *src, size_t bytes, int kind, void *stream);

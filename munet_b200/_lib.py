@@ -41,6 +41,7 @@ SIGNATURES = {
     "mu_last_error": (C.c_char_p, [_vp]),
     "mu_ctx_num_sms": (_i, [_vp]),
     "mu_ctx_force_simt": (_i, [_vp, _i]),
+    "mu_ctx_set_sm_budget": (_i, [_vp, _i]),
     "mu_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "mu_free": (_i, [_vp, _vp]),
     "mu_copy": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),

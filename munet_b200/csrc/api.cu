@@ -35,6 +35,7 @@ struct mu_ctx {
   int device = 0;
   int num_sms = 0;
   int force_simt = 0;
+  int sm_budget = 0; // > 0: persistent GEMM grids use at most this many SMs
   int *d_status = nullptr;
   char err[512] = {0};
 };
@@ -87,7 +88,8 @@ int run_gemm(mu_ctx *ctx, const mu::GemmOperands &op, const mu::GemmShape &sh, m
     return fail(ctx, MU_ERR_CUDA, "%s: cannot select device %d", who, ctx->device);
   if (dtype == MU_BF16 && !ctx->force_simt && sh.K > 0) {
     ep.vec_ok = epilogue_vec_ok(ep) ? 1 : 0;
-    int rc = mu::launch_gemm_bf16_tcgen05(op, sh, ep, ctx->d_status, ctx->num_sms, st);
+    const int sms = (ctx->sm_budget > 0 && ctx->sm_budget < ctx->num_sms) ? ctx->sm_budget : ctx->num_sms;
+    int rc = mu::launch_gemm_bf16_tcgen05(op, sh, ep, ctx->d_status, sms, st);
     if (rc == 0)
       return MU_OK;
     if (rc == 2)
@@ -201,6 +203,12 @@ const char *mu_last_error(const mu_ctx *ctx) { return ctx ? ctx->err : "null con
 int mu_set_error(mu_ctx *ctx, int code, const char *msg) { return fail(ctx, code, "%s", msg); }
 int mu_ctx_num_sms(const mu_ctx *ctx) { return ctx ? ctx->num_sms : 0; }
 int mu_ctx_select_device(mu_ctx *ctx) { return (ctx && set_device(ctx)) ? MU_OK : MU_ERR_CUDA; }
+int mu_ctx_set_sm_budget(mu_ctx *ctx, int n) {
+  if (!ctx || n < 0)
+    return MU_ERR_INVALID;
+  ctx->sm_budget = n;
+  return MU_OK;
+}
 int mu_ctx_force_simt(mu_ctx *ctx, int on) {
   if (!ctx)
     return MU_ERR_INVALID;

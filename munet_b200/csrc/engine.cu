@@ -287,7 +287,7 @@ struct mu_engine {
   int lower_block(const std::string &prefix, int d, int H, Val &v);
   int plan_and_allocate();
   int launch_all(cudaStream_t st);
-  int n_events = 0, tp_overlap = 1;
+  int n_events = 0, tp_overlap = 1, tp_comm_sms = 20;
   std::vector<cudaEvent_t> events;
   cudaStream_t side_stream = nullptr;
   // rows [row0, ...) of a [rows, cols] tensor (nullptr stays nullptr)
@@ -844,7 +844,11 @@ int mu_engine::launch_all(cudaStream_t st) {
     cudaStream_t s = op.side ? side_stream : st;
     if (op.wait_ev >= 0 && cudaStreamWaitEvent(s, events[op.wait_ev], 0) != cudaSuccess)
       return fail(MU_ERR_CUDA, "stream wait failed");
+    // a chunked GEMM leaves a few SMs free: the all-reduce of the previous chunk runs beside it
+    const bool chunked_gemm = op.kind == OP_LINEAR && op.rec_ev >= 0;
+    if (chunked_gemm) mu_ctx_set_sm_budget(ctx, std::max(2, mu_ctx_num_sms(ctx) - tp_comm_sms));
     int rc = launch_op(op, s);
+    if (chunked_gemm) mu_ctx_set_sm_budget(ctx, 0);
     if (rc) return rc;
     if (op.rec_ev >= 0 && cudaEventRecord(events[op.rec_ev], s) != cudaSuccess)
       return fail(MU_ERR_CUDA, "event record failed");
@@ -1074,6 +1078,7 @@ int mu_engine_set_option(mu_engine *e, const char *name, int value) {
   else if (n == "tp_rank") e->tp_rank = value;
   else if (n == "tp_size") e->tp_size = value;
   else if (n == "tp_overlap") e->tp_overlap = value;
+  else if (n == "tp_comm_sms") e->tp_comm_sms = value;
   else return e->fail(MU_ERR_INVALID, "unknown option '%s'", name);
   return MU_OK;
 }

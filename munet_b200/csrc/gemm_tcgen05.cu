@@ -719,14 +719,20 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=       \
           cudaSuccess)                                                                           \
         return 2;                                                                                \
-      cfg.gridDim = dim3(num_sms & ~1);                                                          \
+      int dev = 0, dev_sms = 0; /* the whole device, whatever SM budget this call runs under */   \
+      if (cudaGetDevice(&dev) != cudaSuccess ||                                                  \
+          cudaDeviceGetAttribute(&dev_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)  \
+        return 2;                                                                                \
+      cfg.gridDim = dim3(dev_sms & ~1);                                                          \
       int n = 0;                                                                                 \
       if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0)               \
         return 2;                                                                                \
       max_clusters = n;                                                                          \
       cluster_cache.set(n);                                                                      \
     }                                                                                            \
-    const long long nc = pair_tiles < max_clusters ? pair_tiles : max_clusters;                  \
+    long long nc = pair_tiles < max_clusters ? pair_tiles : max_clusters;                        \
+    if (nc > num_sms / 2)                                                                        \
+      nc = num_sms / 2;                                                                          \
     cfg.gridDim = dim3(static_cast<unsigned>(2 * nc));                                           \
     if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmR, s2, ep2, status) != cudaSuccess)      \
       return 2;                                                                                  \
