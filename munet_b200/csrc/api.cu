@@ -203,6 +203,9 @@ const char *mu_last_error(const mu_ctx *ctx) { return ctx ? ctx->err : "null con
 int mu_set_error(mu_ctx *ctx, int code, const char *msg) { return fail(ctx, code, "%s", msg); }
 int mu_ctx_num_sms(const mu_ctx *ctx) { return ctx ? ctx->num_sms : 0; }
 int mu_ctx_select_device(mu_ctx *ctx) { return (ctx && set_device(ctx)) ? MU_OK : MU_ERR_CUDA; }
+// accessors for the entry points that live in other translation units
+int *mu_ctx_status_ptr(mu_ctx *ctx) { return ctx ? ctx->d_status : nullptr; }
+int mu_ctx_simt_forced(const mu_ctx *ctx) { return ctx ? ctx->force_simt : 0; }
 int mu_ctx_set_sm_budget(mu_ctx *ctx, int n) {
   if (!ctx || n < 0)
     return MU_ERR_INVALID;

@@ -8,6 +8,8 @@
 
 namespace mu {
 int launch_conv2d(const ConvArgs &, cudaStream_t);
+size_t conv2d_tf32x3_scratch_bytes(const ConvArgs &);
+int launch_conv2d_tf32x3(const ConvArgs &, void *, int *, int, cudaStream_t);
 int launch_max_pool2d(const float *, float *, int, int, int, int, int, int, int, cudaStream_t);
 int launch_global_avg_pool(const float *, float *, long long, int, cudaStream_t);
 } // namespace mu
@@ -16,6 +18,9 @@ extern "C" {
 
 // Error text goes through the context of the other entry points.
 int mu_set_error(mu_ctx *ctx, int code, const char *msg);
+int *mu_ctx_status_ptr(mu_ctx *ctx);
+int mu_ctx_simt_forced(const mu_ctx *ctx);
+int mu_ctx_select_device(mu_ctx *ctx);
 
 int mu_conv2d(mu_ctx *ctx, const void *x, const void *w, const void *bias, void *y, int B, int iC,
               int iH, int iW, int oC, int k, int stride, int pad, int relu, int pool, int dtype,
@@ -40,7 +45,24 @@ int mu_conv2d(mu_ctx *ctx, const void *x, const void *w, const void *bias, void 
   a.bias = static_cast<const float *>(bias), a.y = static_cast<float *>(y);
   a.B = B, a.iC = iC, a.iH = iH, a.iW = iW, a.oC = oC, a.oH = oH, a.oW = oW;
   a.k = k, a.s = stride, a.p = pad, a.relu = relu ? 1 : 0, a.pool = pool;
-  const int rc = mu::launch_conv2d(a, static_cast<cudaStream_t>(stream));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // From 2^31 multiply-adds on: im2col + 3xTF32 tensor-core GEMM (float32-class accuracy); below,
+  // and whenever that path declines, the direct kernel with the reference's accumulation order.
+  const double macs = 1.0 * B * oH * oW * oC * iC * k * k;
+  if (macs >= 2147483648.0 && !mu_ctx_simt_forced(ctx) && mu_ctx_select_device(ctx) == MU_OK) {
+    void *scratch = nullptr;
+    if (cudaMallocAsync(&scratch, mu::conv2d_tf32x3_scratch_bytes(a), st) == cudaSuccess) {
+      const int trc = mu::launch_conv2d_tf32x3(a, scratch, mu_ctx_status_ptr(ctx), mu_ctx_num_sms(ctx), st);
+      cudaFreeAsync(scratch, st);
+      if (trc == 0)
+        return MU_OK;
+      if (trc == 2)
+        return mu_set_error(ctx, MU_ERR_CUDA, cudaGetErrorString(cudaGetLastError()));
+    } else {
+      cudaGetLastError();
+    }
+  }
+  const int rc = mu::launch_conv2d(a, st);
   if (rc == 1)
     return mu_set_error(ctx, MU_ERR_UNSUPPORTED, "conv2d: shape outside the kernel's envelope");
   if (rc)

@@ -23,8 +23,7 @@
 
 namespace mu {
 
-constexpr int T3_BM = 128, T3_BN = 256, T3_BK = 32; // 32 fp32 = 128 bytes = one swizzle row
-constexpr int T3_STAGES = 2;
+constexpr int T3_BM = 128, T3_BK = 32; // 32 fp32 = 128 bytes = one swizzle row
 // The tensor core adds into its fp32 accumulator with truncation, a bias toward zero that grows
 // linearly with K (measured: -1e-5 of the result's RMS per 2048 values of k, -4e-5 at K = 8192,
 // beyond the 1e-4 bound on some elements). The K loop is therefore cut into chunks of
@@ -33,10 +32,17 @@ constexpr int T3_STAGES = 2;
 // the one-chunk level (-5e-6, worst element at 0.19 of the bound) for any K.
 constexpr int T3_CHUNK_KB = 32;
 constexpr int T3_THREADS = 320;
-constexpr int T3_A_BYTES = T3_BM * 128, T3_B_BYTES = T3_BN * 128;
-constexpr int T3_STAGE_BYTES = 2 * T3_A_BYTES + 2 * T3_B_BYTES;
+constexpr int T3_A_BYTES = T3_BM * 128;
 constexpr int T3_OUT_BOX = 32 * 128; // 32 rows x 32 fp32
-constexpr int T3_SMEM = T3_STAGES * T3_STAGE_BYTES + 8 * T3_OUT_BOX + 1024 + 256;
+// Column-tile width BN = 256 for wide outputs; 128 and 64 for the narrow ones (a convolution's
+// output channels), where a 256-wide MMA would mostly multiply zero fill.
+template <int BN> struct T3Cfg {
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = 2 * T3_A_BYTES + 2 * B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 8 * T3_OUT_BOX + 1024 + 256;
+  static constexpr int NG = BN >= 64 ? BN / 64 : 1; // 32-column groups per epilogue warp
+};
 
 struct T3Args {
   int M, N, K;
@@ -122,11 +128,14 @@ __device__ __forceinline__ void t3_tma_store_2d(const void *tmap, const void *sr
                : "memory");
 }
 
+template <int T3_BN>
 __global__ void __launch_bounds__(T3_THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                    const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                    T3Args g, int *status) {
+  constexpr int T3_STAGES = T3Cfg<T3_BN>::STAGES, T3_STAGE_BYTES = T3Cfg<T3_BN>::STAGE_BYTES;
+  constexpr int T3_B_BYTES = T3Cfg<T3_BN>::B_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t *out_stage = smem + T3_STAGES * T3_STAGE_BYTES;
@@ -250,7 +259,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_consta
     uint8_t *buf = out_stage + (warp - 2) * T3_OUT_BOX;
     int it = 0, gcount = 0; // `it` counts K chunks, like the MMA warp
     bool ok = true;
-    constexpr int NG = T3_BN / 64; // 32-column groups per warp
+    constexpr int NG = T3Cfg<T3_BN>::NG; // 32-column groups per warp
     for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int nt = static_cast<int>(tile % tiles_n), mt = static_cast<int>(tile / tiles_n);
       const int m0 = mt * T3_BM + q * 32;
@@ -390,30 +399,37 @@ size_t gemm_tf32x3_scratch_bytes(int M, int N, int K) {
   return 2 * up(static_cast<size_t>(M) * K * 4) + 2 * up(static_cast<size_t>(N) * K * 4);
 }
 
-// Returns 0 ok, 1 shape/alignment outside this kernel's envelope, 2 launch/encode failure.
-// a [M,K] (row stride lda); b [K,N] (row stride ldb) or, with b_kmajor, [N,K]; c, residual [M,N]
-// (row stride ldc).
-int launch_gemm_tf32x3(const float *a, long long lda, const float *b, long long ldb, int b_kmajor, float *c,
-                       long long ldc, const float *bias, const float *residual, float alpha, int act, int M,
-                       int N, int K, void *scratch, int *status, int num_sms, cudaStream_t st) {
-  auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-  if (M <= 0 || N <= 0 || K <= 0 || (K % 4) || (ldc % 4) || !al(c) || (residual && !al(residual)) || !scratch)
+template <int BN>
+static int t3_launch(const CUtensorMap &tmAh, const CUtensorMap &tmAl, const float *bh, const float *bl,
+                     const CUtensorMap &tmC, const CUtensorMap &tmR, const T3Args &g, int *status, int num_sms,
+                     cudaStream_t st) {
+  CUtensorMap tmBh, tmBl;
+  if (!t3_map(&tmBh, bh, g.K, g.N, g.K, BN) || !t3_map(&tmBl, bl, g.K, g.N, g.K, BN))
+    return 2;
+  auto kern = gemm_tf32x3_kernel<BN>;
+  static PerDeviceOnce attr_set;
+  if (attr_set.get() < 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T3Cfg<BN>::SMEM) != cudaSuccess)
+      return 2;
+    attr_set.set(1);
+  }
+  const long long tiles = 1ll * ((g.M + T3_BM - 1) / T3_BM) * ((g.N + BN - 1) / BN);
+  const unsigned grid = static_cast<unsigned>(tiles < num_sms ? tiles : num_sms);
+  kern<<<grid, T3_THREADS, T3Cfg<BN>::SMEM, st>>>(tmAh, tmAl, tmBh, tmBl, tmC, tmR, g, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// The GEMM on operands that are already split: ah, al [M,K] and bh, bl [N,K], dense, K % 4 == 0.
+// c and residual [M,N] with row stride ldc. Returns 0 ok, 1 outside the envelope, 2 failure.
+int gemm_tf32x3_presplit(const float *ah, const float *al, const float *bh, const float *bl, float *c,
+                         long long ldc, const float *bias, const float *residual, float alpha, int act, int M,
+                         int N, int K, int *status, int num_sms, cudaStream_t st) {
+  auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 4) || (ldc % 4) || !al16(c) || (residual && !al16(residual)) ||
+      !al16(ah) || !al16(al) || !al16(bh) || !al16(bl))
     return 1;
-  auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
-  uint8_t *s = static_cast<uint8_t *>(scratch);
-  float *ah = reinterpret_cast<float *>(s), *alo = reinterpret_cast<float *>(s + up(1ull * M * K * 4));
-  float *bh = reinterpret_cast<float *>(s + 2 * up(1ull * M * K * 4));
-  float *bl = reinterpret_cast<float *>(s + 2 * up(1ull * M * K * 4) + up(1ull * N * K * 4));
-  const unsigned eb = static_cast<unsigned>(num_sms > 0 ? num_sms * 16 : 1024);
-  split_tf32_kernel<<<eb, 256, 0, st>>>(a, lda, ah, alo, M, K);
-  if (b_kmajor)
-    split_tf32_kernel<<<eb, 256, 0, st>>>(b, ldb, bh, bl, N, K);
-  else
-    split_tf32_transpose_kernel<<<dim3((N + 31) / 32, (K + 31) / 32), 256, 0, st>>>(b, ldb, bh, bl, K, N);
-  CUtensorMap tmAh, tmAl, tmBh, tmBl, tmC, tmR;
-  if (!t3_map(&tmAh, ah, K, M, K, T3_BM) || !t3_map(&tmAl, alo, K, M, K, T3_BM) ||
-      !t3_map(&tmBh, bh, K, N, K, T3_BN) || !t3_map(&tmBl, bl, K, N, K, T3_BN) ||
-      !t3_map(&tmC, c, N, M, ldc, 32))
+  CUtensorMap tmAh, tmAl, tmC, tmR;
+  if (!t3_map(&tmAh, ah, K, M, K, T3_BM) || !t3_map(&tmAl, al, K, M, K, T3_BM) || !t3_map(&tmC, c, N, M, ldc, 32))
     return 2;
   if (residual) {
     if (!t3_map(&tmR, residual, N, M, ldc, 32))
@@ -424,17 +440,39 @@ int launch_gemm_tf32x3(const float *a, long long lda, const float *b, long long 
   T3Args g;
   g.M = M, g.N = N, g.K = K, g.act = act, g.has_bias = bias != nullptr, g.has_res = residual != nullptr;
   g.alpha = alpha, g.bias = bias;
-  static PerDeviceOnce attr_set;
-  if (attr_set.get() < 0) {
-    if (cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T3_SMEM) !=
-        cudaSuccess)
-      return 2;
-    attr_set.set(1);
-  }
-  const long long tiles = 1ll * ((M + T3_BM - 1) / T3_BM) * ((N + T3_BN - 1) / T3_BN);
-  const unsigned grid = static_cast<unsigned>(tiles < num_sms ? tiles : num_sms);
-  gemm_tf32x3_kernel<<<grid, T3_THREADS, T3_SMEM, st>>>(tmAh, tmAl, tmBh, tmBl, tmC, tmR, g, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  if (N > 128)
+    return t3_launch<256>(tmAh, tmAl, bh, bl, tmC, tmR, g, status, num_sms, st);
+  if (N > 64)
+    return t3_launch<128>(tmAh, tmAl, bh, bl, tmC, tmR, g, status, num_sms, st);
+  return t3_launch<64>(tmAh, tmAl, bh, bl, tmC, tmR, g, status, num_sms, st);
+}
+
+// Split only: x [rows, cols] with row stride ldx -> hi, lo dense [rows, cols].
+void split_tf32(const float *x, long long ldx, float *hi, float *lo, long long rows, int cols, int num_sms,
+                cudaStream_t st) {
+  const unsigned eb = static_cast<unsigned>(num_sms > 0 ? num_sms * 16 : 1024);
+  split_tf32_kernel<<<eb, 256, 0, st>>>(x, ldx, hi, lo, rows, cols);
+}
+
+// Returns 0 ok, 1 shape/alignment outside this kernel's envelope, 2 launch/encode failure.
+// a [M,K] (row stride lda); b [K,N] (row stride ldb) or, with b_kmajor, [N,K]; c, residual [M,N]
+// (row stride ldc).
+int launch_gemm_tf32x3(const float *a, long long lda, const float *b, long long ldb, int b_kmajor, float *c,
+                       long long ldc, const float *bias, const float *residual, float alpha, int act, int M,
+                       int N, int K, void *scratch, int *status, int num_sms, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 4) || !scratch)
+    return 1;
+  auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+  uint8_t *s = static_cast<uint8_t *>(scratch);
+  float *ah = reinterpret_cast<float *>(s), *alo = reinterpret_cast<float *>(s + up(1ull * M * K * 4));
+  float *bh = reinterpret_cast<float *>(s + 2 * up(1ull * M * K * 4));
+  float *bl = reinterpret_cast<float *>(s + 2 * up(1ull * M * K * 4) + up(1ull * N * K * 4));
+  split_tf32(a, lda, ah, alo, M, K, num_sms, st);
+  if (b_kmajor)
+    split_tf32(b, ldb, bh, bl, N, K, num_sms, st);
+  else
+    split_tf32_transpose_kernel<<<dim3((N + 31) / 32, (K + 31) / 32), 256, 0, st>>>(b, ldb, bh, bl, K, N);
+  return gemm_tf32x3_presplit(ah, alo, bh, bl, c, ldc, bias, residual, alpha, act, M, N, K, status, num_sms, st);
 }
 
 } // namespace mu

@@ -6,7 +6,7 @@ import pytest
 
 import oracle
 from oracle import F32
-from tests.util import empty_dev, to_dev, to_host
+from tests.util import assert_close, empty_dev, to_dev, to_host
 
 pytestmark = pytest.mark.gpu
 
@@ -108,3 +108,38 @@ def test_small_cnn_config_bit_exact(ctx, tmp_path):
     if oracle.have_ref():
         same(got, oracle.ref().engine_run_npz(path, x))
     eng.close()
+
+
+@pytest.mark.parametrize("B,iC,H,oC,relu,pool", [(256, 64, 16, 128, True, 2), (96, 128, 8, 256, True, 0),
+                                                 (300, 3, 32, 64, False, 0), (70, 40, 18, 100, True, 2)])
+def test_large_conv_on_tensor_cores_matches_direct_kernel(ctx, B, iC, H, oC, relu, pool):
+    """From 2^31 multiply-adds on a convolution runs as im2col + 3xTF32 GEMM. The direct kernel
+    (the reference's accumulation order, bit-exact against the CPU checker in the tests above) is
+    the witness: float32-class agreement, 1e-5 against the config tolerance of 1e-4."""
+    rng = np.random.default_rng(B + iC)
+    x = rng.standard_normal((B, iC, H, H)).astype(np.float32)
+    w = (rng.standard_normal((oC, iC, 3, 3)) * np.sqrt(2.0 / (iC * 9))).astype(np.float32)
+    b = (rng.standard_normal(oC) * 0.1).astype(np.float32)
+    oH = H // 2 if pool else H
+    outs = []
+    for simt in (True, False):
+        y = empty_dev((B, oC, oH, oH), F32)
+        ctx.force_simt(simt)
+        ctx.conv2d(to_dev(x, F32), to_dev(w, F32), to_dev(b, F32), y, B, iC, H, H, oC, 3, 1, 1, F32,
+                   relu=relu, pool=pool)
+        ctx.check()
+        outs.append(to_host(y))
+    ctx.force_simt(False)
+    direct, tensor = outs
+    macs = B * H * H * oC * iC * 9
+    if macs >= 2 ** 31:
+        assert not np.array_equal(direct, tensor), "expected the tensor-core path"
+    assert_close(tensor, direct, F32, rtol=1e-5, what="conv im2col+3xTF32 vs direct")
+    # one image against the CPU checker ties both to the reference
+    P = oracle.port()
+    want = P.conv2d(x[:1], w, b, 1, 1)
+    if relu:
+        want = np.maximum(want, 0)
+    if pool:
+        want = P.max_pool2d(want)
+    assert_close(tensor[:1], want, F32, rtol=1e-5, what="conv vs checker")
