@@ -88,9 +88,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
   uint64_t *s_full = v_empty + STAGES;
   uint64_t *s_empty = s_full + 2;
   uint64_t *p_full = s_empty + 2;
-  uint64_t *o_full = p_full + 2;
-  uint64_t *o_empty = o_full + 2;
-  uint64_t *xbar = o_empty + 2; // [quarter][tile parity]: paired softmax warps
+  // O accumulates in TMEM over the key tiles of a work (one buffer per work parity):
+  //   o_done[tile parity]  a P·V has completed (P buffer reusable, O readable / rescalable)
+  //   o_free[work parity]  the softmax warps have read the finished O of that buffer
+  uint64_t *o_done = p_full + 2;
+  uint64_t *o_free = o_done + 2;
+  uint64_t *xbar = o_free + 2; // [quarter][tile parity]: paired softmax warps
   uint64_t *xend = xbar + 8;    // [quarter][0: row sums, 1: output staged]
   uint64_t *q_empty = xend + 8;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(q_empty + 1);
@@ -134,8 +137,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       mbar_init(&s_full[b], 1);
       mbar_init(&s_empty[b], 4 * ATT_PARTS);
       mbar_init(&p_full[b], 4 * ATT_PARTS);
-      mbar_init(&o_full[b], 1);
-      mbar_init(&o_empty[b], 4 * ATT_PARTS);
+      mbar_init(&o_done[b], 1);
+      mbar_init(&o_free[b], 4 * ATT_PARTS);
     }
     for (int i = 0; i < 8; ++i) {
       mbar_init(&xbar[i], ATT_PARTS);
@@ -231,12 +234,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       const uint32_t q_addr = smem_u32(sQ);
       bool ok = true;
       uint32_t t = 0, w = 0; // key tiles and works issued so far (they index every ring)
-      // P·V of tile number i (global count): needs its V tile, the probabilities and a free O buffer
-      auto issue_pv = [&](uint32_t i) -> bool {
+      // P·V of tile number i (global count), the j-th of work number wi: needs its V tile and the
+      // probabilities; the first one of a work overwrites that work's O buffer, which the
+      // softmax warps must have drained (two works ago).
+      auto issue_pv = [&](uint32_t i, int j, uint32_t wi) -> bool {
         const int b = i & 1;
         const uint32_t par = (i >> 1) & 1;
-        if (!mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1) || !mbar_wait(&p_full[b], par) ||
-            !mbar_wait(&o_empty[b], par ^ 1))
+        const int ob = wi & 1;
+        if (!mbar_wait(&v_full[i % STAGES], (i / STAGES) & 1) || !mbar_wait(&p_full[b], par))
+          return false;
+        if (j == 0 && !mbar_wait(&o_free[ob], ((wi >> 1) & 1) ^ 1))
           return false;
         tc_fence_after();
         const uint32_t p_addr = smem_u32(sP + b * Cfg::P_BYTES);
@@ -245,9 +252,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         for (int k = 0; k < BKV / 16; ++k) {
           const uint64_t ad = make_smem_desc(p_addr + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
           const uint64_t bd = make_smem_desc(v_addr + (k / 4) * (DB * 8192) + (k % 4) * 2048, 8192, 1024);
-          umma_f16(tmem_O + b * D, ad, bd, idesc_pv, k != 0 ? 1u : 0u);
+          umma_f16(tmem_O + ob * D, ad, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
         }
-        umma_commit(&o_full[b]);
+        umma_commit(&o_done[b]);
         umma_commit(&v_empty[i % STAGES]);
         return true;
       };
@@ -284,12 +291,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
             umma_commit(&k_empty[stage]);
             if (j == wk.nk - 1)
               umma_commit(q_empty); // the producer may fetch the next work's Q
-            if (j > 0 && !issue_pv(t - 1)) {
+            if (j > 0 && !issue_pv(t - 1, j - 1, w - 1)) {
               atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
               ok = false;
             }
           }
-          if (ok && !issue_pv(t - 1)) {
+          if (ok && !issue_pv(t - 1, wk.nk - 1, w - 1)) {
             atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
             ok = false;
           }
@@ -324,35 +331,59 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       return mbar_wait(bar, parity);
     };
 
-    auto consume_o = [&](uint32_t i, float a) -> bool {
-      const int b = i & 1;
-      if (!mbar_wait(&o_full[b], (i >> 1) & 1))
-        return false;
+    // Multiply this thread's part of the work's O accumulator (TMEM) by `a` — the online-softmax
+    // correction. It is only called when the running maximum has grown by more than 2^8 since
+    // the exponent reference was set (see below), and never while a P·V is in flight.
+    auto rescale_o = [&](int ob, float a) {
       tc_fence_after();
       if constexpr (DH % 32 == 0) {
 #pragma unroll
         for (int c = 0; c < DH / 32; ++c) {
           uint32_t r[32];
-          tmem_ld_32x32(tmem_O + lane_sel + b * D + half * DH + c * 32, r);
+          const uint32_t addr = tmem_O + lane_sel + ob * D + half * DH + c * 32;
+          tmem_ld_32x32(addr, r);
           tmem_ld_wait();
 #pragma unroll
           for (int k = 0; k < 32; ++k)
-            o_acc[c * 32 + k] = fmaf(o_acc[c * 32 + k], a, __uint_as_float(r[k]));
+            r[k] = __float_as_uint(__uint_as_float(r[k]) * a);
+          tmem_st_32x32(addr, r);
         }
       } else {
         static_assert(DH % 32 == 0 || DH == 16, "output columns per thread");
-        uint32_t r[16];
-        tmem_ld_32x16(tmem_O + lane_sel + b * D + half * DH, r);
+        uint32_t r16[16];
+        const uint32_t addr = tmem_O + lane_sel + ob * D + half * DH;
+        tmem_ld_32x16(addr, r16);
         tmem_ld_wait();
 #pragma unroll
         for (int k = 0; k < 16; ++k)
-          o_acc[k] = fmaf(o_acc[k], a, __uint_as_float(r[k]));
+          r16[k] = __float_as_uint(__uint_as_float(r16[k]) * a);
+        tmem_st_32x16(addr, r16);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+    };
+    // The finished O of a work: TMEM -> registers.
+    auto load_o = [&](int ob) {
+      tc_fence_after();
+      if constexpr (DH % 32 == 0) {
+#pragma unroll
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_O + lane_sel + ob * D + half * DH + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 32; ++k)
+            o_acc[c * 32 + k] = __uint_as_float(r[k]);
+        }
+      } else {
+        uint32_t r16[16];
+        tmem_ld_32x16(tmem_O + lane_sel + ob * D + half * DH, r16);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          o_acc[k] = __uint_as_float(r16[k]);
       }
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive(&o_empty[b]);
-      return true;
     };
 
     for (long long item = blockIdx.x; item < n_items && ok; item += gridDim.x)
@@ -362,10 +393,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       continue;
     const int q0 = wk.q0, nk = wk.nk, bh = wk.bh;
     const int qrow = q0 + row; // position in the sequence
-    float m_run = -INFINITY, l_run = 0.f, alpha_pending = 1.f;
-#pragma unroll
-    for (int i = 0; i < DH; ++i)
-      o_acc[i] = 0.f;
+    // m_ref is the maximum the exponents are taken against. It follows the running maximum
+    // only when that has moved by more than 2^8: probabilities then stay below 256 (exact enough
+    // in bf16, harmless in the fp32 accumulators) and O in TMEM almost never needs rescaling.
+    float m_ref = -INFINITY, l_run = 0.f;
+    const int ob = w & 1; // this work's O buffer
     for (int j = 0; j < nk && ok; ++j, ++t) {
       const int b = t & 1;
       if (!mbar_wait(&s_full[b], (t >> 1) & 1)) {
@@ -427,13 +459,37 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         ok = false;
         break;
       }
-      float mx = m_run;
+      float mx = m_ref;
 #pragma unroll
       for (int pt = 0; pt < ATT_PARTS; ++pt)
         mx = fmaxf(mx, __uint_as_float(static_cast<uint32_t>(xm[(b * ATT_PARTS + pt) * BQ + row]) << 16));
       // rows past the end of the sequence see no key at all: keep them finite
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float mL = m_use * L2E;
+      const float m_new = (mx == -INFINITY) ? 0.f : mx;
+      if (j == 0) {
+        m_ref = m_new; // nothing accumulated yet
+      } else {
+        // Both warps of a pair see the same rows and the same maxima, so they take the same branch.
+        const bool grow = (m_new - m_ref) * L2E > 8.0f;
+        if (__any_sync(0xffffffffu, grow)) {
+          // the previous P·V must have landed in O before it is scaled
+          if (!mbar_wait(&o_done[(t - 1) & 1], ((t - 1) >> 1) & 1)) {
+            atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+            ok = false;
+            break;
+          }
+          const float a = ex2_approx((m_ref - m_new) * L2E);
+          rescale_o(ob, a);
+          l_run *= a;
+          m_ref = m_new;
+        }
+      }
+      const float mL = m_ref * L2E;
+      // P buffer b was last read by the P·V of tile t-2
+      if (!mbar_wait(&o_done[b], ((t >> 1) & 1) ^ 1)) {
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
       // pass 2: second rounding (times the bf16 scale, one packed multiply), probabilities ->
       // bf16 -> swizzled smem (K-major A operand of P·V). Masked columns hold -inf: exp2 gives 0.
       uint8_t *prow = sP + b * Cfg::P_BYTES + row * 128;
@@ -465,21 +521,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       __syncwarp();
       if (lane == 0)
         mbar_arrive(&p_full[b]);
-      const float alpha = exp2f((m_run - m_use) * L2E); // first tile: exp2(-inf) = 0
-      l_run = l_run * alpha + (sum0 + sum1);
-      m_run = m_use;
-      if (j > 0) {
-        if (!consume_o(t - 1, alpha_pending)) {
-          atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
-          ok = false;
-          break;
-        }
-      }
-      alpha_pending = alpha;
+      l_run += sum0 + sum1;
     }
-    if (ok && !consume_o(t - 1, alpha_pending)) {
+    // the last P·V of the work has completed: drain O and hand the buffer back
+    if (ok && !mbar_wait(&o_done[(t - 1) & 1], ((t - 1) >> 1) & 1)) {
       atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
       ok = false;
+    }
+    if (ok) {
+      load_o(ob);
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive(&o_free[ob]);
     }
     if (ok) {
       // full row sum = the pair's partial sums (every P·V has completed: xchg is idle)

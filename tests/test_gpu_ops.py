@@ -324,6 +324,32 @@ def test_attention_core(ctx, dtype, kmode, causal, B, H, T, D):
     assert_close(to_host(out), want, dtype, what="attention")
 
 
+@pytest.mark.parametrize("kmode", [oracle.K_LITERAL, oracle.K_MATH])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_growing_maximum_rescales_accumulator(ctx, kmode, causal):
+    """Keys whose magnitude grows along the sequence: the row maximum jumps by far more than 2^8
+    from one 128-key tile to the next, which is the case where the output accumulator kept in
+    tensor memory has to be rescaled in place (otherwise it is left alone)."""
+    rng = np.random.default_rng(99)
+    B, H, T, D = 1, 2, 512, 64
+    n = B * H * T
+    q = rnd(rng, (n, D), BF16)
+    grow = (1.0 + 30.0 * (np.arange(n) % T) / T)[:, None]
+    k = oracle.to_bf16(oracle.from_bf16(rnd(rng, (n, D), BF16)) * grow.astype(np.float32))
+    v = rnd(rng, (n, D), BF16)
+    want_hm = oracle.port().attention_core(q, k, v, B * H, T, D, causal, BF16, kmode)
+    want = np.ascontiguousarray(want_hm.reshape(B, H, T, D).transpose(0, 2, 1, 3)).reshape(B * T, H * D)
+    out = empty_dev((B * T, H * D), BF16)
+    nbytes = ctx.attention_workspace_bytes(B, H, T, D, BF16)
+    ws = empty_dev((max(nbytes, 16),), oracle.I32) if False else None
+    import torch
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+    ctx.attention(to_dev(q, BF16), to_dev(k, BF16), to_dev(v, BF16), out, B, H, T, D, causal, kmode, BF16,
+                  ws, nbytes)
+    ctx.check()
+    assert_close(to_host(out), want, BF16, what="attention with growing maxima")
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("B,T,E,H", [(2, 64, 256, 4), (1, 24, 48, 3)])
 def test_linear_qkv_head_major(ctx, dtype, B, T, E, H):
