@@ -418,7 +418,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       // (positive) scale are monotone, so the maximum of the transformed scores is the transform
       // of the maximum.
       uint32_t sp[SC / 2];
-      uint32_t mx2 = 0xFF80FF80u; // (-inf, -inf)
+      uint32_t mxa[4] = {0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u}; // four short max chains
       {
         uint32_t r[SC / 32][32];
 #pragma unroll
@@ -438,13 +438,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
                 u = (u & 0x0000FFFFu) | 0xFF800000u;
             }
             sp[c * 16 + k / 2] = u;
-            mx2 = bf16x2_max(mx2, u);
+            mxa[(k >> 1) & 3] = bf16x2_max(mxa[(k >> 1) & 3], u);
           }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0)
         mbar_arrive(&s_empty[b]); // the scores now live in registers
+      const uint32_t mx2 = bf16x2_max(bf16x2_max(mxa[0], mxa[1]), bf16x2_max(mxa[2], mxa[3]));
       const float raw_mx = fmaxf(bf16_lo(mx2), bf16_hi(mx2));
       const float mine = bf16_round(raw_mx * scale_b); // exactly a bf16 value (or -inf)
       xm[(b * ATT_PARTS + half) * BQ + row] = static_cast<uint16_t>(__float_as_uint(mine) >> 16);
