@@ -223,7 +223,7 @@ def run_ours(args, cfg):
     if tp > 1:
         # tensor-parallel variant: all ranks form ONE model replica and run the SAME batch; heads,
         # MLP columns and the vocabulary are split over ranks, partial sums meet in an NCCL
-        # all-reduce. Needs true Q.K^T (literal K addressing reads across heads).
+        # all-reduce. Needs true Q.K^T: literal K addressing reads across heads and cannot be head-sharded.
         if world != tp:
             raise SystemExit("--tp N runs one tensor-parallel group: launch exactly N ranks")
         comm = mb.Comm.from_torch_distributed(ctx)
