@@ -319,8 +319,8 @@ def run_ours(args, cfg):
         "achieved": achieved, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
         "frac": achieved / pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (sustained)",
         # DRAM bytes per launch, averaged over the 97 GEMM launches of one forward of the
-        # default config: ncu captures of each model shape at a quarter of the rows, scaled by 4
-        # (profiles/gemm_bf16_tcgen05_M16384_N2048_K2048_gelu.md); algorithmic: 1.135e9.
+        # default config: ncu captures (dram__bytes_read.sum + dram__bytes_write.sum) of each model
+        # shape at a quarter of the rows, scaled by 4; algorithmic: 1.135e9.
         "traffic": 1.347e9 if (cfg["d_model"], cfg["n_layers"], cfg["batch"], tp) == (2048, 24, 64, 1) else None,
         "traffic_unit": "bytes/launch (ncu dram read+write, offline capture)",
         "launches_per_step": by_kind.get("linear", {"n": 0})["n"] + by_kind.get("qkv_linear", {"n": 0})["n"],
