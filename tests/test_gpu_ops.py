@@ -306,7 +306,8 @@ def test_argmax_bf16_ties(ctx, rows, cols):
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("kmode", [oracle.K_LITERAL, oracle.K_MATH])
 @pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("B,H,T,D", [(2, 4, 64, 64), (1, 2, 256, 128), (2, 2, 24, 16), (1, 3, 10, 8)])
+@pytest.mark.parametrize("B,H,T,D", [(2, 4, 64, 64), (1, 2, 256, 128), (2, 2, 24, 16), (1, 3, 10, 8),
+                                     (1, 3, 384, 128), (1, 2, 696, 64), (2, 1, 640, 128)])
 def test_attention_core(ctx, dtype, kmode, causal, B, H, T, D):
     rng = np.random.default_rng(B * 1000 + T + D)
     n = B * H * T
@@ -321,7 +322,9 @@ def test_attention_core(ctx, dtype, kmode, causal, B, H, T, D):
     ctx.attention(to_dev(q, dtype), to_dev(k, dtype), to_dev(v, dtype), out, B, H, T, D, causal,
                   kmode, dtype, ws, nbytes)
     ctx.check()
-    assert_close(to_host(out), want, dtype, what="attention")
+    # long causal rows average hundreds of values: outputs far below the tensor's RMS, where the
+    # rounding of single probabilities to bf16 (ours unnormalised, the reference's normalised) shows
+    assert_close(to_host(out), want, dtype, what="attention", worst_cap=2.0 if T >= 512 else 1.0)
 
 
 @pytest.mark.parametrize("kmode", [oracle.K_LITERAL, oracle.K_MATH])

@@ -52,6 +52,12 @@ def close(got: np.ndarray, want: np.ndarray, dtype: int, rtol=None):
     return bool(np.all(err <= bound)) and bool(np.isfinite(g).all()), worst, rel_inf
 
 
-def assert_close(got, want, dtype, rtol=None, what=""):
+def assert_close(got, want, dtype, rtol=None, what="", worst_cap=1.0):
+    """``worst_cap`` > 1 relaxes the elementwise bound by that factor while still holding the
+    norm-wise error ``max|a-b| / max|b|`` to the tolerance (used where outputs are averages over
+    hundreds of terms, much smaller than the tensor's RMS, and one bf16 rounding of a term shows)."""
     ok, worst, rel_inf = close(got, want, dtype, rtol)
+    tol = RTOL[dtype] if rtol is None else rtol
+    ok = ok or (worst_cap > 1.0 and worst <= worst_cap and rel_inf <= tol and np.isfinite(
+        oracle.as_float(got, dtype)).all())
     assert ok, f"{what}: worst err/bound {worst:.3g}, rel-inf {rel_inf:.3g}"
