@@ -93,7 +93,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
   //   o_free[work parity]  the softmax warps have read the finished O of that buffer
   uint64_t *o_done = p_full + 2;
   uint64_t *o_free = o_done + 2;
-  uint64_t *xbar = o_free + 2; // [quarter]: staging of the previous work's output is free again
+  uint64_t *xbar = o_free + 2; // [quarter][tile parity]: paired softmax warps
   uint64_t *xend = xbar + 8;    // [quarter][0: row sums, 1: output staged]
   uint64_t *q_empty = xend + 8;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(q_empty + 1);
@@ -141,7 +141,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       mbar_init(&o_free[b], 4 * ATT_PARTS);
     }
     for (int i = 0; i < 8; ++i) {
-      mbar_init(&xbar[i], 1); // [quarter]: the previous work's output store has read its staging
+      mbar_init(&xbar[i], ATT_PARTS);
       mbar_init(&xend[i], ATT_PARTS);
     }
     fence_barrier_init();
@@ -317,6 +317,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
     constexpr float L2E = 1.4426950408889634f;
     constexpr int SC = BKV / ATT_PARTS; // score columns per thread
     constexpr int DH = D / ATT_PARTS;   // output columns per thread
+    uint16_t *xm = reinterpret_cast<uint16_t *>(xchg); // [tile parity][half][row] partial maxima (bf16)
     float *xl = reinterpret_cast<float *>(xchg);       // [half][row] partial row sums (end only)
     float o_acc[DH];
     bool ok = true;
@@ -440,56 +441,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
             mxa[(k >> 1) & 3] = bf16x2_max(mxa[(k >> 1) & 3], u);
           }
       }
-      // The other warps of this row quarter own the remaining columns. Instead of exchanging
-      // partial maxima through shared memory and a barrier every tile, each warp also reads those
-      // columns and takes the maximum over the whole row itself: the warps of a quarter then agree
-      // on it by construction and run independently of each other until the end of the work.
-#pragma unroll
-      for (int oh = 1; oh < ATT_PARTS; ++oh) {
-        const int other = (half + oh) % ATT_PARTS;
-        uint32_t r[SC / 32][32];
-#pragma unroll
-        for (int c = 0; c < SC / 32; ++c)
-          tmem_ld_32x32(tmem_S + lane_sel + b * BKV + other * SC + c * 32, r[c]);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < SC / 32; ++c)
-#pragma unroll
-          for (int k = 0; k < 32; k += 2) {
-            uint32_t u = pack_bf16x2(__uint_as_float(r[c][k]), __uint_as_float(r[c][k + 1]));
-            if (need_mask) {
-              const int col = other * SC + c * 32 + k;
-              if (col >= lim)
-                u = (u & 0xFFFF0000u) | 0x0000FF80u;
-              if (col + 1 >= lim)
-                u = (u & 0x0000FFFFu) | 0xFF800000u;
-            }
-            mxa[(k >> 1) & 3] = bf16x2_max(mxa[(k >> 1) & 3], u);
-          }
-      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0)
         mbar_arrive(&s_empty[b]); // the scores now live in registers
       const uint32_t mx2 = bf16x2_max(bf16x2_max(mxa[0], mxa[1]), bf16x2_max(mxa[2], mxa[3]));
       const float raw_mx = fmaxf(bf16_lo(mx2), bf16_hi(mx2));
-      const float mx = fmaxf(m_ref, bf16_round(raw_mx * scale_b)); // a bf16 value (or -inf)
-      if (j == 0 && w > 0) {
-        // The previous work's output was staged in the P buffers. Its store must have read them
-        // before any warp of this row quarter writes P again: the issuing thread waits for that
-        // and releases the quarter (once per work; phases count works from the second on).
-        if (half == 0 && lane == 0) {
-          if (store_pending)
-            bulk_wait_read<0>();
-          store_pending = false;
-          mbar_arrive(&xbar[q]);
-        }
-        if (!mbar_wait(&xbar[q], (w - 1) & 1)) {
-          atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
-          ok = false;
-          break;
-        }
+      const float mine = bf16_round(raw_mx * scale_b); // exactly a bf16 value (or -inf)
+      xm[(b * ATT_PARTS + half) * BQ + row] = static_cast<uint16_t>(__float_as_uint(mine) >> 16);
+      if (store_pending) {
+        // The previous work's output was staged in the P buffers; its store must have read them
+        // before anyone of this row quarter (all behind the barrier below) writes P again.
+        bulk_wait_read<0>();
+        store_pending = false;
       }
+      if (!pair_sync(&xbar[q * 2 + b], (t >> 1) & 1)) {
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+        ok = false;
+        break;
+      }
+      float mx = m_ref;
+#pragma unroll
+      for (int pt = 0; pt < ATT_PARTS; ++pt)
+        mx = fmaxf(mx, __uint_as_float(static_cast<uint32_t>(xm[(b * ATT_PARTS + pt) * BQ + row]) << 16));
       // rows past the end of the sequence see no key at all: keep them finite
       const float m_new = (mx == -INFINITY) ? 0.f : mx;
       if (j == 0) {
