@@ -9,6 +9,11 @@
  * launch time (a bounded wait that ran out, an out-of-range embedding id) are
  * latched in a per-context status word and reported by mu_check().
  *
+ * Threading: a context may be used from any host thread, by one thread at a time
+ * (its error text and its SM budget are per-context state); kernels of different
+ * contexts and of different streams of one context run concurrently. An engine
+ * belongs to the context it was created on and is driven by one thread at a time.
+ *
  * Citations name the interface of the reference (bryan-pakulski/MuNet, paths
  * relative to its checkout) that each entry point stands in for.
  *
