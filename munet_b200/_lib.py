@@ -176,6 +176,10 @@ class Context:
     def force_simt(self, on: bool):
         self._rc(self._lib.mu_ctx_force_simt(self._h, int(on)))
 
+    def set_sm_budget(self, n: int):
+        """Limit persistent GEMM grids to ``n`` SMs (0 = all): room for a kernel running beside them."""
+        self._rc(self._lib.mu_ctx_set_sm_budget(self._h, int(n)))
+
     def check(self, stream=None):
         """Synchronise the stream and raise if a kernel latched a device-side error."""
         self._rc(self._lib.mu_check(self._h, _stream(stream)))

@@ -66,6 +66,23 @@ def test_linear_bf16_cta_pairs(ctx, M, K, N, transB):
         assert_close(to_host(c), P.matmul(x, w, BF16), BF16, what="pair matmul transB")
 
 
+@pytest.mark.parametrize("budget", [2, 37, 100])
+def test_linear_bf16_under_an_sm_budget(ctx, budget):
+    """A persistent GEMM limited to a few SMs (what the executor does while a collective runs
+    beside it) walks the same tiles with fewer CTAs: same bits as the unrestricted launch, for the
+    CTA-pair kernel (odd budgets round down to whole pairs) and the single-CTA kernel."""
+    rng = np.random.default_rng(budget)
+    for M, K, N in ((2560, 128, 2048), (300, 256, 512)):
+        x, w, b = rnd(rng, (M, K), BF16), rnd(rng, (K, N), BF16, 1.0 / np.sqrt(K)), rnd(rng, (N,), BF16, 0.05)
+        full = dev_linear(ctx, x, w, b, BF16, "gelu")
+        ctx.set_sm_budget(budget)
+        try:
+            limited = dev_linear(ctx, x, w, b, BF16, "gelu")
+        finally:
+            ctx.set_sm_budget(0)
+        assert np.array_equal(full, limited)
+
+
 def test_linear_bf16_wide_weights_use_column_panels(ctx):
     """A weight matrix wider than the L2 budget (here 49 MB) is swept in panels of column tiles,
     the last one narrower. Every output tile must still be produced exactly once: compared with
