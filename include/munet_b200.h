@@ -76,6 +76,24 @@ int mu_ctx_set_sm_budget(mu_ctx *ctx, int n);
 int mu_alloc(mu_ctx *ctx, size_t bytes, void **ptr);
 int mu_free(mu_ctx *ctx, void *ptr);
 int mu_copy(mu_ctx *ctx, void *dst, const void *src, size_t bytes, int kind, void *stream);
+/* Backend::memset (src/core/backend.hpp:209; CUDA reference src/backend/cuda_backend.cu:946-950):
+ * every byte of [ptr, ptr+bytes) becomes (unsigned char)value, asynchronous on `stream`. */
+int mu_memset(mu_ctx *ctx, void *ptr, int value, size_t bytes, void *stream);
+/* Backend::to_contiguous (src/core/backend.hpp:224-226; CPU kernel
+ * src/backend/cpu_backend.hpp:1139-1156): dst[row-major index] = src[offset + sum idx_d *
+ * strides_d] for a view of up to 6 dimensions; strides and offset in elements, elem_size in
+ * bytes (1, 2, 4 or 8 — whatever the dtype). Views whose last dimension is contiguous (the
+ * head split / merge permutes of attention) move 16 bytes per thread. */
+int mu_to_contiguous(mu_ctx *ctx, const void *src, void *dst, int ndim, const int *shape,
+                     const long long *strides, long long offset, int elem_size, void *stream);
+/* Backend::get_last_kernel_time_us (src/core/backend.hpp:231; the CUDA reference brackets each
+ * kernel with an event pair, src/backend/cuda_backend.cu:952-961): mu_timer_begin / mu_timer_end
+ * record the context's event pair on `stream` around whatever the caller enqueues in between;
+ * mu_timer_last_us waits for the closing event and returns the device time in microseconds
+ * (0 when no bracket has been closed). */
+int mu_timer_begin(mu_ctx *ctx, void *stream);
+int mu_timer_end(mu_ctx *ctx, void *stream);
+double mu_timer_last_us(mu_ctx *ctx);
 int mu_synchronize(mu_ctx *ctx);
 /* Synchronise `stream`, then report and clear the latched device status. */
 int mu_check(mu_ctx *ctx, void *stream);
@@ -118,6 +136,12 @@ int mu_linear_qkv_heads(mu_ctx *ctx, const void *x, const void *w_qkv, const voi
  * token-major context [B*T, H*D] that feeds out_proj. Block-diagonal masking is
  * implicit (each head attends to itself only). workspace: mu_attention_workspace_bytes. */
 size_t mu_attention_workspace_bytes(int B, int H, int T, int D, int dtype);
+/* mu_attention_workspace_bytes returns 0 where the fused kernel applies (bfloat16, D 64 or 128,
+ * T a multiple of 8). A context switched to the CUDA-core kernels (mu_ctx_force_simt) takes the
+ * composed GEMM -> softmax -> GEMM path for every shape and always needs the [B*H,T,T] score
+ * buffer: this returns that size (0 if it would not fit in 2^46 bytes or B*H*T exceeds 2^31-1,
+ * which mu_attention rejects with MU_ERR_SIZE). */
+size_t mu_attention_workspace_bytes_composed(int B, int H, int T, int D, int dtype);
 int mu_attention(mu_ctx *ctx, const void *q, const void *k, const void *v, void *out, int B, int H,
                  int T, int D, int causal, int kmode, int dtype, void *workspace,
                  size_t workspace_bytes, void *stream);
@@ -131,7 +155,9 @@ int mu_attention(mu_ctx *ctx, const void *q, const void *k, const void *v, void 
  * library image (MU_ATTENTION_STATIC_SCRATCH_BYTES on every device that loads the
  * library, until process exit). It takes no context and calls no cudaMalloc,
  * cudaFree or allocating library routine.
- *  - B*H*T*T*sizeof(dtype) beyond the array is rejected with MU_ERR_SIZE.
+ *  - B*H*T*T*sizeof(dtype) beyond the array is rejected with MU_ERR_SIZE (checked without
+ *    overflow, before anything is launched).
+ *  - The launches need `device` current; the caller's current device is restored on return.
  *  - The first call on a device looks the array up (cudaGetSymbolAddress with
  *    that device current); make that first call before any stream capture.
  *  - All calls share the array: two calls whose kernels overlap on the GPU
@@ -158,8 +184,11 @@ int mu_softmax(mu_ctx *ctx, const void *x, void *y, long long rows, int cols, in
  * (src/nn/pooling.hpp:8-26). weight is [oC,iC,k,k]; stride/pad are square; bias may
  * be NULL. mu_conv2d can fuse the ReLU module and a MaxPool2d(2,2,0) that follow it
  * in a Sequential (relu != 0, pool == 2): y is then [B,oC,oH/2,oW/2].
- * Every output is bit-identical to the reference CPU kernel (same summation order,
- * no fused multiply-add). */
+ * Layers below 2^31 multiply-adds (and every layer on a context with mu_ctx_force_simt) are
+ * bit-identical to the reference CPU kernel (same summation order, no fused multiply-add);
+ * larger ones run as im2col + 3xTF32 on the tensor cores: float32-class accuracy (within the
+ * 1e-4 relative bound), not identical bits. The same split applies to float32 mu_matmul /
+ * mu_linear at 2^31 multiply-adds. */
 int mu_conv2d(mu_ctx *ctx, const void *x, const void *w, const void *bias, void *y, int B, int iC,
               int iH, int iW, int oC, int k, int stride, int pad, int relu, int pool, int dtype,
               void *stream);
@@ -272,6 +301,14 @@ int mu_comm_world(const mu_comm *comm);
 int mu_all_reduce_sum(mu_ctx *ctx, mu_comm *comm, void *buffer, long long n, int dtype,
                       void *stream);
 int mu_comm_check(mu_ctx *ctx, mu_comm *comm);
+/* Host deadline for the collectives enqueued on `stream`: returns MU_OK once the stream has
+ * drained, or after timeout_ms (<= 0: MUNET_ALLREDUCE_TIMEOUT_MS, default 10000, the reference's
+ * variable and default) aborts the communicator and returns MU_ERR_TIMEOUT with the reference's
+ * message "all_reduce: timeout waiting for participants" (src/core/all_reduce_runtime.hpp:205-225:
+ * a participant that never arrives). mu_comm_abort is ncclCommAbort: the communicator is unusable
+ * afterwards and every later call on it fails. */
+int mu_comm_wait(mu_ctx *ctx, mu_comm *comm, void *stream, int timeout_ms);
+int mu_comm_abort(mu_comm *comm);
 
 /* ---- compiled inference executor -------------------------------------------
  * Stands in for munet::inference::Engine (src/inference.hpp:292-801) and
@@ -294,7 +331,8 @@ typedef struct mu_engine mu_engine;
 int mu_engine_create(mu_ctx *ctx, mu_engine **out);
 void mu_engine_destroy(mu_engine *engine);
 const char *mu_engine_last_error(const mu_engine *engine);
-/* options: "kmode" (mu_kmode), "use_graph" (0/1), "argmax" (0/1: also produce int32 argmax) */
+/* options: "kmode" (mu_kmode), "use_graph" (0/1), "argmax" (0/1: also produce int32 argmax),
+ * "plan_cache_entries" (plans kept under a wildcard contract). Set them before the first compile. */
 int mu_engine_set_option(mu_engine *engine, const char *name, int value);
 int mu_engine_load(mu_engine *engine, const char *artifact_path, int compute_dtype);
 /* shapes: all tensors' dims concatenated, ndims[i] of them per tensor */
@@ -310,6 +348,18 @@ int mu_engine_load_memory(mu_engine *engine, const char *config_json, int n_tens
  * the all-reduce of one chunk on a second stream under the GEMM of the next. */
 int mu_engine_set_comm(mu_engine *engine, mu_comm *comm);
 int mu_engine_compile(mu_engine *engine, const int *input_shape, int ndim, int input_dtype);
+/* Engine::compile(example, expected_input_shape) with -1 wildcards (detail::ShapeContract,
+ * src/inference.hpp:128-176; tests/test_inference.cpp:402-438): expected_shape[i] == -1 lets
+ * dimension i vary from run to run (NULL = the example's exact shape). The plan for the example
+ * shape is built now; mu_engine_select_shape makes the plan of another shape that fits the
+ * contract the active one, building it on first sight (weights are shared, each plan has its own
+ * arena and graph; option "plan_cache_entries", default 8, bounds how many are kept, least
+ * recently used first out). A shape that breaks the contract is refused with the reference's
+ * words ("rank mismatch" / "dim mismatch at index i"). mu_engine_run always runs the active plan. */
+int mu_engine_compile_contract(mu_engine *engine, const int *example_shape, int ndim,
+                               const int *expected_shape, int input_dtype);
+int mu_engine_select_shape(mu_engine *engine, const int *shape, int ndim);
+int mu_engine_plan_count(const mu_engine *engine);
 int mu_engine_output_shape(const mu_engine *engine, int *shape, int *ndim, int *dtype);
 int mu_engine_stats(const mu_engine *engine, long long *arena_bytes, long long *weight_bytes,
                     long long *n_ops, long long *n_launches, long long *unplanned_bytes);

@@ -45,6 +45,11 @@ SIGNATURES = {
     "mu_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "mu_free": (_i, [_vp, _vp]),
     "mu_copy": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
+    "mu_memset": (_i, [_vp, _vp, _i, _sz, _vp]),
+    "mu_to_contiguous": (_i, [_vp, _vp, _vp, _i, C.POINTER(_i), C.POINTER(_ll), _ll, _i, _vp]),
+    "mu_timer_begin": (_i, [_vp, _vp]),
+    "mu_timer_end": (_i, [_vp, _vp]),
+    "mu_timer_last_us": (C.c_double, [_vp]),
     "mu_synchronize": (_i, [_vp]),
     "mu_check": (_i, [_vp, _vp]),
     "mu_matmul": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
@@ -53,6 +58,7 @@ SIGNATURES = {
     "mu_linear_qkv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "mu_linear_qkv_heads": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "mu_attention_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "mu_attention_workspace_bytes_composed": (_sz, [_i, _i, _i, _i, _i]),
     "mu_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "mu_attention_static_scratch": (_i, [_i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i,
                                          C.c_char_p, _sz]),
@@ -84,6 +90,8 @@ SIGNATURES = {
     "mu_comm_world": (_i, [_vp]),
     "mu_all_reduce_sum": (_i, [_vp, _vp, _vp, _ll, _i, _vp]),
     "mu_comm_check": (_i, [_vp, _vp]),
+    "mu_comm_wait": (_i, [_vp, _vp, _vp, _i]),
+    "mu_comm_abort": (_i, [_vp]),
     "mu_engine_create": (_i, [_vp, C.POINTER(_vp)]),
     "mu_engine_destroy": (None, [_vp]),
     "mu_engine_last_error": (C.c_char_p, [_vp]),
@@ -93,6 +101,9 @@ SIGNATURES = {
                                    C.POINTER(_i), C.POINTER(_i), C.POINTER(_ll), _i, _i]),
     "mu_engine_set_comm": (_i, [_vp, _vp]),
     "mu_engine_compile": (_i, [_vp, C.POINTER(_i), _i, _i]),
+    "mu_engine_compile_contract": (_i, [_vp, C.POINTER(_i), _i, C.POINTER(_i), _i]),
+    "mu_engine_select_shape": (_i, [_vp, C.POINTER(_i), _i]),
+    "mu_engine_plan_count": (_i, [_vp]),
     "mu_engine_output_shape": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "mu_engine_stats": (_i, [_vp] + [C.POINTER(_ll)] * 5),
     "mu_engine_run": (_i, [_vp, _vp, _i, _vp, _i, _vp, _i, _vp]),
@@ -186,6 +197,25 @@ class Context:
 
     def synchronize(self):
         self._rc(self._lib.mu_synchronize(self._h))
+
+    def memset(self, ptr, value: int, nbytes: int, stream=None):
+        self._rc(self._lib.mu_memset(self._h, _ptr(ptr), int(value), int(nbytes), _stream(stream)))
+
+    def to_contiguous(self, src, dst, shape, strides, offset: int, elem_size: int, stream=None):
+        """Row-major copy of a strided view (strides / offset in elements, at most 6 dims)."""
+        n = len(shape)
+        self._rc(self._lib.mu_to_contiguous(
+            self._h, _ptr(src), _ptr(dst), n, (C.c_int * max(n, 1))(*shape),
+            (C.c_longlong * max(n, 1))(*strides), int(offset), int(elem_size), _stream(stream)))
+
+    def timer_begin(self, stream=None):
+        self._rc(self._lib.mu_timer_begin(self._h, _stream(stream)))
+
+    def timer_end(self, stream=None):
+        self._rc(self._lib.mu_timer_end(self._h, _stream(stream)))
+
+    def timer_last_us(self) -> float:
+        return float(self._lib.mu_timer_last_us(self._h))
 
     # -- BLAS ----------------------------------------------------------------
     def matmul(self, a, b, c, M, K, N, dtype, transA=False, transB=False, stream=None):
@@ -348,6 +378,17 @@ class Comm:
         rc = self._lib.mu_comm_check(self.ctx._h, self._h)
         if rc != 0:
             raise MuNetError(rc, self._lib.mu_last_error(self.ctx._h).decode())
+
+    def wait(self, stream=None, timeout_ms: int = 0):
+        """Host deadline for the collectives enqueued on ``stream`` (0 = MUNET_ALLREDUCE_TIMEOUT_MS
+        or 10 s): raises MuNetError(MU_ERR_TIMEOUT) and aborts the communicator when a participant
+        never arrives."""
+        rc = self._lib.mu_comm_wait(self.ctx._h, self._h, _stream(stream), int(timeout_ms))
+        if rc != 0:
+            raise MuNetError(rc, self._lib.mu_last_error(self.ctx._h).decode())
+
+    def abort(self):
+        self._lib.mu_comm_abort(self._h)
 
     def close(self):
         if getattr(self, "_h", None):

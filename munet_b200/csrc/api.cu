@@ -190,9 +190,12 @@ int mu_ctx_create(int device, mu_ctx **out) {
   return MU_OK;
 }
 
+void mu_timer_release(mu_ctx *ctx); // memory_ops.cu
+
 void mu_ctx_destroy(mu_ctx *ctx) {
   if (!ctx)
     return;
+  mu_timer_release(ctx);
   if (ctx->d_status)
     cudaFree(ctx->d_status);
   delete ctx;
@@ -414,6 +417,28 @@ int mu_linear_qkv(mu_ctx *ctx, const void *x, const void *w_qkv, const void *bia
   return mu_linear_qkv_heads(ctx, x, w_qkv, bias_qkv, q, k, v, B, T, E, H, E / H, dtype, stream);
 }
 
+// Bytes of the [B*H, T, T] score matrix of the composed path, or false when the product (or
+// B*H*T, which the kernels index with 32-bit tile coordinates) does not fit: the factors are
+// bounded by division so that nothing wraps.
+static bool score_bytes(int B, int H, int T, int dtype, size_t *out) {
+  const unsigned long long es = esize(dtype), uB = B, uH = H, uT = T;
+  const unsigned long long cap = 1ull << 46; // 64 TiB: far beyond any device, far below 2^64
+  if (uB * uH > 0x7fffffffull || uB * uH * uT > 0x7fffffffull)
+    return false;
+  if (uT > cap / uT || uB * uH > cap / (uT * uT) / es)
+    return false;
+  *out = static_cast<size_t>(uB * uH * uT * uT * es);
+  return true;
+}
+
+size_t mu_attention_workspace_bytes_composed(int B, int H, int T, int D, int dtype) {
+  (void)D;
+  size_t n = 0;
+  if (B <= 0 || H <= 0 || T <= 0 || !score_bytes(B, H, T, dtype, &n))
+    return 0;
+  return n;
+}
+
 size_t mu_attention_workspace_bytes(int B, int H, int T, int D, int dtype) {
   if (B <= 0 || H <= 0 || T <= 0)
     return 0;
@@ -421,7 +446,7 @@ size_t mu_attention_workspace_bytes(int B, int H, int T, int D, int dtype) {
   if (dtype == MU_BF16 && (D == 64 || D == 128) && T % 8 == 0)
     return 0;
   // composed path: one [B*H, T, T] score/probability buffer (softmax runs in place)
-  return static_cast<size_t>(B) * H * T * T * esize(dtype);
+  return mu_attention_workspace_bytes_composed(B, H, T, D, dtype);
 }
 
 int mu_attention(mu_ctx *ctx, const void *q, const void *k, const void *v, void *out, int B, int H,
@@ -449,7 +474,10 @@ int mu_attention(mu_ctx *ctx, const void *q, const void *k, const void *v, void 
       return cuda_fail(ctx, "attention", cudaGetLastError());
   }
   // composed path (any head size, float32): batched GEMM → softmax → batched GEMM
-  const size_t need = static_cast<size_t>(B) * H * T * T * esize(dtype);
+  size_t need = 0;
+  if (!score_bytes(B, H, T, dtype, &need))
+    return fail(ctx, MU_ERR_SIZE, "attention: B=%d H=%d T=%d is beyond what the kernels can index", B,
+                H, T);
   MU_REQUIRE(workspace && workspace_bytes >= need,
              "attention: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
   const int BH = B * H;

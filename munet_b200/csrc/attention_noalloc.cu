@@ -97,16 +97,33 @@ extern "C" int mu_attention_static_scratch(int device, const void *q, const void
   if (!q || !k || !v || !out)
     return fail(err, err_len, MU_ERR_INVALID, "attention: null pointer");
   const size_t es = dtype == MU_F32 ? 4 : 2;
-  const unsigned long long need = 1ull * B * H * T * T * es;
-  if (need > MU_ATTENTION_STATIC_SCRATCH_BYTES)
+  // B*H*T*T*es can wrap in 64 bits (e.g. B = H = 32768, T = 65536, fp32 is 2^64): divide the
+  // limit down factor by factor instead of multiplying the sizes up.
+  const unsigned long long cap = MU_ATTENTION_STATIC_SCRATCH_BYTES / es;
+  const unsigned long long uB = B, uH = H, uT = T;
+  if (uT > cap / uT || uH > cap / (uT * uT) || uB > cap / (uT * uT * uH))
     return fail(err, err_len, MU_ERR_SIZE,
-                "attention: B*H*T*T*%zu = %llu bytes of scores exceed the built-in scratch of %u "
-                "bytes; use mu_attention with a caller-provided workspace",
-                es, need, MU_ATTENTION_STATIC_SCRATCH_BYTES);
+                "attention: B*H*T*T*%zu bytes of scores (B=%d H=%d T=%d) exceed the built-in scratch "
+                "of %u bytes; use mu_attention with a caller-provided workspace",
+                es, B, H, T, MU_ATTENTION_STATIC_SCRATCH_BYTES);
 
-  int cur = -1;
-  if (cudaGetDevice(&cur) != cudaSuccess || (cur != device && cudaSetDevice(device) != cudaSuccess))
-    return fail(err, err_len, MU_ERR_CUDA, "attention: cannot select device %d", device);
+  // The launches below need `device` current; the caller's current device is put back on
+  // every way out.
+  struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    ~DeviceGuard() {
+      if (switched)
+        cudaSetDevice(prev);
+    }
+  } guard;
+  if (cudaGetDevice(&guard.prev) != cudaSuccess)
+    return fail(err, err_len, MU_ERR_CUDA, "attention: cannot query the current device");
+  if (guard.prev != device) {
+    if (cudaSetDevice(device) != cudaSuccess)
+      return fail(err, err_len, MU_ERR_CUDA, "attention: cannot select device %d", device);
+    guard.switched = true;
+  }
 
   PerDevice pd;
   {
@@ -172,8 +189,12 @@ extern "C" int mu_attention_static_scratch(int device, const void *q, const void
     ep.round_each = 1;
     rc = gemm(pd, op, sh, ep, dtype, st);
   }
+  if (rc == 1)
+    return fail(err, err_len, MU_ERR_INVALID,
+                "attention: B=%d H=%d T=%d D=%d is outside what the kernels of the composed path "
+                "address (nothing was launched for the rejected step)", B, H, T, D);
   if (rc != 0)
-    return fail(err, err_len, rc == 1 ? MU_ERR_INVALID : MU_ERR_CUDA, "attention: launch failed: %s",
+    return fail(err, err_len, MU_ERR_CUDA, "attention: launch failed: %s",
                 cudaGetErrorString(cudaGetLastError()));
   if (sync_and_check) {
     cudaError_t e = cudaStreamSynchronize(st);

@@ -16,10 +16,11 @@
 //             buffered TMEM O tile.
 //   warps 2-9 two threads per query row (TMEM lane = row, each owns half of the
 //             columns; two warps per scheduler): rounding/scale/mask,
-//             running max and sum, P_j → swizzled smem (A operand of P·V),
-//             O accumulated in registers with the online-softmax correction,
-//             final O/l staged to smem and written with TMA (token-major,
-//             heads merged: the [B,T,H·D] layout out_proj consumes).
+//             running max and sum, P_j → swizzled smem (A operand of P·V);
+//             O accumulates in TMEM over the key tiles of a work and is rescaled in
+//             place only when the row maximum has grown by more than 2^8; the final
+//             O/l is staged to smem and written with TMA (token-major, heads merged:
+//             the [B,T,H·D] layout out_proj consumes).
 // K addressing: LITERAL reads K's [N,D] buffer as a row-major [D,N] matrix
 // (what the reference computes, see include/munet_b200.h), MATH is Q·Kᵀ.
 // Numerics follow the reference's bf16 pipeline where it is cheap to: scores are

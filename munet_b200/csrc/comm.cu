@@ -10,7 +10,10 @@
 // memory themselves.
 #include "../../include/munet_b200.h"
 #include <cstdio>
+#include <chrono>
+#include <cstdlib>
 #include <cstring>
+#include <thread>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 #include <mutex>
@@ -39,7 +42,10 @@ NcclApi &api() {
   static NcclApi a;
   static std::once_flag once;
   std::call_once(once, [] {
-    a.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    // MUNET_B200_NCCL_LIBRARY names another library with the same entry points (a site build of
+    // NCCL; the tests put a stand-in there whose collective never completes in time).
+    const char *path = getenv("MUNET_B200_NCCL_LIBRARY");
+    a.handle = dlopen((path && path[0]) ? path : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
     if (!a.handle)
       return;
     auto sym = [&](const char *n) { return dlsym(a.handle, n); };
@@ -60,6 +66,7 @@ NcclApi &api() {
 struct mu_comm {
   NcclComm comm = nullptr;
   int rank = 0, world = 1;
+  bool aborted = false; // ncclCommAbort has run: the handle is gone, every later call fails
 };
 
 extern "C" {
@@ -103,7 +110,7 @@ int mu_comm_create(mu_ctx *ctx, const void *unique_id, int rank, int world, mu_c
 void mu_comm_destroy(mu_comm *comm) {
   if (!comm)
     return;
-  if (comm->comm)
+  if (comm->comm && !comm->aborted)
     api().CommDestroy(comm->comm);
   delete comm;
 }
@@ -122,6 +129,8 @@ int mu_all_reduce_sum(mu_ctx *ctx, mu_comm *comm, void *buffer, long long n, int
     return MU_OK; // a single participant: the sum is the buffer itself
   if (!buffer)
     return mu_set_error(ctx, MU_ERR_INVALID, "all_reduce: null buffer");
+  if (comm->aborted)
+    return mu_set_error(ctx, MU_ERR_CUDA, "all_reduce: the communicator was aborted after a timeout");
   int nd;
   if (dtype == MU_F32) nd = kNcclFloat32;
   else if (dtype == MU_BF16) nd = kNcclBfloat16;
@@ -142,6 +151,8 @@ int mu_comm_check(mu_ctx *ctx, mu_comm *comm) {
     return MU_ERR_INVALID;
   if (!comm || !comm->comm)
     return MU_OK;
+  if (comm->aborted)
+    return mu_set_error(ctx, MU_ERR_CUDA, "all_reduce: the communicator was aborted after a timeout");
   NcclApi &a = api();
   if (!a.CommGetAsyncError)
     return MU_OK;
@@ -150,5 +161,60 @@ int mu_comm_check(mu_ctx *ctx, mu_comm *comm) {
   if (rc != kNcclSuccess || async_err != kNcclSuccess)
     return mu_set_error(ctx, MU_ERR_CUDA, a.GetErrorString(rc != kNcclSuccess ? rc : async_err));
   return MU_OK;
+}
+
+// Tear the communicator down without waiting for the peers (ncclCommAbort): collectives of this
+// rank that are still in flight end, the handle becomes unusable.
+int mu_comm_abort(mu_comm *comm) {
+  if (!comm || !comm->comm || comm->aborted)
+    return MU_OK;
+  NcclApi &a = api();
+  comm->aborted = true;
+  if (a.CommAbort)
+    a.CommAbort(comm->comm);
+  return MU_OK;
+}
+
+// Host deadline around the collectives already enqueued on `stream`: polls the stream (and the
+// communicator's asynchronous error) until the work has completed or `timeout_ms` has passed.
+// The reference waits that long for every participant to arrive and then throws
+// "all_reduce: timeout waiting for participants" (src/core/all_reduce_runtime.hpp:205-225,
+// MUNET_ALLREDUCE_TIMEOUT_MS, default 10 s). A participant that never joins shows up here the
+// same way: the collective cannot finish, the deadline passes, the communicator is aborted so
+// that nothing of it stays on the device, and MU_ERR_TIMEOUT comes back with that message.
+int mu_comm_wait(mu_ctx *ctx, mu_comm *comm, void *stream, int timeout_ms) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  if (timeout_ms <= 0) {
+    const char *env = getenv("MUNET_ALLREDUCE_TIMEOUT_MS");
+    timeout_ms = env ? atoi(env) : 0;
+    if (timeout_ms <= 0)
+      timeout_ms = 10000;
+  }
+  const auto t0 = std::chrono::steady_clock::now();
+  NcclApi &a = api();
+  for (;;) {
+    const cudaError_t q = cudaStreamQuery(static_cast<cudaStream_t>(stream));
+    if (q == cudaSuccess)
+      return MU_OK;
+    if (q != cudaErrorNotReady)
+      return mu_set_error(ctx, MU_ERR_CUDA, cudaGetErrorString(q));
+    if (comm && comm->comm && !comm->aborted && a.CommGetAsyncError) {
+      int async_err = 0;
+      if (a.CommGetAsyncError(comm->comm, &async_err) == kNcclSuccess && async_err != kNcclSuccess) {
+        mu_comm_abort(comm);
+        return mu_set_error(ctx, MU_ERR_CUDA, a.GetErrorString(async_err));
+      }
+    }
+    const auto waited = std::chrono::duration_cast<std::chrono::milliseconds>(
+                            std::chrono::steady_clock::now() - t0).count();
+    if (waited >= timeout_ms) {
+      mu_comm_abort(comm);
+      char msg[160];
+      snprintf(msg, sizeof(msg), "all_reduce: timeout waiting for participants (waited %d ms)", timeout_ms);
+      return mu_set_error(ctx, MU_ERR_TIMEOUT, msg);
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(200));
+  }
 }
 }

@@ -32,6 +32,8 @@
 using mu::Json;
 using mu::NamedTensor;
 
+extern "C" int mu_ctx_simt_forced(const mu_ctx *ctx); // api.cu
+
 namespace {
 
 enum OpKind {
@@ -96,6 +98,26 @@ uint16_t f2bf(float v) { // RNE exactly like the reference (src/types.hpp:311-31
 
 } // namespace
 
+// Everything that depends on the concrete input shape: the lowered op list, the arena behind it
+// and the captured graph. An engine keeps one of these per shape it has met under a wildcard
+// contract; the weights are staged once and shared by all of them.
+struct PlanState {
+  std::vector<Tensor> tensors;
+  std::vector<Op> ops;
+  void *arena = nullptr;
+  void *input_buf = nullptr;
+  size_t arena_bytes = 0, input_bytes = 0;
+  std::vector<int> in_shape, out_shape;
+  int in_dtype = MU_F32, out_dtype = MU_F32;
+  int out_tid = -1, argmax_tid = -1;
+  cudaGraphExec_t gexec = nullptr;
+  cudaGraph_t graph = nullptr;
+  long long n_launches = 0;
+  int n_events = 0;
+  std::vector<cudaEvent_t> events;
+  unsigned long long last_used = 0;
+};
+
 struct mu_engine {
   mu_ctx *ctx = nullptr;
   int dtype = MU_F32; // compute dtype of floating tensors
@@ -122,6 +144,7 @@ struct mu_engine {
   void *arena = nullptr;
   void *input_buf = nullptr;
   size_t arena_bytes = 0, weight_bytes = 0, input_bytes = 0;
+  size_t weights_uploaded = 0; // how many entries of `weights` already live in the slab
   std::vector<int> in_shape, out_shape;
   int in_dtype = MU_F32, out_dtype = MU_F32;
   int out_tid = -1, argmax_tid = -1;
@@ -130,6 +153,57 @@ struct mu_engine {
   cudaStream_t cap_stream = nullptr;
   long long n_launches = 0;
   char err[768] = {0};
+  // Shape contract of compile(): extents the input must have, -1 = any
+  // (detail::ShapeContract, src/inference.hpp:128-176). Plans of other shapes that satisfy it
+  // wait in `parked`; the members above are the active plan.
+  std::vector<int> contract;
+  std::vector<PlanState> parked;
+  int plan_cache_entries = 8;
+  unsigned long long use_clock = 0;
+
+  void park_active() {
+    PlanState p;
+    p.tensors.swap(tensors), p.ops.swap(ops);
+    p.arena = arena, p.input_buf = input_buf, arena = nullptr, input_buf = nullptr;
+    p.arena_bytes = arena_bytes, p.input_bytes = input_bytes;
+    p.in_shape.swap(in_shape), p.out_shape.swap(out_shape);
+    p.in_dtype = in_dtype, p.out_dtype = out_dtype, p.out_tid = out_tid, p.argmax_tid = argmax_tid;
+    p.gexec = gexec, p.graph = graph, gexec = nullptr, graph = nullptr;
+    p.n_launches = n_launches, p.n_events = n_events, n_events = 0;
+    p.events.swap(events);
+    p.last_used = use_clock;
+    out_tid = argmax_tid = -1;
+    parked.push_back(std::move(p));
+  }
+  void activate(size_t i) {
+    PlanState p = std::move(parked[i]);
+    parked.erase(parked.begin() + static_cast<long>(i));
+    tensors.swap(p.tensors), ops.swap(p.ops);
+    arena = p.arena, input_buf = p.input_buf, arena_bytes = p.arena_bytes, input_bytes = p.input_bytes;
+    in_shape.swap(p.in_shape), out_shape.swap(p.out_shape);
+    in_dtype = p.in_dtype, out_dtype = p.out_dtype, out_tid = p.out_tid, argmax_tid = p.argmax_tid;
+    gexec = p.gexec, graph = p.graph, n_launches = p.n_launches, n_events = p.n_events;
+    events.swap(p.events);
+  }
+  void free_plan(PlanState &p) {
+    if (p.gexec) cudaGraphExecDestroy(p.gexec);
+    if (p.graph) cudaGraphDestroy(p.graph);
+    for (auto &ev : p.events) cudaEventDestroy(ev);
+    if (p.arena) mu_free(ctx, p.arena);
+    if (p.input_buf) mu_free(ctx, p.input_buf);
+  }
+  // the active plan only (weights stay)
+  void release_active_plan() {
+    if (gexec) cudaGraphExecDestroy(gexec), gexec = nullptr;
+    if (graph) cudaGraphDestroy(graph), graph = nullptr;
+    for (auto &ev : events) cudaEventDestroy(ev);
+    events.clear(), n_events = 0;
+    if (arena) mu_free(ctx, arena), arena = nullptr;
+    if (input_buf) mu_free(ctx, input_buf), input_buf = nullptr;
+    tensors.clear(), ops.clear();
+    out_tid = argmax_tid = -1;
+  }
+  int build_plan(const std::vector<int> &shape, int input_dtype);
 
   int fail(int code, const char *fmt, ...) {
     va_list ap;
@@ -139,19 +213,22 @@ struct mu_engine {
     return code;
   }
 
+  // every plan, but not the weights: compile() with a new contract starts from here
+  void release_plans() {
+    release_active_plan();
+    for (auto &p : parked) free_plan(p);
+    parked.clear();
+    contract.clear();
+    compiled = false;
+  }
   void release_compiled() {
-    if (gexec) cudaGraphExecDestroy(gexec), gexec = nullptr;
-    if (graph) cudaGraphDestroy(graph), graph = nullptr;
+    release_plans();
     if (cap_stream) cudaStreamDestroy(cap_stream), cap_stream = nullptr;
-    for (auto &ev : events) cudaEventDestroy(ev);
-    events.clear(), n_events = 0;
     if (side_stream) cudaStreamDestroy(side_stream), side_stream = nullptr;
     if (weight_slab) mu_free(ctx, weight_slab), weight_slab = nullptr;
-    if (arena) mu_free(ctx, arena), arena = nullptr;
-    if (input_buf) mu_free(ctx, input_buf), input_buf = nullptr;
-    tensors.clear(), ops.clear(), weights.clear(), weight_ids.clear();
+    weights.clear(), weight_ids.clear();
     weight_stage.clear(), dev_copies.clear(), dev_weight.clear();
-    compiled = false;
+    weight_bytes = 0, weights_uploaded = 0;
   }
 
   // ---- lowering helpers ----------------------------------------------------
@@ -443,7 +520,9 @@ int mu_engine::lower_mha(const std::string &prefix, int E, int H, bool causal, i
   a.kind = OP_ATTN;
   a.in = q.out;
   a.B = B, a.T = T, a.H = H, a.D = D, a.causal = causal;
-  a.ws_bytes = mu_attention_workspace_bytes(B, H, T, D, dtype);
+  // a context forced onto the CUDA-core kernels runs the composed path for every shape
+  a.ws_bytes = mu_ctx_simt_forced(ctx) ? mu_attention_workspace_bytes_composed(B, H, T, D, dtype)
+                                       : mu_attention_workspace_bytes(B, H, T, D, dtype);
   a.ws = new_tensor(a.ws_bytes);
   a.out = new_tensor(per);
   push(a);
@@ -804,14 +883,21 @@ int mu_engine::plan_and_allocate() {
   }
   int rc = mu_alloc(ctx, std::max<size_t>(arena_bytes, 16), &arena);
   if (rc) return fail(rc, "arena allocation of %zu bytes failed: %s", arena_bytes, mu_last_error(ctx));
-  rc = mu_alloc(ctx, std::max<size_t>(weight_bytes, 16), &weight_slab);
-  if (rc) return fail(rc, "weight slab allocation of %zu bytes failed: %s", weight_bytes, mu_last_error(ctx));
   rc = mu_alloc(ctx, std::max<size_t>(input_bytes, 16), &input_buf);
   if (rc) return fail(rc, "input buffer allocation failed: %s", mu_last_error(ctx));
   // the warm-up forward of compile() reads this buffer before any run(): all-zero
   // ids / activations are valid inputs for every op
   if (cudaMemset(input_buf, 0, std::max<size_t>(input_bytes, 16)) != cudaSuccess)
     return fail(MU_ERR_CUDA, "input buffer clear failed");
+  if (weight_slab) {
+    // a further plan of an engine whose weights are already on the device: the module tree is
+    // the same, so lowering must have found every parameter in the slab
+    if (weights.size() != weights_uploaded)
+      return fail(MU_ERR_INVALID, "Engine: this input shape needs parameters the first plan did not stage");
+    return MU_OK;
+  }
+  rc = mu_alloc(ctx, std::max<size_t>(weight_bytes, 16), &weight_slab);
+  if (rc) return fail(rc, "weight slab allocation of %zu bytes failed: %s", weight_bytes, mu_last_error(ctx));
   // upload weights: host-staged ones in one copy per contiguous run, device ones D2D
   for (size_t i = 0; i < weights.size(); ++i) {
     const Weight &w = weights[i];
@@ -825,6 +911,8 @@ int mu_engine::plan_and_allocate() {
                      d.rows, cudaMemcpyDeviceToDevice) != cudaSuccess)
       return fail(MU_ERR_CUDA, "weight copy failed: %s", cudaGetErrorString(cudaGetLastError()));
   std::vector<uint8_t>().swap(weight_stage);
+  dev_copies.clear();
+  weights_uploaded = weights.size();
   return MU_OK;
 }
 
@@ -1079,6 +1167,7 @@ int mu_engine_set_option(mu_engine *e, const char *name, int value) {
   else if (n == "tp_size") e->tp_size = value;
   else if (n == "tp_overlap") e->tp_overlap = value;
   else if (n == "tp_comm_sms") e->tp_comm_sms = value;
+  else if (n == "plan_cache_entries") e->plan_cache_entries = value;
   else return e->fail(MU_ERR_INVALID, "unknown option '%s'", name);
   return MU_OK;
 }
@@ -1132,8 +1221,79 @@ int mu_engine_set_comm(mu_engine *e, mu_comm *comm) {
   return MU_OK;
 }
 
-int mu_engine_compile(mu_engine *e, const int *input_shape, int ndim, int input_dtype) {
-  if (!e || !input_shape || ndim <= 0) return MU_ERR_INVALID;
+// Lower, plan and capture the forward for one concrete input shape into the active plan
+// (which must be empty). The weights are staged and uploaded by the first plan only.
+int mu_engine::build_plan(const std::vector<int> &shape, int input_dtype) {
+  Val v;
+  v.shape = shape;
+  v.dtype = input_dtype;
+  in_shape = v.shape, in_dtype = input_dtype;
+  input_bytes = static_cast<size_t>(v.numel()) * esize(input_dtype);
+  v.tid = new_tensor(input_bytes);
+  tensors[v.tid].external = true;
+  const bool first = weight_slab == nullptr;
+  used_params.clear();
+  int rc = lower(config, "", v, nullptr, nullptr);
+  if (rc) return rc;
+  // Every serialized tensor must belong to a module of the tree, as in the reference's loader
+  // (src/inference_serialization.cpp:1043-1051). BatchNorm2d's momentum-only state and Dropout
+  // have no tensors, so anything left over is a mismatch between config and payload.
+  if (first)
+    for (const auto &kv : params)
+      if (!used_params.count(kv.first))
+        return fail(MU_ERR_INVALID,
+                    "Serialized tensor '%s' does not match any named parameter/buffer in the "
+                    "reconstructed module", kv.first.c_str());
+  out_tid = v.tid, out_shape = v.shape, out_dtype = v.dtype;
+  if (want_argmax) {
+    Op a;
+    a.kind = OP_ARGMAX, a.N = v.shape.back(), a.M = static_cast<int>(v.numel() / a.N);
+    a.in = v.tid, a.out = new_tensor(static_cast<size_t>(a.M) * 4);
+    push(a);
+    argmax_tid = a.out;
+  }
+  // the outputs stay live to the end of the plan
+  const int last = static_cast<int>(ops.size());
+  touch(out_tid, last);
+  if (argmax_tid >= 0) touch(argmax_tid, last);
+  rc = plan_and_allocate();
+  if (rc) return rc;
+  if (use_graph) {
+    if (!cap_stream && cudaStreamCreateWithFlags(&cap_stream, cudaStreamNonBlocking) != cudaSuccess)
+      return fail(MU_ERR_CUDA, "stream creation failed");
+    // warm-up launch outside capture (sets per-kernel attributes), then capture
+    rc = launch_all(cap_stream);
+    if (rc) return rc;
+    rc = mu_check(ctx, cap_stream);
+    if (rc) return fail(rc, "warm-up forward failed: %s", mu_last_error(ctx));
+    if (cudaStreamBeginCapture(cap_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
+      return fail(MU_ERR_CUDA, "graph capture could not start");
+    rc = launch_all(cap_stream);
+    cudaError_t ce = cudaStreamEndCapture(cap_stream, &graph);
+    if (rc) return rc;
+    if (ce != cudaSuccess) return fail(MU_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
+    ce = cudaGraphInstantiate(&gexec, graph, 0);
+    if (ce != cudaSuccess) return fail(MU_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(ce));
+  }
+  return MU_OK;
+}
+
+// Why `actual` breaks the contract, in the reference's words (ShapeContract::mismatch_reason,
+// src/inference.hpp:162-176); nullptr when it fits.
+static const char *contract_mismatch(const std::vector<int> &contract, const int *actual, int ndim,
+                                     int *index) {
+  if (static_cast<int>(contract.size()) != ndim) return "rank mismatch";
+  for (int i = 0; i < ndim; ++i)
+    if (contract[i] != -1 && contract[i] != actual[i]) {
+      *index = i;
+      return "dim mismatch at index";
+    }
+  return nullptr;
+}
+
+int mu_engine_compile_contract(mu_engine *e, const int *example_shape, int ndim,
+                               const int *expected_shape, int input_dtype) {
+  if (!e || !example_shape || ndim <= 0) return MU_ERR_INVALID;
   if (!e->loaded) return e->fail(MU_ERR_INVALID, "Engine: no module loaded");
   if (e->tp_size < 1 || e->tp_rank < 0 || e->tp_rank >= e->tp_size)
     return e->fail(MU_ERR_INVALID, "Engine: bad tensor-parallel rank %d of %d", e->tp_rank, e->tp_size);
@@ -1147,63 +1307,83 @@ int mu_engine_compile(mu_engine *e, const int *input_shape, int ndim, int input_
                    "across all heads and cannot be sharded by head)");
   if (e->tp_size > 1 && e->want_argmax)
     return e->fail(MU_ERR_UNSUPPORTED, "Engine: argmax over a vocabulary-sharded head is not implemented");
-  e->release_compiled();
-  e->weight_bytes = 0;
-  Val v;
-  v.shape.assign(input_shape, input_shape + ndim);
-  v.dtype = input_dtype;
-  for (int s : v.shape)
-    if (s <= 0) return e->fail(MU_ERR_INVALID, "Engine: compile needs a concrete positive input shape");
+  for (int i = 0; i < ndim; ++i)
+    if (example_shape[i] <= 0)
+      return e->fail(MU_ERR_INVALID, "Engine: compile needs a concrete positive input shape");
   if (input_dtype != MU_I32 && input_dtype != e->dtype)
     return e->fail(MU_ERR_INVALID, "Engine: input dtype %d does not match compute dtype %d", input_dtype, e->dtype);
-  e->in_shape = v.shape, e->in_dtype = input_dtype;
-  e->input_bytes = static_cast<size_t>(v.numel()) * esize(input_dtype);
-  v.tid = e->new_tensor(e->input_bytes);
-  e->tensors[v.tid].external = true;
-  e->used_params.clear();
-  int rc = e->lower(e->config, "", v, nullptr, nullptr);
-  if (rc) return rc;
-  // Every serialized tensor must belong to a module of the tree, as in the reference's loader
-  // (src/inference_serialization.cpp:1043-1051). BatchNorm2d's momentum-only state and Dropout
-  // have no tensors, so anything left over is a mismatch between config and payload.
-  for (const auto &kv : e->params)
-    if (!e->used_params.count(kv.first))
-      return e->fail(MU_ERR_INVALID,
-                     "Serialized tensor '%s' does not match any named parameter/buffer in the "
-                     "reconstructed module", kv.first.c_str());
-  e->out_tid = v.tid, e->out_shape = v.shape, e->out_dtype = v.dtype;
-  if (e->want_argmax) {
-    Op a;
-    a.kind = OP_ARGMAX, a.N = v.shape.back(), a.M = static_cast<int>(v.numel() / a.N);
-    a.in = v.tid, a.out = e->new_tensor(static_cast<size_t>(a.M) * 4);
-    e->push(a);
-    e->argmax_tid = a.out;
+  std::vector<int> contract(example_shape, example_shape + ndim);
+  if (expected_shape) {
+    contract.assign(expected_shape, expected_shape + ndim);
+    for (int i = 0; i < ndim; ++i)
+      if (contract[i] != -1 && contract[i] <= 0)
+        return e->fail(MU_ERR_INVALID, "Engine: expected input shape holds positive extents or -1");
+    int idx = 0;
+    if (const char *why = contract_mismatch(contract, example_shape, ndim, &idx))
+      return e->fail(MU_ERR_INVALID, "Engine compile input shape mismatch: %s %d", why, idx);
   }
-  // the outputs stay live to the end of the plan
-  const int last = static_cast<int>(e->ops.size());
-  e->touch(e->out_tid, last);
-  if (e->argmax_tid >= 0) e->touch(e->argmax_tid, last);
-  rc = e->plan_and_allocate();
-  if (rc) return rc;
-  if (e->use_graph) {
-    if (cudaStreamCreateWithFlags(&e->cap_stream, cudaStreamNonBlocking) != cudaSuccess)
-      return e->fail(MU_ERR_CUDA, "stream creation failed");
-    // warm-up launch outside capture (sets per-kernel attributes), then capture
-    rc = e->launch_all(e->cap_stream);
-    if (rc) return rc;
-    rc = mu_check(e->ctx, e->cap_stream);
-    if (rc) return e->fail(rc, "warm-up forward failed: %s", mu_last_error(e->ctx));
-    if (cudaStreamBeginCapture(e->cap_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
-      return e->fail(MU_ERR_CUDA, "graph capture could not start");
-    rc = e->launch_all(e->cap_stream);
-    cudaError_t ce = cudaStreamEndCapture(e->cap_stream, &e->graph);
-    if (rc) return rc;
-    if (ce != cudaSuccess) return e->fail(MU_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
-    ce = cudaGraphInstantiate(&e->gexec, e->graph, 0);
-    if (ce != cudaSuccess) return e->fail(MU_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(ce));
+  // The weights staged by an earlier compile() stay in their slab (the sources they were read
+  // from may be gone by now); only the plans are rebuilt. Options that change which slices of
+  // the parameters a rank holds ("tp_size", "tp_rank") therefore belong before the first compile.
+  e->release_plans();
+  e->contract = contract;
+  int rc = e->build_plan(std::vector<int>(example_shape, example_shape + ndim), input_dtype);
+  if (rc) {
+    e->contract.clear();
+    return rc;
   }
   e->compiled = true;
   return MU_OK;
+}
+
+int mu_engine_compile(mu_engine *e, const int *input_shape, int ndim, int input_dtype) {
+  return mu_engine_compile_contract(e, input_shape, ndim, nullptr, input_dtype);
+}
+
+// Make the plan of `shape` the active one: the active plan itself, a parked one, or a new one
+// (lowered, planned and captured now; the least recently used plan is dropped beyond
+// "plan_cache_entries"). The shape must satisfy the compile-time contract.
+int mu_engine_select_shape(mu_engine *e, const int *shape, int ndim) {
+  if (!e || !shape || ndim <= 0) return MU_ERR_INVALID;
+  if (!e->compiled) return e->fail(MU_ERR_INVALID, "Engine: run() called before compile()");
+  int idx = 0;
+  if (const char *why = contract_mismatch(e->contract, shape, ndim, &idx)) {
+    if (why[0] == 'r') return e->fail(MU_ERR_INVALID, "Engine run input shape mismatch: %s", why);
+    return e->fail(MU_ERR_INVALID, "Engine run input shape mismatch: %s %d", why, idx);
+  }
+  for (int i = 0; i < ndim; ++i)
+    if (shape[i] <= 0) return e->fail(MU_ERR_INVALID, "Engine: input extents must be positive");
+  const std::vector<int> want(shape, shape + ndim);
+  ++e->use_clock;
+  if (want == e->in_shape) return MU_OK;
+  const int in_dtype = e->in_dtype;
+  e->park_active();
+  for (size_t i = 0; i < e->parked.size(); ++i)
+    if (e->parked[i].in_shape == want) {
+      e->activate(i);
+      return MU_OK;
+    }
+  // room for one more: drop the least recently used plans
+  while (static_cast<int>(e->parked.size()) + 1 > std::max(1, e->plan_cache_entries)) {
+    size_t lru = 0;
+    for (size_t i = 1; i < e->parked.size(); ++i)
+      if (e->parked[i].last_used < e->parked[lru].last_used) lru = i;
+    e->free_plan(e->parked[lru]);
+    e->parked.erase(e->parked.begin() + static_cast<long>(lru));
+  }
+  int rc = e->build_plan(want, in_dtype);
+  if (rc) {
+    // fall back to a plan that works so that the engine stays usable
+    e->release_active_plan();
+    if (!e->parked.empty()) e->activate(e->parked.size() - 1);
+    else e->compiled = false;
+    return rc;
+  }
+  return MU_OK;
+}
+
+int mu_engine_plan_count(const mu_engine *e) {
+  return (e && e->compiled) ? static_cast<int>(e->parked.size()) + 1 : 0;
 }
 
 int mu_engine_output_shape(const mu_engine *e, int *shape, int *ndim, int *dtype) {

@@ -1,5 +1,6 @@
 // JSON reader and deploy-artifact (.npz) loader. Host code only.
 #include "engine_io.h"
+#include <exception>
 #include <algorithm>
 #include <cctype>
 #include <cstdint>
@@ -191,20 +192,21 @@ bool read_zip(const std::vector<unsigned char> &f, std::vector<Member> *out, std
   if (count == 0xFFFF || cd_size == 0xFFFFFFFFu || cd_off == 0xFFFFFFFFu) {
     if (eocd < 20 || rd32(&f[eocd - 20]) != 0x07064b50u) { *why = "zip64 locator missing"; return false; }
     const uint64_t z = rd64(&f[eocd - 20 + 8]);
-    if (z + 56 > n || rd32(&f[z]) != 0x06064b50u) { *why = "zip64 end-of-central-directory record missing"; return false; }
+    if (z > n || n - z < 56 || rd32(&f[z]) != 0x06064b50u) { *why = "zip64 end-of-central-directory record missing"; return false; }
     count = rd64(&f[z + 32]);
     cd_size = rd64(&f[z + 40]);
     cd_off = rd64(&f[z + 48]);
   }
-  if (cd_off + cd_size > n) { *why = "zip central directory out of bounds"; return false; }
+  // sizes come from the file (64-bit in zip64): compare by subtraction so that nothing wraps
+  if (cd_off > n || cd_size > n - cd_off) { *why = "zip central directory out of bounds"; return false; }
   size_t p = static_cast<size_t>(cd_off);
   for (uint64_t k = 0; k < count; ++k) {
-    if (p + 46 > n || rd32(&f[p]) != 0x02014b50u) { *why = "corrupt zip central directory"; return false; }
+    if (p > n || n - p < 46 || rd32(&f[p]) != 0x02014b50u) { *why = "corrupt zip central directory"; return false; }
     const uint16_t method = rd16(&f[p + 10]);
     uint64_t csize = rd32(&f[p + 20]), usize = rd32(&f[p + 24]);
     const uint16_t nlen = rd16(&f[p + 28]), xlen = rd16(&f[p + 30]), clen = rd16(&f[p + 32]);
     uint64_t lho = rd32(&f[p + 42]);
-    if (p + 46 + nlen + xlen + clen > n) { *why = "corrupt zip central directory entry"; return false; }
+    if (n - p - 46 < static_cast<size_t>(nlen) + xlen + clen) { *why = "corrupt zip central directory entry"; return false; }
     std::string name(reinterpret_cast<const char *>(&f[p + 46]), nlen);
     // zip64 extra field
     size_t x = p + 46 + nlen, xe = x + xlen;
@@ -220,10 +222,10 @@ bool read_zip(const std::vector<unsigned char> &f, std::vector<Member> *out, std
     }
     if (method != 0) { *why = "Compressed npz entries are not supported: " + name; return false; }
     if (csize != usize) { *why = "zip entry size mismatch: " + name; return false; }
-    if (lho + 30 > n || rd32(&f[lho]) != 0x04034b50u) { *why = "corrupt zip local header: " + name; return false; }
+    if (lho > n || n - lho < 30 || rd32(&f[lho]) != 0x04034b50u) { *why = "corrupt zip local header: " + name; return false; }
     const uint16_t ln = rd16(&f[lho + 26]), lx = rd16(&f[lho + 28]);
-    const uint64_t start = lho + 30 + ln + lx;
-    if (start + usize > n) { *why = "zip entry out of bounds: " + name; return false; }
+    const uint64_t start = lho + 30 + ln + lx; // lho <= n and three 16-bit terms: cannot wrap
+    if (start > n || usize > n - start) { *why = "zip entry out of bounds: " + name; return false; }
     out->push_back({name, &f[start], usize});
     p += 46 + nlen + xlen + clen;
   }
@@ -256,15 +258,19 @@ bool parse_npy(const Member &m, Npy *out, std::string *why) {
   };
   size_t p = find_val("descr");
   if (p == std::string::npos) { *why = "npy header lacks descr"; return false; }
-  size_t q1 = h.find('\'', p), q2 = h.find('\'', q1 + 1);
+  const size_t q1 = h.find('\'', p);
+  const size_t q2 = q1 == std::string::npos ? q1 : h.find('\'', q1 + 1);
   if (q1 == std::string::npos || q2 == std::string::npos) { *why = "npy header: bad descr"; return false; }
   out->descr = h.substr(q1 + 1, q2 - q1 - 1);
   p = find_val("fortran_order");
   if (p == std::string::npos) { *why = "npy header lacks fortran_order"; return false; }
-  out->fortran = h.compare(h.find_first_not_of(' ', p), 4, "True") == 0;
+  const size_t fv = h.find_first_not_of(' ', p);
+  if (fv == std::string::npos) { *why = "npy header: bad fortran_order"; return false; }
+  out->fortran = h.compare(fv, 4, "True") == 0;
   p = find_val("shape");
   if (p == std::string::npos) { *why = "npy header lacks shape"; return false; }
-  size_t a = h.find('(', p), b = h.find(')', a);
+  const size_t a = h.find('(', p);
+  const size_t b = a == std::string::npos ? a : h.find(')', a);
   if (a == std::string::npos || b == std::string::npos) { *why = "npy header: bad shape"; return false; }
   const std::string sh = h.substr(a + 1, b - a - 1);
   size_t i = 0;
@@ -323,8 +329,27 @@ const char *kForbidden[] = {"optim", "optimizer", "scheduler", "scaler", "master
 
 } // namespace
 
+static bool load_artifact_impl(const std::string &path, Json *config,
+                               std::map<std::string, NamedTensor> *tensors, std::string *why);
+
+// The callers are extern "C" entry points that promise never to throw: anything the parser
+// raises on a malformed file (std::out_of_range from a string search, std::bad_alloc from a
+// size field that asks for more memory than there is) becomes an ordinary load failure.
 bool load_artifact(const std::string &path, Json *config,
                    std::map<std::string, NamedTensor> *tensors, std::string *why) {
+  try {
+    return load_artifact_impl(path, config, tensors, why);
+  } catch (const std::exception &e) {
+    *why = std::string("Malformed serialized artifact: ") + e.what();
+  } catch (...) {
+    *why = "Malformed serialized artifact";
+  }
+  tensors->clear();
+  return false;
+}
+
+static bool load_artifact_impl(const std::string &path, Json *config,
+                               std::map<std::string, NamedTensor> *tensors, std::string *why) {
   FILE *fp = fopen(path.c_str(), "rb");
   if (!fp) { *why = "Unable to open serialized artifact: " + path; return false; }
   fseek(fp, 0, SEEK_END);
@@ -384,7 +409,16 @@ bool load_artifact(const std::string &path, Json *config,
     else { *why = "Unsupported npy dtype descriptor: " + a.descr; return false; }
     if (a.fortran) { *why = "Fortran-order npy arrays are not supported: " + name; return false; }
     t.shape = a.shape;
-    const uint64_t need = static_cast<uint64_t>(t.numel()) * (t.dtype == 1 ? 2 : 4);
+    // the extents come from the file: their product must not wrap before it is compared
+    uint64_t count = 1;
+    for (long long ext : a.shape) {
+      if (ext < 0 || (ext > 0 && count > (a.bytes + 1) / static_cast<uint64_t>(ext))) {
+        *why = "npy payload shorter than its shape: " + name;
+        return false;
+      }
+      count *= static_cast<uint64_t>(ext);
+    }
+    const uint64_t need = count * (t.dtype == 1 ? 2 : 4);
     if (need > a.bytes) { *why = "npy payload shorter than its shape: " + name; return false; }
     t.owned.assign(a.data, a.data + need);
     t.data = t.owned.data();

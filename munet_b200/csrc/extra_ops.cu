@@ -30,31 +30,70 @@ __device__ __forceinline__ void stf(__nv_bfloat16 *p, long long i, float v) { p[
   for (long long i = 1ll * blockIdx.x * blockDim.x + threadIdx.x, _s = 1ll * gridDim.x * blockDim.x; \
        i < (n); i += _s)
 
-template <typename T>
-__global__ void __launch_bounds__(256) unary_kernel(const T *x, T *y, long long n, int op, float slope) {
-  MU_GRID_STRIDE(i, n) {
-    const float v = ldf(x, i);
-    float r;
-    switch (op) {
-    case MU_UN_EXP: r = expf(v); break;
-    case MU_UN_LOG: r = logf(v); break;
-    case MU_UN_SQRT: r = __fsqrt_rn(v); break;
-    case MU_UN_RSQRT: r = __fdiv_rn(1.0f, __fsqrt_rn(v)); break;
-    case MU_UN_SIN: r = sinf(v); break;
-    case MU_UN_COS: r = cosf(v); break;
-    default: { // leaky relu, in the reference's own op order
-      const float p = v > 0.f ? v : 0.f;
-      r = __fadd_rn(p, __fmul_rn(__fsub_rn(v, p), slope));
-    }
-    }
-    stf(y, i, r);
+// 16 bytes of T: what one thread moves per load / store in the memory-bound kernels below
+// (4 floats or 8 bfloat16). The host picks the vector form when the pointers are 16-byte
+// aligned; a tail shorter than one pack is finished element by element by the same launch.
+template <typename T> struct alignas(16) Pack {
+  static constexpr int N = 16 / sizeof(T);
+  T v[N];
+};
+template <typename T> __device__ __forceinline__ float pack_get(const Pack<T> &p, int k);
+template <> __device__ __forceinline__ float pack_get<float>(const Pack<float> &p, int k) { return p.v[k]; }
+template <> __device__ __forceinline__ float pack_get<__nv_bfloat16>(const Pack<__nv_bfloat16> &p, int k) {
+  return __bfloat162float(p.v[k]);
+}
+__device__ __forceinline__ void pack_set(Pack<float> &p, int k, float v) { p.v[k] = v; }
+__device__ __forceinline__ void pack_set(Pack<__nv_bfloat16> &p, int k, float v) { p.v[k] = __float2bfloat16_rn(v); }
+static bool al16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+__device__ __forceinline__ float unary_math(float v, int op, float slope) {
+  switch (op) {
+  case MU_UN_EXP: return expf(v);
+  case MU_UN_LOG: return logf(v);
+  case MU_UN_SQRT: return __fsqrt_rn(v);
+  case MU_UN_RSQRT: return __fdiv_rn(1.0f, __fsqrt_rn(v));
+  case MU_UN_SIN: return sinf(v);
+  case MU_UN_COS: return cosf(v);
+  default: { // leaky relu, in the reference's own op order
+    const float p = v > 0.f ? v : 0.f;
+    return __fadd_rn(p, __fmul_rn(__fsub_rn(v, p), slope));
+  }
   }
 }
 
-template <typename T>
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) unary_kernel(const T *x, T *y, long long n, int op, float slope) {
+  long long done = 0;
+  if (VEC) {
+    constexpr int N = Pack<T>::N;
+    const long long n_vec = n / N;
+    MU_GRID_STRIDE(i, n_vec) {
+      const Pack<T> in = reinterpret_cast<const Pack<T> *>(x)[i];
+      Pack<T> out;
+#pragma unroll
+      for (int k = 0; k < N; ++k)
+        pack_set(out, k, unary_math(pack_get(in, k), op, slope));
+      reinterpret_cast<Pack<T> *>(y)[i] = out;
+    }
+    done = n_vec * N;
+  }
+  MU_GRID_STRIDE(j, n - done) stf(y, done + j, unary_math(ldf(x, done + j), op, slope));
+}
+
+// out[r, :] = row: with the row a whole number of packs, every thread stores 16 bytes and reads
+// its pack of the (cache-resident) row once per store.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) broadcast_row_kernel(const T *row, T *out, long long rows, int cols) {
-  const long long n = rows * cols;
-  MU_GRID_STRIDE(i, n) out[i] = row[i % cols];
+  if (VEC) {
+    constexpr int N = Pack<T>::N;
+    const int cv = cols / N;
+    const long long n_vec = rows * cv;
+    MU_GRID_STRIDE(i, n_vec)
+      reinterpret_cast<Pack<T> *>(out)[i] = reinterpret_cast<const Pack<T> *>(row)[i % cv];
+  } else {
+    const long long n = rows * cols;
+    MU_GRID_STRIDE(i, n) out[i] = row[i % cols];
+  }
 }
 
 struct ConcatArgs {
@@ -89,20 +128,32 @@ upsample2d_kernel(const T *x, T *y, long long BC, int iH, int iW, int scale) {
   }
 }
 
-template <typename T>
+// VEC: H*W is a whole number of packs, so the elements of a pack share their channel.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 batch_norm_eval_kernel(const T *x, const T *g, const T *b, const float *mean, const float *var, T *y,
                        long long n, int C, int spatial, float eps) {
-  MU_GRID_STRIDE(i, n) {
-    const int c = static_cast<int>((i / spatial) % C);
+  constexpr int N = VEC ? Pack<T>::N : 1;
+  MU_GRID_STRIDE(i, n / N) {
+    const int c = static_cast<int>((i * N / spatial) % C);
     const float inv_std = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var[c], eps)));
-    const float d = __fsub_rn(ldf(x, i), mean[c]);
-    stf(y, i, __fadd_rn(__fmul_rn(__fmul_rn(ldf(g, c), d), inv_std), ldf(b, c)));
+    const float gc = ldf(g, c), bc = ldf(b, c), mc = mean[c];
+    if (VEC) {
+      const Pack<T> in = reinterpret_cast<const Pack<T> *>(x)[i];
+      Pack<T> out;
+#pragma unroll
+      for (int k = 0; k < N; ++k)
+        pack_set(out, k, __fadd_rn(__fmul_rn(__fmul_rn(gc, __fsub_rn(pack_get(in, k), mc)), inv_std), bc));
+      reinterpret_cast<Pack<T> *>(y)[i] = out;
+    } else {
+      stf(y, i, __fadd_rn(__fmul_rn(__fmul_rn(gc, __fsub_rn(ldf(x, i), mc)), inv_std), bc));
+    }
   }
 }
 
 // One warp per row; accumulation in double like the reference's mean (cpu_backend.hpp:1124-1137).
-template <typename T>
+// VEC: rows are a whole number of 16-byte packs and 16-byte aligned, so a lane moves a pack at a time.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 rms_norm_kernel(const T *x, const T *w, T *y, long long rows, int cols, float eps) {
   const int lane = threadIdx.x & 31;
@@ -110,18 +161,39 @@ rms_norm_kernel(const T *x, const T *w, T *y, long long rows, int cols, float ep
   if (row >= rows)
     return;
   const T *xr = x + row * cols;
+  constexpr int N = VEC ? Pack<T>::N : 1;
   double s = 0.0;
-  for (int c = lane; c < cols; c += 32) {
-    const float v = ldf(xr, c);
-    s += static_cast<double>(__fmul_rn(v, v));
+  for (int c = lane * N; c < cols; c += 32 * N) {
+    if (VEC) {
+      const Pack<T> p = *reinterpret_cast<const Pack<T> *>(xr + c);
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const float v = pack_get(p, k);
+        s += static_cast<double>(__fmul_rn(v, v));
+      }
+    } else {
+      const float v = ldf(xr, c);
+      s += static_cast<double>(__fmul_rn(v, v));
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1)
     s += __shfl_xor_sync(0xffffffffu, s, o);
   const float m = static_cast<float>(s / static_cast<double>(cols));
   const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(m, eps)));
-  for (int c = lane; c < cols; c += 32)
-    stf(y + row * cols, c, __fmul_rn(__fmul_rn(ldf(xr, c), r), ldf(w, c)));
+  for (int c = lane * N; c < cols; c += 32 * N) {
+    if (VEC) {
+      const Pack<T> p = *reinterpret_cast<const Pack<T> *>(xr + c);
+      const Pack<T> g = *reinterpret_cast<const Pack<T> *>(w + c);
+      Pack<T> o;
+#pragma unroll
+      for (int k = 0; k < N; ++k)
+        pack_set(o, k, __fmul_rn(__fmul_rn(pack_get(p, k), r), pack_get(g, k)));
+      *reinterpret_cast<Pack<T> *>(y + row * cols + c) = o;
+    } else {
+      stf(y + row * cols, c, __fmul_rn(__fmul_rn(ldf(xr, c), r), ldf(w, c)));
+    }
+  }
 }
 
 template <typename T>
@@ -238,6 +310,22 @@ int mu_ctx_select_device(mu_ctx *ctx);
   if (cudaGetLastError() != cudaSuccess)                                                           \
     return mu_set_error(ctx, MU_ERR_CUDA, name ": launch failed");                                 \
   return MU_OK;
+// launch KERNEL<T, VEC> for the dtype, vector form when `vec_ok`; `work` = threads' worth of items
+#define MU_X_LAUNCH(KERNEL, vec_ok, work, ...)                                                     \
+  do {                                                                                             \
+    const unsigned nb = mu::blocks_for((work), sms);                                               \
+    if (dtype == MU_F32) {                                                                         \
+      typedef float T;                                                                             \
+      if (vec_ok) KERNEL<T, true><<<nb, 256, 0, st>>>(__VA_ARGS__);                                \
+      else KERNEL<T, false><<<nb, 256, 0, st>>>(__VA_ARGS__);                                      \
+    } else {                                                                                       \
+      typedef __nv_bfloat16 T;                                                                     \
+      if (vec_ok) KERNEL<T, true><<<nb, 256, 0, st>>>(__VA_ARGS__);                                \
+      else KERNEL<T, false><<<nb, 256, 0, st>>>(__VA_ARGS__);                                      \
+    }                                                                                              \
+  } while (0)
+#define TP(p) static_cast<const T *>(p)
+#define TPW(p) static_cast<T *>(p)
 #define F32P(p) static_cast<const float *>(p)
 #define BF16P(p) static_cast<const __nv_bfloat16 *>(p)
 
@@ -251,11 +339,9 @@ int mu_unary(mu_ctx *ctx, int op, const void *x, void *y, long long n, int dtype
     return MU_OK;
   if (!x || !y)
     return mu_set_error(ctx, MU_ERR_INVALID, "unary: null pointer");
-  if (dtype == MU_F32)
-    mu::unary_kernel<float><<<mu::blocks_for(n, sms), 256, 0, st>>>(F32P(x), static_cast<float *>(y), n, op, 0.f);
-  else
-    mu::unary_kernel<__nv_bfloat16><<<mu::blocks_for(n, sms), 256, 0, st>>>(
-        BF16P(x), static_cast<__nv_bfloat16 *>(y), n, op, 0.f);
+  const bool vec = mu::al16(x) && mu::al16(y) && n >= 64;
+  const int per = dtype == MU_F32 ? 4 : 8;
+  MU_X_LAUNCH(mu::unary_kernel, vec, vec ? n / per + per : n, TP(x), TPW(y), n, op, 0.f);
   MU_X_END("unary")
 }
 
@@ -267,14 +353,11 @@ int mu_leaky_relu(mu_ctx *ctx, const void *x, void *y, long long n, float slope,
     return MU_OK;
   if (!x || !y)
     return mu_set_error(ctx, MU_ERR_INVALID, "LeakyReLU: null pointer");
-  if (dtype == MU_F32)
-    mu::unary_kernel<float><<<mu::blocks_for(n, sms), 256, 0, st>>>(F32P(x), static_cast<float *>(y), n, -1, slope);
-  else {
-    // the slope tensor of the reference has the activation's dtype: round it the same way
-    const float sl = __bfloat162float(__float2bfloat16_rn(slope));
-    mu::unary_kernel<__nv_bfloat16><<<mu::blocks_for(n, sms), 256, 0, st>>>(
-        BF16P(x), static_cast<__nv_bfloat16 *>(y), n, -1, sl);
-  }
+  // the slope tensor of the reference has the activation's dtype: round it the same way
+  const float sl = dtype == MU_F32 ? slope : __bfloat162float(__float2bfloat16_rn(slope));
+  const bool vec = mu::al16(x) && mu::al16(y) && n >= 64;
+  const int per = dtype == MU_F32 ? 4 : 8;
+  MU_X_LAUNCH(mu::unary_kernel, vec, vec ? n / per + per : n, TP(x), TPW(y), n, -1, sl);
   MU_X_END("LeakyReLU")
 }
 
@@ -287,12 +370,9 @@ int mu_broadcast_row(mu_ctx *ctx, const void *row, void *out, long long rows, in
     return MU_OK;
   if (!row || !out)
     return mu_set_error(ctx, MU_ERR_INVALID, "broadcast_row: null pointer");
-  if (dtype == MU_F32)
-    mu::broadcast_row_kernel<float><<<mu::blocks_for(rows * cols, sms), 256, 0, st>>>(
-        F32P(row), static_cast<float *>(out), rows, cols);
-  else
-    mu::broadcast_row_kernel<__nv_bfloat16><<<mu::blocks_for(rows * cols, sms), 256, 0, st>>>(
-        BF16P(row), static_cast<__nv_bfloat16 *>(out), rows, cols);
+  const int per = dtype == MU_F32 ? 4 : 8;
+  const bool vec = mu::al16(row) && mu::al16(out) && cols % per == 0;
+  MU_X_LAUNCH(mu::broadcast_row_kernel, vec, vec ? rows * cols / per : rows * cols, TP(row), TPW(out), rows, cols);
   MU_X_END("broadcast_row")
 }
 
@@ -368,13 +448,10 @@ int mu_batch_norm_eval(mu_ctx *ctx, const void *x, const void *gamma, const void
     return MU_OK;
   if (!x || !gamma || !beta || !running_mean || !running_var || !y)
     return mu_set_error(ctx, MU_ERR_INVALID, "batch_norm: null pointer");
-  if (dtype == MU_F32)
-    mu::batch_norm_eval_kernel<float><<<mu::blocks_for(n, sms), 256, 0, st>>>(
-        F32P(x), F32P(gamma), F32P(beta), running_mean, running_var, static_cast<float *>(y), n, C, H * W, eps);
-  else
-    mu::batch_norm_eval_kernel<__nv_bfloat16><<<mu::blocks_for(n, sms), 256, 0, st>>>(
-        BF16P(x), BF16P(gamma), BF16P(beta), running_mean, running_var, static_cast<__nv_bfloat16 *>(y), n, C,
-        H * W, eps);
+  const int per = dtype == MU_F32 ? 4 : 8;
+  const bool vec = mu::al16(x) && mu::al16(y) && (H * W) % per == 0;
+  MU_X_LAUNCH(mu::batch_norm_eval_kernel, vec, vec ? n / per : n, TP(x), TP(gamma), TP(beta), running_mean,
+              running_var, TPW(y), n, C, H * W, eps);
   MU_X_END("batch_norm")
 }
 
@@ -388,11 +465,15 @@ int mu_rms_norm(mu_ctx *ctx, const void *x, const void *weight, void *y, long lo
   if (!x || !weight || !y)
     return mu_set_error(ctx, MU_ERR_INVALID, "RMSNorm: null pointer");
   const unsigned nb = static_cast<unsigned>((rows + 7) / 8);
-  if (dtype == MU_F32)
-    mu::rms_norm_kernel<float><<<nb, 256, 0, st>>>(F32P(x), F32P(weight), static_cast<float *>(y), rows, cols, eps);
-  else
-    mu::rms_norm_kernel<__nv_bfloat16><<<nb, 256, 0, st>>>(BF16P(x), BF16P(weight),
-                                                          static_cast<__nv_bfloat16 *>(y), rows, cols, eps);
+  const int per = dtype == MU_F32 ? 4 : 8;
+  const bool vec = mu::al16(x) && mu::al16(weight) && mu::al16(y) && cols % per == 0;
+  if (dtype == MU_F32) {
+    if (vec) mu::rms_norm_kernel<float, true><<<nb, 256, 0, st>>>(F32P(x), F32P(weight), static_cast<float *>(y), rows, cols, eps);
+    else mu::rms_norm_kernel<float, false><<<nb, 256, 0, st>>>(F32P(x), F32P(weight), static_cast<float *>(y), rows, cols, eps);
+  } else {
+    if (vec) mu::rms_norm_kernel<__nv_bfloat16, true><<<nb, 256, 0, st>>>(BF16P(x), BF16P(weight), static_cast<__nv_bfloat16 *>(y), rows, cols, eps);
+    else mu::rms_norm_kernel<__nv_bfloat16, false><<<nb, 256, 0, st>>>(BF16P(x), BF16P(weight), static_cast<__nv_bfloat16 *>(y), rows, cols, eps);
+  }
   MU_X_END("RMSNorm")
 }
 

@@ -11,8 +11,11 @@
 //   warp 1   allocates TMEM and issues tcgen05.mma (kind::f16, M=128, N=BN, K=16)
 //            from one thread; accumulators are double-buffered in TMEM so the
 //            epilogue of tile i overlaps the main loop of tile i+1.
-//   warps 2-9 epilogue (two per TMEM lane quarter, alternate 64-column groups): tcgen05.ld 32 lanes x 32 columns, scale / bias /
-//            activation / residual in registers, 128-bit stores.
+//   warps 2-9 epilogue (two per TMEM lane quarter, alternate 64-column groups): tcgen05.ld
+//            32 lanes x 32 columns, scale / bias / activation / residual on packed pairs in
+//            registers, result staged in a swizzled shared-memory box and written with one
+//            TMA store per 32 x 64 box (the residual arrives in the same box by TMA load).
+//            Outputs that no tensor map can address fall back to guarded 128-bit stores.
 // A is row-major [M,K] (K-major operand). B is either row-major [K,N] as MuNet
 // stores Linear weights (MN-major operand) or row-major [N,K] (K-major, "B
 // transposed"). All operands may be batched through a third tensor-map dim.
@@ -21,7 +24,6 @@
 #include "ptx.cuh"
 #include "epilogue_math.cuh"
 #include <cuda.h>
-#include <cstdlib>
 
 namespace mu {
 
@@ -647,14 +649,9 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
   const unsigned long long b_nb = s2.b_batched ? sh.batch : 1;
   const unsigned long long a_bs = s2.a_batched ? op.a_batch : 1ull * op.lda * sh.M;
   const int BN = sh.N > 128 ? 256 : (sh.N > 64 ? 128 : 64);
-  // CTA pairs (256 x 256 tiles) for the large, tile-rich problems; MU_GEMM_CTAS=1 in the
-  // environment keeps every problem on single CTAs (for A/B timing).
-  static const bool pairs_enabled = [] {
-    const char *e = getenv("MU_GEMM_CTAS");
-    return !(e && e[0] == '1');
-  }();
+  // CTA pairs (256 x 256 tiles) for the large, tile-rich problems
   const long long pair_tiles = 1ll * ((sh.M + 2 * BM - 1) / (2 * BM)) * ((sh.N + BN - 1) / BN) * sh.batch;
-  const bool pairs = pairs_enabled && BN == 256 && sh.M >= 1024 && num_sms >= 2 && pair_tiles >= num_sms / 2;
+  const bool pairs = BN == 256 && sh.M >= 1024 && num_sms >= 2 && pair_tiles >= num_sms / 2;
   const int CT = pairs ? 2 : 1;
   // B wider than a third of L2 is cut into panels of about 32 MB (see decode_tile)
   {

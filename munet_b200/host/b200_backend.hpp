@@ -9,12 +9,16 @@
 // Loss and OptimizerStep are not advertised, so MuNet's dispatcher keeps them on its CPU
 // path exactly as it does for any partial backend (src/core/op_dispatch.cpp:670-718).
 // Backward entry points and batch_norm(training=true) are training-only and throw.
+// memset and to_contiguous run on the device; all_reduce sums over NCCL when a communicator
+// is attached and otherwise joins the reference's in-process rendezvous;
+// get_last_kernel_time_us reports the event time of the last compute call.
 //
 // Errors follow the reference convention: std::runtime_error with the C ABI's
 // message (src/backend/cuda_backend.cu:15-31). copy() is complete on return
 // because callers read host memory right after it (src/tensor.cpp:342-351).
 #pragma once
 
+#include "core/all_reduce_runtime.hpp"
 #include "core/backend.hpp"
 #include "munet_b200.h"
 #include "storage.hpp"
@@ -96,11 +100,7 @@ public:
   }
   void deallocate(void *ptr) override { check(mu_free(ctx_, ptr)); }
   void memset(void *ptr, int value, size_t bytes) override {
-    if (bytes == 0) return;
-    // no memset in the C ABI: stage a host buffer (rare, start-up only)
-    std::string host(bytes, static_cast<char>(value));
-    check(mu_copy(ctx_, ptr, host.data(), bytes, MU_COPY_H2D, nullptr));
-    check(mu_check(ctx_, nullptr));
+    check(mu_memset(ctx_, ptr, value, bytes, nullptr));
   }
   void copy(const void *src, void *dst, size_t bytes, Device src_dev, Device dst_dev) override {
     const bool s_host = src_dev.type == DeviceType::CPU, d_host = dst_dev.type == DeviceType::CPU;
@@ -110,45 +110,63 @@ public:
     check(mu_check(ctx_, nullptr));
   }
   void synchronize() override { check(mu_synchronize(ctx_)); check(mu_check(ctx_, nullptr)); }
-  void all_reduce(Storage &, size_t) override { training_only("all_reduce"); }
-  double get_last_kernel_time_us() override { return 0.0; }
+  // Backend::all_reduce = elementwise sum over the participants. With a communicator attached
+  // (one process per GPU, set_comm) the sum runs in NCCL on the device, under a host deadline
+  // like the reference's (MUNET_ALLREDUCE_TIMEOUT_MS). Without one the participants are threads
+  // of this process, each with its own backend: that is the reference's own rendezvous
+  // (src/core/all_reduce_runtime.hpp:107-240), staged through the host exactly as its CUDA
+  // backend does (src/backend/cuda_backend.cu:963-966).
+  void all_reduce(Storage &buffer, size_t num_elements) override {
+    if (comm_) {
+      if (num_elements * dtype_size(buffer.dtype()) > buffer.size_bytes())
+        throw std::runtime_error("all_reduce: num_elements exceeds storage size");
+      check(mu_all_reduce_sum(ctx_, comm_, buffer.data(), static_cast<long long>(num_elements),
+                              code(buffer), nullptr));
+      check(mu_comm_wait(ctx_, comm_, nullptr, 0));
+      return;
+    }
+    detail::all_reduce_via_host(buffer, num_elements, *this, buffer.device(), true);
+  }
+  // The communicator stays owned by the caller and must outlive this backend's use of it.
+  void set_comm(mu_comm *comm) { comm_ = comm; }
+  double get_last_kernel_time_us() override { return mu_timer_last_us(ctx_); }
+  bool reports_gpu_kernel_time() const override { return true; }
   void to_contiguous(const Storage &src, Storage &dst, const Shape &shape, const Strides &strides,
                      size_t offset) override {
-    // strided gather on the host side of the boundary (head split/merge permutes);
-    // the executor never needs it because its GEMM epilogues write the final layout
-    const size_t es = dtype_size(src.dtype());
-    std::string in(src.size_bytes(), 0), out(numel(shape) * es, 0);
-    check(mu_copy(ctx_, in.data(), src.data(), in.size(), MU_COPY_D2H, nullptr));
-    check(mu_check(ctx_, nullptr));
-    const size_t total = numel(shape);
-    for (size_t linear = 0; linear < total; ++linear) {
-      size_t rem = linear, off = offset;
-      for (int d = static_cast<int>(shape.size()) - 1; d >= 0; --d) {
-        off += (rem % shape[d]) * strides[d];
-        rem /= shape[d];
-      }
-      std::memcpy(&out[linear * es], &in[off * es], es);
-    }
-    check(mu_copy(ctx_, dst.data(), out.data(), out.size(), MU_COPY_H2D, nullptr));
-    check(mu_check(ctx_, nullptr));
+    // strided gather on the device, any element size (head split / merge permutes of the
+    // reference's own MultiHeadAttention go through here)
+    if (shape.size() > 6 || shape.size() != strides.size())
+      throw std::runtime_error("B200Backend: to_contiguous supports at most 6 dimensions");
+    int sh[6];
+    long long st[6];
+    for (size_t d = 0; d < shape.size(); ++d) sh[d] = shape[d], st[d] = strides[d];
+    timed([&] {
+      check(mu_to_contiguous(ctx_, src.data(), dst.data(), static_cast<int>(shape.size()), sh, st,
+                             static_cast<long long>(offset), static_cast<int>(dtype_size(src.dtype())),
+                             nullptr));
+    });
   }
 
   // ---- BLAS --------------------------------------------------------------------
   void matmul(const Storage &a, const Storage &b, Storage &out, int M, int K, int N, bool transA,
               bool transB) override {
-    check(mu_matmul(ctx_, a.data(), b.data(), out.data(), M, K, N, transA, transB, code(a), nullptr));
+    timed([&] {
+      check(mu_matmul(ctx_, a.data(), b.data(), out.data(), M, K, N, transA, transB, code(a), nullptr));
+    });
   }
   void batched_matmul(const Storage &a, const Storage &b, Storage &out, int batch, int M, int K,
                       int N, bool transA, bool transB, int64_t sa, int64_t sb, int64_t so) override {
-    check(mu_batched_matmul(ctx_, a.data(), b.data(), out.data(), batch, M, K, N, transA, transB, sa,
-                            sb, so, code(a), nullptr));
+    timed([&] {
+      check(mu_batched_matmul(ctx_, a.data(), b.data(), out.data(), batch, M, K, N, transA, transB, sa,
+                              sb, so, code(a), nullptr));
+    });
   }
 
   // ---- elementwise ---------------------------------------------------------------
   void relu(const Storage &in, Storage &out, size_t n) override { unary(in, out, n, MU_ACT_RELU); }
   void sigmoid(const Storage &in, Storage &out, size_t n) override { unary(in, out, n, MU_ACT_SIGMOID); }
   void softmax(const Storage &in, Storage &out, int rows, int cols) override {
-    check(mu_softmax(ctx_, in.data(), out.data(), rows, cols, code(in), nullptr));
+    timed([&] { check(mu_softmax(ctx_, in.data(), out.data(), rows, cols, code(in), nullptr)); });
   }
   void add(const Storage &a, const Storage &b, Storage &o, const BroadcastInfo &i) override { binary(MU_OP_ADD, a, b, o, i); }
   void sub(const Storage &a, const Storage &b, Storage &o, const BroadcastInfo &i) override { binary(MU_OP_SUB, a, b, o, i); }
@@ -171,8 +189,10 @@ public:
   void conv2d(const Storage &in, const Storage &weight, const Storage *bias, Storage &out, int B,
               int iC, int iH, int iW, int oC, int kH, int kW, int s, int p) override {
     if (kH != kW) throw std::runtime_error("B200Backend: conv2d needs a square kernel");
-    check(mu_conv2d(ctx_, in.data(), weight.data(), bias ? bias->data() : nullptr, out.data(), B, iC,
-                    iH, iW, oC, kH, s, p, 0, 0, code(in), nullptr));
+    timed([&] {
+      check(mu_conv2d(ctx_, in.data(), weight.data(), bias ? bias->data() : nullptr, out.data(), B, iC,
+                      iH, iW, oC, kH, s, p, 0, 0, code(in), nullptr));
+    });
   }
   void max_pool2d(const Storage &in, Storage &out, int B, int C, int iH, int iW, int k, int s,
                   int p) override {
@@ -244,17 +264,27 @@ public:
 
 private:
   mu_ctx *ctx_ = nullptr;
+  mu_comm *comm_ = nullptr;
+  // every compute call sits between the context's event pair, like the reference's CUDA backend
+  // brackets each kernel (src/backend/cuda_backend.cu:952-961)
+  template <typename Fn> void timed(Fn &&fn) {
+    mu_timer_begin(ctx_, nullptr);
+    fn();
+    mu_timer_end(ctx_, nullptr);
+  }
   unsigned long long fill_calls_ = 41; // seeds successive fills differently, reproducibly per process
   void math(int op, const Storage &in, Storage &out, size_t n) {
-    check(mu_unary(ctx_, op, in.data(), out.data(), static_cast<long long>(n), code(in), nullptr));
+    timed([&] { check(mu_unary(ctx_, op, in.data(), out.data(), static_cast<long long>(n), code(in), nullptr)); });
   }
   static int code(const Storage &s) { return static_cast<int>(s.dtype()); } // same enum order
   void check(int rc) const {
     if (rc != MU_OK) throw std::runtime_error(std::string("B200Backend: ") + mu_last_error(ctx_));
   }
   void unary(const Storage &in, Storage &out, size_t n, int act) {
-    check(mu_eltwise(ctx_, in.data(), nullptr, nullptr, out.data(), static_cast<long long>(n), 1, act,
-                     code(in), nullptr));
+    timed([&] {
+      check(mu_eltwise(ctx_, in.data(), nullptr, nullptr, out.data(), static_cast<long long>(n), 1, act,
+                       code(in), nullptr));
+    });
   }
   void binary(int op, const Storage &a, const Storage &b, Storage &out, const BroadcastInfo &info) {
     const int nd = static_cast<int>(info.out_shape.size());
@@ -266,8 +296,10 @@ private:
       sa[d] = info.strides_a[d];
       sb[d] = info.strides_b[d];
     }
-    check(mu_binary_broadcast(ctx_, op, a.data(), b.data(), out.data(), nd, shape, sa, sb, code(a),
-                              nullptr));
+    timed([&] {
+      check(mu_binary_broadcast(ctx_, op, a.data(), b.data(), out.data(), nd, shape, sa, sb, code(a),
+                                nullptr));
+    });
   }
   [[noreturn]] static void training_only(const char *op) {
     throw std::runtime_error(std::string("B200Backend: '") + op + "' is a training-only entry point");

@@ -193,8 +193,49 @@ class Engine:
                         "prepared_input_cache_hits": 0, "prepared_input_cache_misses": 0,
                         "prepared_input_cache_evictions": 0}
         self._observer = None
+        # EngineConfig flags of the reference (src/inference.hpp:30-41)
+        self._strict_shape_check = True
+        self._lean_mode = False
+        self._capture_profiler_memory = False
+        self._contract = None  # expected input shape, -1 = any extent
 
     # -- reference-style configuration and bookkeeping ------------------------------
+    def set_strict_shape_check(self, enabled: bool):
+        """Engine::set_strict_shape_check (src/inference.hpp:317-319). With the check off the
+        reference forwards whatever arrives; here an input of another shape (same rank) gets a
+        plan of its own on first sight."""
+        self._strict_shape_check = bool(enabled)
+
+    def set_lean_mode(self, enabled: bool):
+        """Engine::set_lean_mode (src/inference.hpp:330-335): drop the diagnostic bookkeeping —
+        memory capture is switched off with it, and the load event no longer reports parameter
+        counts."""
+        self._lean_mode = bool(enabled)
+        if enabled:
+            self._capture_profiler_memory = False
+
+    def set_capture_profiler_memory(self, enabled: bool):
+        """Engine::set_capture_profiler_memory (src/inference.hpp:323-328): record the device
+        memory behind the engine after load, compile and every run; leaves lean mode."""
+        self._capture_profiler_memory = bool(enabled)
+        if enabled:
+            self._lean_mode = False
+
+    @property
+    def lean_mode(self) -> bool:
+        return self._lean_mode
+
+    @property
+    def capture_profiler_memory(self) -> bool:
+        return self._capture_profiler_memory
+
+    def _refresh_memory_stats(self):
+        if self._capture_profiler_memory and self.input_shape is not None:
+            st = self.stats()
+            self._estats["current_memory_bytes"] = st["arena_bytes"] + st["weight_bytes"]
+            self._estats["peak_memory_bytes"] = max(self._estats.get("peak_memory_bytes", 0),
+                                                    self._estats["current_memory_bytes"])
+
     def set_observer(self, observer):
         """``observer(event: dict)`` is called for load/compile/run completion and errors
         (EngineEvent, src/inference.hpp:70-92)."""
@@ -235,10 +276,11 @@ class Engine:
         self._estats["prepared_input_cache_misses"] += 1
         import torch
         t = x if hasattr(x, "data_ptr") else torch.from_numpy(x)
-        if tuple(t.shape) != self.input_shape:
-            raise MuNetError(1, f"Engine: input shape {tuple(t.shape)} does not match compiled "
-                                f"contract {self.input_shape}")
-        dev = t.contiguous().to(torch.device("cuda", self.ctx.device))
+        self._check_contract(tuple(t.shape))
+        # the same conversion the uncached path applies (np.ascontiguousarray(x, dtype=...)):
+        # an int64 id tensor or a float64 array must not reach the engine as raw bytes
+        t = t.contiguous().to(_torch_dtype(self.input_dtype))
+        dev = t.to(torch.device("cuda", self.ctx.device))
         self._estats["prepared_input_cache_evictions"] += self._cache.store(
             key[0], key[1], dev, dev.numel() * dev.element_size())
         return dev
@@ -254,6 +296,50 @@ class Engine:
     def _rc(self, rc):
         if rc:
             raise MuNetError(rc, self._lib.mu_engine_last_error(self._h).decode())
+
+    def _check_contract(self, shape):
+        """The compile-time contract (exact extents or -1 wildcards) against ``shape``, with the
+        reference's reasons (ShapeContract::mismatch_reason, src/inference.hpp:162-176)."""
+        c = self._contract if self._strict_shape_check else (-1,) * len(self._contract)
+        reason = None
+        if len(shape) != len(c):
+            reason = "rank mismatch"
+        else:
+            for i, (want, got) in enumerate(zip(c, shape)):
+                if want != -1 and want != got:
+                    reason = f"dim mismatch at index {i}"
+                    break
+        if reason:
+            self._emit("error", message="run failed: shape contract")
+            raise MuNetError(1, f"Engine run input shape mismatch: {reason} (input shape "
+                                f"{tuple(shape)} does not match compiled contract {tuple(self._contract)})")
+
+    def _select(self, shape):
+        """Make the plan of ``shape`` the active one (built on first sight)."""
+        if tuple(shape) == self.input_shape:
+            return
+        if not self._strict_shape_check and any(w != -1 and w != g for w, g in zip(self._contract, shape)):
+            # outside the compiled contract but allowed: widen the engine's contract to the rank
+            n = len(shape)
+            self._rc(self._lib.mu_engine_compile_contract(
+                self._h, (C.c_int * n)(*shape), n, (C.c_int * n)(*([-1] * n)), self.input_dtype))
+            self._contract = (-1,) * n
+        else:
+            self._rc(self._lib.mu_engine_select_shape(self._h, (C.c_int * len(shape))(*shape), len(shape)))
+        self.input_shape = tuple(shape)
+        self._read_output_shape()
+
+    def _read_output_shape(self):
+        out = (C.c_int * 8)()
+        nd, odt = C.c_int(), C.c_int()
+        self._rc(self._lib.mu_engine_output_shape(self._h, out, C.byref(nd), C.byref(odt)))
+        self.output_shape = tuple(out[i] for i in range(nd.value))
+        self.output_dtype = odt.value
+
+    @property
+    def plan_count(self) -> int:
+        """Plans (one per concrete input shape met so far) the engine holds."""
+        return int(self._lib.mu_engine_plan_count(self._h))
 
     def _opt(self, name, value):
         self._rc(self._lib.mu_engine_set_option(self._h, name.encode(), int(value)))
@@ -282,7 +368,7 @@ class Engine:
                 self._emit("error", message=f"load failed: {e}")
                 raise
             self._estats["load_to_device_ms"] = (time.perf_counter() - t0) * 1e3
-            self._emit("load_completed", self._estats["load_to_device_ms"])
+            self._emit("load_completed", self._estats["load_to_device_ms"], self._load_message(None))
             return self
         names = list(tensors)
         n = len(names)
@@ -315,30 +401,54 @@ class Engine:
             (C.c_int * n)(*dts), (C.c_int * n)(*nds), (C.c_longlong * max(len(shp), 1))(*shp),
             int(on_device), self.compute_dtype))
         self._estats["load_to_device_ms"] = (time.perf_counter() - t0) * 1e3
-        self._emit("load_completed", self._estats["load_to_device_ms"])
+        self._emit("load_completed", self._estats["load_to_device_ms"], self._load_message(n))
         return self
 
+    def _load_message(self, n_tensors):
+        """The reference's load event text (src/inference.hpp:426-438); the tensor census is part
+        of the diagnostics that lean mode leaves out."""
+        msg = f"Module loaded on cuda:{self.ctx.device}; gradients will remain disabled during compile/run"
+        if not self._lean_mode and n_tensors is not None:
+            msg += f" ({n_tensors} parameter/buffer tensor(s) staged)"
+        return msg
+
     # -- compile ---------------------------------------------------------------
-    def compile(self, input_shape, input_dtype: int | None = None):
+    def compile(self, input_shape, input_dtype: int | None = None, expected_input_shape=None,
+                expected_output_shape=None):
+        """Engine::compile (src/inference.hpp:446-539). ``expected_input_shape`` may hold -1 for
+        extents that vary between runs (tests/test_inference.cpp:402-438); every concrete shape
+        met later gets its own plan, the weights are shared. ``expected_output_shape`` is checked
+        against the example's output like the reference does."""
         import time
         t0 = time.perf_counter()
         shape = tuple(int(s) for s in input_shape)
         dt = self.compute_dtype if input_dtype is None else input_dtype
+        n = len(shape)
+        exp = None if expected_input_shape is None else tuple(int(s) for s in expected_input_shape)
         try:
-            self._rc(self._lib.mu_engine_compile(self._h, (C.c_int * len(shape))(*shape), len(shape), dt))
+            if exp is not None and len(exp) != n:
+                raise MuNetError(1, "Engine compile input shape mismatch: rank mismatch")
+            self._rc(self._lib.mu_engine_compile_contract(
+                self._h, (C.c_int * n)(*shape), n, None if exp is None else (C.c_int * n)(*exp), dt))
         except MuNetError as e:
             self._emit("error", message=f"compile failed: {e}")
             raise
         self._keep = None  # weights now live in the engine's slab
         self.input_shape, self.input_dtype = shape, dt
-        out = (C.c_int * 8)()
-        nd, odt = C.c_int(), C.c_int()
-        self._rc(self._lib.mu_engine_output_shape(self._h, out, C.byref(nd), C.byref(odt)))
-        self.output_shape = tuple(out[i] for i in range(nd.value))
-        self.output_dtype = odt.value
+        self._contract = exp if exp is not None else shape
+        self._read_output_shape()
+        if expected_output_shape is not None:
+            eo = tuple(int(s) for s in expected_output_shape)
+            bad = len(eo) != len(self.output_shape) or any(
+                w != -1 and w != g for w, g in zip(eo, self.output_shape))
+            if bad:
+                self._emit("error", message="compile failed: output shape contract")
+                raise MuNetError(1, f"Engine compile output shape mismatch: expected {eo}, "
+                                    f"got {self.output_shape}")
         self._cache.reset()
         self._estats.update(compile_ms=(time.perf_counter() - t0) * 1e3,
                             compiled_input_shape=list(shape), compiled_output_shape=list(self.output_shape))
+        self._refresh_memory_stats()
         self._emit("compile_completed", self._estats["compile_ms"])
         return self
 
@@ -358,10 +468,8 @@ class Engine:
         t0 = time.perf_counter()
         self._estats["last_prepare_input_ms"] = 0.0
         host_in = isinstance(x, np.ndarray) or (hasattr(x, "is_cuda") and not x.is_cuda)
-        if tuple(x.shape) != self.input_shape:
-            self._emit("error", message="run failed: shape contract")
-            raise MuNetError(1, f"Engine: input shape {tuple(x.shape)} does not match compiled "
-                                f"contract {self.input_shape}")
+        self._check_contract(tuple(x.shape))
+        self._select(tuple(x.shape))
         if host_in and len(self._cache) and _input_identity(x) is not None \
                 and self._cache.find(*_input_identity(x)) is not None:
             dev = self._prepared(x)  # prepared earlier and unchanged since: no host copy
@@ -386,6 +494,13 @@ class Engine:
                                              _stream(stream)))
             self._ran(t0)
             return (out, am) if self.argmax else out
+        # a device tensor is consumed as raw bytes: its dtype must be the compiled input dtype
+        if _torch_code(x.dtype) != self.input_dtype:
+            self._emit("error", message="run failed: input dtype")
+            raise MuNetError(1, f"Engine: CUDA input has dtype {x.dtype}, the engine was compiled for "
+                                f"dtype code {self.input_dtype}; convert it before run()")
+        if not x.is_contiguous():
+            x = x.contiguous()
         self._rc(self._lib.mu_engine_run(self._h, x.data_ptr(), 0,
                                          None if out is None else out.data_ptr(), 0, None, 0,
                                          _stream(stream)))
@@ -398,6 +513,7 @@ class Engine:
         self._estats["runs"] += 1
         self._estats["last_run_ms"] = ms
         self._estats["last_forward_ms"] = ms - self._estats["last_prepare_input_ms"]
+        self._refresh_memory_stats()
         self._emit("run_completed", ms)
 
     OP_KINDS = ["embed", "layer_norm", "linear", "qkv_linear", "attention", "eltwise", "argmax",
@@ -440,4 +556,9 @@ class Engine:
 
 def _torch_code(dt) -> int:
     import torch
-    return {torch.float32: F32, torch.bfloat16: BF16, torch.int32: I32, torch.float16: 1}[dt]
+    return {torch.float32: F32, torch.bfloat16: BF16, torch.int32: I32, torch.float16: 1}.get(dt, -1)
+
+
+def _torch_dtype(code: int):
+    import torch
+    return {F32: torch.float32, BF16: torch.bfloat16, I32: torch.int32, 1: torch.float16}[code]

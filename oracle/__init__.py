@@ -29,16 +29,22 @@ ACT = {"none": 0, "relu": 1, "gelu": 2, "sigmoid": 3, "tanh": 4}
 K_LITERAL, K_MATH = 0, 1
 
 
+def reference_checkout() -> str | None:
+    """Where the reference's sources are: $MUNET_REF, else a directory named ``reference`` beside
+    this repository; None when neither exists (the prebuilt oracle/_ref is then used as it is)."""
+    cand = os.environ.get("MUNET_REF") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "src")) else None
+
+
 def build(ref: bool = True) -> None:
     """Compile the checkers (C port always; the reference core when its checkout exists)."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "port"])
-    if ref and os.path.isdir(os.environ.get("MUNET_REF", "/root/reference")):
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "-j8",
-                               "REF=" + os.environ.get("MUNET_REF", "/root/reference")])
+    src = reference_checkout() if ref else None
+    if src:
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "-j8", "REF=" + src])
         lib_dir = os.path.join(_HERE, "..", "munet_b200", "lib", "libmunet_b200.so")
         if os.path.exists(lib_dir):  # drop-in proof: reference core + our Backend adapter
-            subprocess.check_call(["make", "-s", "-C", _HERE, "refb200", "-j8",
-                                   "REF=" + os.environ.get("MUNET_REF", "/root/reference")])
+            subprocess.check_call(["make", "-s", "-C", _HERE, "refb200", "-j8", "REF=" + src])
 
 
 def to_bf16(a) -> np.ndarray:
@@ -275,6 +281,12 @@ class Port(_Lib):
         self._call("attention_core", _p(q), _p(k), _p(v), _p(y), BH, T, D, int(causal), dtype, kmode)
         return y
 
+    def set_variant(self, flags: int):
+        """Diagnostic arithmetic variants of the C restatement (0 = the pinned reference
+        behaviour; 1 = float accumulation in contractions; 2 = unnormalised-P rounding in
+        attention). Only drift measurements use non-zero values; parity tests never do."""
+        self.lib.orc_set_variant(int(flags))
+
     def argmax(self, x, dtype):
         x = _c(x, dtype)
         cols = x.shape[-1]
@@ -287,6 +299,13 @@ class Port(_Lib):
 class Ref(_Lib):
     def __init__(self):
         super().__init__(REF_PATH, "ref_")
+
+    def convert(self, x, from_dtype, to_dtype):
+        """Tensor::to(DataType) of the reference on a flat host array."""
+        x = _c(x, from_dtype)
+        y = np.empty(x.shape, np_dtype(to_dtype))
+        self._call("convert", _p(x), _p(y), C.c_long(x.size), from_dtype, to_dtype)
+        return y
 
     def hardware_concurrency(self) -> int:
         return int(self.lib.ref_hardware_concurrency())
@@ -366,3 +385,26 @@ class RefB200:
             raise RuntimeError(self.lib.refb200_last_error().decode())
         shp = tuple(oshape[i] for i in range(ond.value))
         return out[: int(np.prod(shp))].reshape(shp).copy()
+
+    def mha_forward(self, x, params, H, causal, dtype, device_index=0):
+        """nn::MultiHeadAttention of the reference on the B200 backend; returns (y, last kernel us)."""
+        x = _c(x, dtype)
+        B, T, E = x.shape
+        ps = [_c(p, dtype) for p in params]
+        arr = (C.c_void_p * 8)(*[p.ctypes.data for p in ps])
+        y = np.empty_like(x)
+        us = C.c_double(0.0)
+        rc = self.lib.refb200_mha_forward(_p(x), arr, _p(y), B, T, E, H, int(causal), dtype, device_index,
+                                          C.byref(us))
+        if rc != 0:
+            raise RuntimeError(self.lib.refb200_last_error().decode())
+        return y, us.value
+
+    def all_reduce_threads(self, bufs, dtype, device_index=0):
+        """Backend::all_reduce from len(bufs) threads of this process; returns what each one holds."""
+        bs = [np.array(_c(b, dtype)) for b in bufs]
+        arr = (C.c_void_p * len(bs))(*[b.ctypes.data for b in bs])
+        rc = self.lib.refb200_all_reduce_threads(arr, len(bs), C.c_long(bs[0].size), dtype, device_index)
+        if rc != 0:
+            raise RuntimeError(self.lib.refb200_last_error().decode())
+        return bs

@@ -50,6 +50,20 @@ static inline float bf2f(uint16_t v) {
 static inline uint16_t d2bf(double v) { return f2bf((float)v); }
 static inline double bf2d(uint16_t v) { return (double)bf2f(v); }
 
+/* ---- diagnostic variants (NOT the parity reference) ----
+ * orc_set_variant(0), the default, is the pinned restatement of the reference. The bits below
+ * swap one piece of its bfloat16 arithmetic for what a tensor-core kernel does instead, so that
+ * how far two valid evaluation orders of the same bf16 pipeline drift apart can be measured on
+ * the CPU, without any kernel in the loop:
+ *   1  contractions (matmul, Q.K', P.V) accumulate in float instead of double
+ *   2  attention rounds the UNNORMALISED probabilities exp(s - max) to bf16 before P.V and
+ *      divides the float result by the float row sum (online-softmax order) instead of
+ *      rounding the normalised probabilities (the reference's order)
+ * Tests that compare a kernel with the checker always run variant 0. */
+static int g_variant = 0;
+void orc_set_variant(int flags) { g_variant = flags; }
+int orc_get_variant(void) { return g_variant; }
+
 uint16_t orc_float_to_bf16(float v) { return f2bf(v); }
 float orc_bf16_to_float(uint16_t v) { return bf2f(v); }
 
@@ -72,8 +86,34 @@ static void matmul_f32(const float *a, const float *b, float *c, int M, int K,
   }
 }
 
+static void matmul_bf16_facc(const uint16_t *a, const uint16_t *b, uint16_t *c,
+                             int M, int K, int N) {
+#pragma omp parallel
+  {
+    float *acc = (float *)malloc(sizeof(float) * (size_t)N);
+#pragma omp for schedule(static)
+    for (int m = 0; m < M; ++m) {
+      for (int n = 0; n < N; ++n)
+        acc[n] = 0.0f;
+      for (int k = 0; k < K; ++k) {
+        const float av = bf2f(a[(size_t)m * K + k]);
+        const uint16_t *br = b + (size_t)k * N;
+        for (int n = 0; n < N; ++n)
+          acc[n] = acc[n] + av * bf2f(br[n]);
+      }
+      for (int n = 0; n < N; ++n)
+        c[(size_t)m * N + n] = f2bf(acc[n]);
+    }
+    free(acc);
+  }
+}
+
 static void matmul_bf16(const uint16_t *a, const uint16_t *b, uint16_t *c,
                         int M, int K, int N) {
+  if (g_variant & 1) {
+    matmul_bf16_facc(a, b, c, M, K, N);
+    return;
+  }
   double *bd = (double *)malloc(sizeof(double) * (size_t)K * N);
   for (size_t i = 0; i < (size_t)K * N; ++i)
     bd[i] = bf2d(b[i]);
@@ -397,6 +437,15 @@ int orc_attention_core(const void *q, const void *k, const void *v, void *ctx,
                                              : K[(size_t)j * D + d];
             s += bf2d(Q[(size_t)i * D + d]) * bf2d(kv);
           }
+          if (g_variant & 1) { /* diagnostic: float accumulation of Q.K' */
+            float sfl = 0.0f;
+            for (int d = 0; d < D; ++d) {
+              uint16_t kv = kmode == K_LITERAL ? K[(size_t)d * N + j]
+                                               : K[(size_t)j * D + d];
+              sfl += bf2f(Q[(size_t)i * D + d]) * bf2f(kv);
+            }
+            s = (double)sfl;
+          }
           uint16_t sb = mul_bf16(d2bf(s), scale_b);
           p[jj] = bf2d(sb);
           if (jj == 0 || p[jj] > mx)
@@ -405,6 +454,27 @@ int orc_attention_core(const void *q, const void *k, const void *v, void *ctx,
         double sum = 0.0;
         for (int jj = 0; jj < cnt; ++jj)
           sum += exp(p[jj] - mx);
+        uint16_t *out = (uint16_t *)ctx + (size_t)i * D;
+        if (g_variant & 2) { /* diagnostic: unnormalised P rounded, divide at the end */
+          float lsum = 0.0f;
+          for (int jj = 0; jj < cnt; ++jj) {
+            const float e = (float)exp(p[jj] - mx);
+            lsum += e;
+            p[jj] = bf2d(f2bf(e));
+          }
+          for (int d = 0; d < D; ++d)
+            acc[d] = 0.0;
+          for (int jj = 0; jj < cnt; ++jj) {
+            const double pv = p[jj];
+            const uint16_t *vr = V + (size_t)(j0 + jj) * D;
+            for (int d = 0; d < D; ++d)
+              acc[d] = (g_variant & 1) ? (double)((float)acc[d] + (float)pv * bf2f(vr[d]))
+                                       : acc[d] + pv * bf2d(vr[d]);
+          }
+          for (int d = 0; d < D; ++d)
+            out[d] = f2bf((float)acc[d] * (1.0f / lsum));
+          continue;
+        }
         for (int jj = 0; jj < cnt; ++jj)
           p[jj] = bf2d(d2bf(exp(p[jj] - mx) / sum));
         for (int d = 0; d < D; ++d)
@@ -413,9 +483,9 @@ int orc_attention_core(const void *q, const void *k, const void *v, void *ctx,
           const double pv = p[jj];
           const uint16_t *vr = V + (size_t)(j0 + jj) * D;
           for (int d = 0; d < D; ++d)
-            acc[d] += pv * bf2d(vr[d]);
+            acc[d] = (g_variant & 1) ? (double)((float)acc[d] + (float)pv * bf2f(vr[d]))
+                                     : acc[d] + pv * bf2d(vr[d]);
         }
-        uint16_t *out = (uint16_t *)ctx + (size_t)i * D;
         for (int d = 0; d < D; ++d)
           out[d] = d2bf(acc[d]);
       }

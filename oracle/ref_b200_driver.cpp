@@ -13,8 +13,11 @@
 #include "tensor.hpp"
 #include "backend/plugin_loader.hpp"
 
+#include <cstdlib>
 #include <cstring>
 #include <string>
+#include <thread>
+#include <vector>
 
 using namespace munet;
 
@@ -91,6 +94,77 @@ int refb200_engine_run_npz(const char *path, int device_index, int dtype, const 
     for (int i = 0; i < *out_ndim && i < 8; ++i) out_shape[i] = yf.shape()[i];
     Tensor c = yf.is_contiguous() ? yf : yf.contiguous();
     std::memcpy(out, c.data(), c.bytes());
+  });
+}
+
+// The reference's own nn::MultiHeadAttention module (src/nn/attention.hpp:34-103) on
+// DeviceType::CUDA: its three projections, the head split / merge permutes (to_contiguous),
+// the stride-ignoring score matmul, scale, softmax and P.V all reach the B200 kernels through
+// the adapter; the mask build and masked_fill take MuNet's CPU path, as on its own CUDA backend.
+// params: q.w q.b k.w k.b v.w v.b o.w o.b in `dtype`; x and y are host buffers in `dtype`.
+// *kernel_us receives Backend::get_last_kernel_time_us() after the forward.
+int refb200_mha_forward(const void *x, const void *const *params, void *y, int B, int T, int E,
+                        int H, int causal, int dtype, int device_index, double *kernel_us) {
+  return guarded([&] {
+    const Device cpu{DeviceType::CPU, 0}, dev{DeviceType::CUDA, device_index};
+    const DataType dt = static_cast<DataType>(dtype);
+    TensorOptions opt(cpu, dt, false);
+    auto mha = std::make_shared<nn::MultiHeadAttention>(E, H, causal != 0, opt);
+    auto named = mha->named_parameters("");
+    const char *names[8] = {"q_proj.weight", "q_proj.bias", "k_proj.weight", "k_proj.bias",
+                            "v_proj.weight", "v_proj.bias", "out_proj.weight", "out_proj.bias"};
+    for (int i = 0; i < 8; ++i) {
+      Tensor t = named.at(names[i]);
+      std::memcpy(t.data(), params[i], t.bytes());
+      t.set_requires_grad(false);
+    }
+    mha->to(dev);
+    mha->eval();
+    Tensor in({B, T, E}, cpu, dt, false);
+    std::memcpy(in.data(), x, in.bytes());
+    inference::detail::InferenceModeGuard guard;
+    Tensor out = mha->forward(in.to(dev));
+    if (kernel_us) *kernel_us = BackendManager::get(dev)->get_last_kernel_time_us();
+    Tensor oc = out.to(cpu);
+    Tensor c = oc.is_contiguous() ? oc : oc.contiguous();
+    std::memcpy(y, c.data(), c.bytes());
+  });
+}
+
+// Backend::all_reduce through the adapter without a communicator: `world` threads of this
+// process, each with its own device buffer, meet in the reference's in-process rendezvous
+// (tests/test_backend_manager.cpp:1371-1397 does the same on its CPU backend).
+// bufs[i] are host arrays of n elements; every one receives the sum.
+int refb200_all_reduce_threads(void *const *bufs, int world, long n, int dtype, int device_index) {
+  return guarded([&] {
+    setenv("MUNET_ALLREDUCE_WORLD_SIZE", std::to_string(world).c_str(), 1);
+    const Device cpu{DeviceType::CPU, 0}, dev{DeviceType::CUDA, device_index};
+    const DataType dt = static_cast<DataType>(dtype);
+    auto backend = BackendManager::get(dev);
+    std::vector<Tensor> ts;
+    for (int i = 0; i < world; ++i) {
+      Tensor h({static_cast<int>(n)}, cpu, dt, false);
+      std::memcpy(h.data(), bufs[i], h.bytes());
+      ts.push_back(h.to(dev));
+    }
+    std::vector<std::string> errs(world);
+    std::vector<std::thread> th;
+    for (int i = 0; i < world; ++i)
+      th.emplace_back([&, i] {
+        try {
+          backend->all_reduce(*ts[i].impl_->storage, static_cast<size_t>(n));
+        } catch (const std::exception &e) {
+          errs[i] = e.what();
+        }
+      });
+    for (auto &t : th) t.join();
+    unsetenv("MUNET_ALLREDUCE_WORLD_SIZE");
+    for (auto &e : errs)
+      if (!e.empty()) throw std::runtime_error(e);
+    for (int i = 0; i < world; ++i) {
+      Tensor h = ts[i].to(cpu);
+      std::memcpy(bufs[i], h.data(), h.bytes());
+    }
   });
 }
 

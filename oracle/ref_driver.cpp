@@ -159,6 +159,15 @@ int ref_activation(const void *x, void *y, long n, int dtype, int act) {
   });
 }
 
+// Tensor::to(DataType) (src/tensor.cpp:249-284): the conversion the reference applies to every
+// parameter when a float32 model is moved to another dtype.
+int ref_convert(const void *x, void *y, long n, int from_dtype, int to_dtype) {
+  return guarded([&] {
+    Tensor out = from_host(x, {static_cast<int>(n)}, from_dtype).to(dt(to_dtype));
+    to_host(out, y);
+  });
+}
+
 // out = a + b, same shape (the residual add).
 int ref_add(const void *a, const void *b, void *y, long n, int dtype) {
   return guarded([&] {

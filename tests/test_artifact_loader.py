@@ -100,3 +100,58 @@ def test_json_edge_cases(tmp_path):
     save_deploy(p, cfg, {"1.weight": np.ones(4, np.float32), "1.bias": np.zeros(4, np.float32)})
     got = inspect_artifact(p)["config"]
     assert got["layers"][0]["p"] == 0.25 and abs(got["layers"][1]["eps"] - 1e-5) < 1e-12
+
+
+def _patch(path, old: bytes, new: bytes, dst):
+    data = open(path, "rb").read()
+    assert old in data and len(old) == len(new)
+    open(dst, "wb").write(data.replace(old, new))
+
+
+def test_malformed_files_are_refused_not_crashed_on(tmp_path):
+    """Truncated headers and size fields that point outside the file: the loader is reached through
+    extern "C" entry points that promise never to throw, so every one of these must come back as
+    an ordinary load failure."""
+    import struct
+    good = str(tmp_path / "good.npz")
+    save_deploy(good, CFG, TENSORS)
+    # 1. an npy header in which nothing follows 'fortran_order:'
+    bad = str(tmp_path / "fortran.npz")
+    data = open(good, "rb").read()
+    i = data.index(b"'fortran_order': False")
+    j = data.index(b"\n", i)  # npy headers end with a newline
+    data = data[:i] + b"'fortran_order':" + b" " * (j - i - len(b"'fortran_order':")) + data[j:]
+    open(bad, "wb").write(data)
+    with pytest.raises(MuNetError):
+        inspect_artifact(bad)
+    # 2. the file cut short at several places
+    raw = open(good, "rb").read()
+    for cut in (10, 30, len(raw) // 2, len(raw) - 30, len(raw) - 5):
+        t = str(tmp_path / f"cut{cut}.npz")
+        open(t, "wb").write(raw[:cut])
+        with pytest.raises(MuNetError):
+            inspect_artifact(t)
+    # 3. central-directory fields (entry sizes, local header offsets, directory offset) blown up
+    eocd = raw.rindex(b"PK\x05\x06")
+    cd_off = struct.unpack_from("<I", raw, eocd + 16)[0]
+    for field_off, value in ((20, 0xFFFFFFF0), (24, 0xFFFFFFF0), (42, 0xFFFFFFF0)):
+        b = bytearray(raw)
+        struct.pack_into("<I", b, cd_off + field_off, value)
+        t = str(tmp_path / f"cd{field_off}.npz")
+        open(t, "wb").write(bytes(b))
+        with pytest.raises(MuNetError):
+            inspect_artifact(t)
+    b = bytearray(raw)
+    struct.pack_into("<I", b, eocd + 16, 0xFFFFFFF0)
+    struct.pack_into("<I", b, eocd + 12, 0x20)
+    t = str(tmp_path / "eocd.npz")
+    open(t, "wb").write(bytes(b))
+    with pytest.raises(MuNetError):
+        inspect_artifact(t)
+    # 4. a shape whose element count wraps around 2^64
+    t = str(tmp_path / "shape.npz")
+    i = raw.index(b"'shape': (3, 2)")
+    b = raw[:i] + b"'shape': (3, 9)" + raw[i + len(b"'shape': (3, 2)"):]
+    open(t, "wb").write(b)
+    with pytest.raises(MuNetError, match="shorter than its shape"):
+        inspect_artifact(t)

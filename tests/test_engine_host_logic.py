@@ -32,3 +32,24 @@ def test_only_inputs_whose_changes_can_be_seen_are_cached():
     t.add_(1.0)
     k1 = _input_identity(t)
     assert k0[0] == k1[0] and k1[1] == k0[1] + 1                   # in-place op bumps the version
+
+
+def test_attention_size_checks_do_not_wrap():
+    """Sizes whose product B*H*T*T*sizeof wraps in 64 bits (2^64 here) must be refused, not taken
+    for zero bytes. Nothing is launched on these paths, so no GPU is needed."""
+    import ctypes as C
+    import munet_b200 as mb
+    lib = mb.lib()
+    err = C.create_string_buffer(512)
+    dummy = 0x1000  # never dereferenced: the size check comes first
+    rc = lib.mu_attention_static_scratch(0, dummy, dummy, dummy, dummy, 32768, 32768, 65536, 16, 1, 0, 0,
+                                         None, 0, err, 512)
+    assert rc == 7 and b"exceed" in err.value                     # MU_ERR_SIZE
+    rc = lib.mu_attention_static_scratch(0, dummy, dummy, dummy, dummy, 1, 1, 8192, 16, 1, 0, 0,
+                                         None, 0, err, 512)
+    assert rc == 7                                                # 256 MiB of scores > 64 MiB
+    assert lib.mu_attention_workspace_bytes_composed(32768, 32768, 65536, 16, 0) == 0
+    assert lib.mu_attention_workspace_bytes(32768, 32768, 65536, 16, 0) == 0
+    assert lib.mu_attention_workspace_bytes_composed(2, 3, 40, 16, 0) == 2 * 3 * 40 * 40 * 4
+    assert lib.mu_attention_workspace_bytes(2, 16, 1024, 128, 2) == 0   # fused kernel: no workspace
+    assert lib.mu_attention_workspace_bytes_composed(2, 16, 1024, 128, 2) == 2 * 16 * 1024 * 1024 * 2

@@ -92,3 +92,44 @@ def test_reference_engine_runs_unet_style_block_on_b200_backend(ref_b200, tmp_pa
     got = ref_b200.engine_run_npz(path, x, F32)
     assert got.shape == want.shape
     assert_close(got, want, F32, what="reference Engine on B200Backend, UNet-style block")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("causal", [True, False])
+def test_reference_mha_module_runs_on_b200_backend(ref_b200, dtype, causal):
+    """The reference's own nn::MultiHeadAttention on the B200 backend: projections, the head split
+    and merge permutes (device-side to_contiguous, 2- and 4-byte elements), the stride-ignoring
+    score matmul (literal K addressing), scale, softmax and P.V — against the checker's module,
+    which is pinned to the same module on the reference's CPU backend."""
+    rng = np.random.default_rng(31 + dtype)
+    B, T, E, H = 2, 24, 64, 4
+
+    def r(shape, scale=1.0):
+        a = (rng.standard_normal(shape) * scale).astype(np.float32)
+        return a if dtype == F32 else oracle.to_bf16(a)
+    params = []
+    for _ in range(4):
+        params += [r((E, E), 1.0 / np.sqrt(E)), r((E,), 0.05)]
+    x = r((B, T, E))
+    got, kernel_us = ref_b200.mha_forward(x, params, H, causal, dtype)
+    want = oracle.port().mha(x, params, H, causal, dtype, kmode=oracle.K_LITERAL)
+    assert_close(got, want, dtype, what="reference MultiHeadAttention on B200Backend")
+    assert kernel_us > 0.0  # get_last_kernel_time_us reports the device time of the last op
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_all_reduce_through_the_adapter_matches_reduce_sum_bytes(ref_b200, dtype):
+    """Tensor.all_reduce on the drop-in backend with two and three in-process participants (the
+    reference's rendezvous, tests/test_backend_manager.cpp:1371-1397): every participant ends
+    with the checker's sum (double accumulation, one rounding)."""
+    rng = np.random.default_rng(33)
+    for world in (2, 3):
+        bufs = [(rng.standard_normal(257)).astype(np.float32) for _ in range(world)]
+        if dtype == BF16:
+            bufs = [oracle.to_bf16(b) for b in bufs]
+        want = oracle.port().all_reduce_sum(bufs, dtype)
+        for got in ref_b200.all_reduce_threads(bufs, dtype):
+            assert np.array_equal(got, want)
+    # the reference's known answer: [1,2] + [3,4] -> [4,6] on both
+    a, b = ref_b200.all_reduce_threads([np.array([1, 2], np.float32), np.array([3, 4], np.float32)], F32)
+    assert a.tolist() == [4.0, 6.0] and b.tolist() == [4.0, 6.0]

@@ -188,3 +188,128 @@ def test_prepared_inputs_stats_and_observer(ctx, tmp_path):
         eng.run(np.zeros((4, 8), np.float32))
     assert events[-1]["type"] == "error"
     eng.close()
+
+
+def test_wildcard_shape_contract_builds_one_plan_per_shape(ctx, tmp_path):
+    """Engine::compile(example, {-1, 8}) (tests/test_inference.cpp:402-438): the batch extent may
+    vary from run to run, the feature extent may not. Every new concrete shape gets its own plan
+    (arena + graph) over the shared weights; a shape seen before reuses its plan; the number of
+    plans kept is bounded."""
+    import munet_b200 as mb
+    rng = np.random.default_rng(21)
+    path, tensors = mlp_artifact(tmp_path, rng, [8, 16, 4], ["ReLU"])
+    eng = make_engine(ctx, F32).load(path)
+    with pytest.raises(mb.MuNetError, match="dim mismatch at index 1"):
+        eng.compile((1, 8), expected_input_shape=(-1, 9))      # the example itself must fit
+    with pytest.raises(mb.MuNetError, match="output shape mismatch"):
+        eng.compile((1, 8), expected_input_shape=(-1, 8), expected_output_shape=(-1, 5))
+    eng.compile((1, 8), expected_input_shape=(-1, 8), expected_output_shape=(-1, 4))
+    assert eng.plan_count == 1
+    for batch in (4, 1, 7, 4):
+        x = rng.standard_normal((batch, 8)).astype(np.float32)
+        got = eng.run(x)
+        assert got.shape == (batch, 4)
+        assert np.array_equal(got, mlp_oracle(x, tensors, ["ReLU"]))
+    assert eng.plan_count == 3                                    # shapes 1, 4 and 7
+    with pytest.raises(mb.MuNetError, match="dim mismatch at index 1"):
+        eng.run(np.zeros((4, 9), np.float32))
+    with pytest.raises(mb.MuNetError, match="rank mismatch"):
+        eng.run(np.zeros((4, 8, 1), np.float32))
+    eng._opt("plan_cache_entries", 2)
+    for batch in (2, 3, 5):
+        x = rng.standard_normal((batch, 8)).astype(np.float32)
+        assert np.array_equal(eng.run(x), mlp_oracle(x, tensors, ["ReLU"]))
+    assert eng.plan_count <= 2
+    x = rng.standard_normal((1, 8)).astype(np.float32)            # an evicted shape is rebuilt
+    assert np.array_equal(eng.run(x), mlp_oracle(x, tensors, ["ReLU"]))
+    # strict_shape_check off: the reference forwards any shape (tests/test_inference.cpp:402-419)
+    eng2 = make_engine(ctx, F32).load(path).compile((2, 8))
+    with pytest.raises(mb.MuNetError, match="dim mismatch at index 0"):
+        eng2.run(np.zeros((3, 8), np.float32))
+    eng2.set_strict_shape_check(False)
+    x = rng.standard_normal((3, 8)).astype(np.float32)
+    assert np.array_equal(eng2.run(x), mlp_oracle(x, tensors, ["ReLU"]))
+    eng.close()
+    eng2.close()
+
+
+def test_lean_mode_and_memory_capture(ctx, tmp_path):
+    """Engine::set_lean_mode / set_capture_profiler_memory (src/inference.hpp:323-341): each one
+    switches the other off; memory figures appear in the stats only while capture is on; the load
+    event carries the tensor census only outside lean mode."""
+    rng = np.random.default_rng(22)
+    path, tensors = mlp_artifact(tmp_path, rng, [8, 4], [])
+    events = []
+    eng = make_engine(ctx, F32)
+    eng.set_observer(events.append)
+    eng.set_capture_profiler_memory(True)
+    assert eng.capture_profiler_memory and not eng.lean_mode
+    eng.load({"type": "Linear", "in_features": 8, "out_features": 4, "bias": True},
+             {"weight": tensors["0.weight"], "bias": tensors["0.bias"]})
+    assert "2 parameter/buffer tensor(s)" in events[-1]["message"]
+    eng.compile((3, 8))
+    x = rng.standard_normal((3, 8)).astype(np.float32)
+    eng.run(x)
+    st = eng.engine_stats
+    assert st["current_memory_bytes"] > 0 and st["peak_memory_bytes"] >= st["current_memory_bytes"]
+    eng.set_lean_mode(True)
+    assert eng.lean_mode and not eng.capture_profiler_memory
+    eng.load({"type": "Linear", "in_features": 8, "out_features": 4, "bias": True},
+             {"weight": tensors["0.weight"], "bias": tensors["0.bias"]})
+    assert "tensor(s)" not in events[-1]["message"] and "gradients will remain disabled" in events[-1]["message"]
+    eng.compile((3, 8))
+    want = oracle.port().linear(x, tensors["0.weight"], tensors["0.bias"], F32)
+    assert np.array_equal(eng.run(x), want)
+    eng.close()
+
+
+def test_prepared_input_is_converted_like_a_plain_run(ctx):
+    """prepare_batch + run must give what a plain run gives for inputs whose dtype is not the
+    compiled one: torch.randint's int64 ids and a float64 array."""
+    import torch
+    import munet_b200 as mb
+    from munet_b200.inference import gpt_decoder_config, gpt_param_names
+    B, T, V, d, H, L = 2, 16, 50, 32, 2, 1
+    rng = np.random.default_rng(23)
+    ps = gpt_params(rng, V, T, d, L, F32, std=0.08)
+    eng = make_engine(ctx, F32, kmode=oracle.K_MATH)
+    eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)))
+    eng.compile((B, T), I32)
+    ids64 = torch.randint(0, V, (B, T))                       # int64
+    plain = eng.run(ids64.numpy().astype(np.int32))
+    eng.prepare_batch([ids64])
+    assert eng.engine_stats["prepared_input_cache_entries"] == 1
+    assert np.array_equal(eng.run(ids64), plain)
+    assert eng.engine_stats["prepared_input_cache_hits"] == 1
+    with pytest.raises(mb.MuNetError, match="dtype"):          # a device tensor is taken as raw bytes
+        eng.run(ids64.cuda())
+    assert eng.run(ids64.to(torch.int32).cuda()) is None       # result stays in the arena
+    eng.close()
+
+
+@pytest.mark.parametrize("kmode", [oracle.K_LITERAL, oracle.K_MATH])
+def test_float32_artifact_runs_in_bfloat16(ctx, tmp_path, kmode):
+    """Module::to(BFloat16) on load (src/core/module.hpp:177-194, Tensor::to src/tensor.cpp:249-284):
+    an artifact of float32 tensors loaded with compute_dtype = bfloat16 must behave like the
+    checker fed with the same tensors rounded to bf16 by the reference's rule (RNE, +0x7fff+lsb)."""
+    from munet_b200.inference import gpt_decoder_config, gpt_param_names, save_deploy
+    B, T, V, d, H, L = 2, 32, 96, 64, 2, 2
+    rng = np.random.default_rng(24)
+    ps32 = gpt_params(rng, V, T, d, L, F32, std=0.08)
+    # values that sit exactly between two bf16 numbers exercise round-to-nearest-even
+    ps32[0].reshape(-1)[:4] = np.array([1.00390625, 1.01171875, -1.00390625, 3.0e-39], np.float32)
+    names = gpt_param_names(L)
+    path = str(tmp_path / "decoder_f32.npz")
+    save_deploy(path, gpt_decoder_config(V, T, d, H, L), dict(zip(names, ps32)))
+    ids = rng.integers(0, V, (B, T)).astype(np.int32)
+    ids[0, 0] = 0  # the row with the tie values is looked up
+    want = oracle.port().gpt_forward(ids, [oracle.to_bf16(p) for p in ps32], V, d, H, L, BF16, kmode=kmode)
+    for source in ("artifact", "memory"):
+        eng = make_engine(ctx, BF16, kmode=kmode)
+        if source == "artifact":
+            eng.load(path)
+        else:
+            eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(names, ps32)))
+        eng.compile((B, T), I32)
+        assert_close(eng.run(ids), want, BF16, what=f"fp32 {source} in bf16")
+        eng.close()

@@ -1,4 +1,4 @@
-"""GPU parity at the BASELINE transformer configs (bf16, literal K addressing).
+"""GPU parity at the two transformer configs of the benchmark (bf16), full size.
 
 The CPU checker cannot run the full batches, so parity uses what the domain offers:
 sequences are independent (Engine::run_batch is a loop over inputs) and attention is
@@ -34,12 +34,22 @@ def decoder_weights(rng, V, T, d, L):
     return ps
 
 
-@pytest.mark.parametrize("name,V,T,d,H,L,B,prefix", [
-    ("gpt_s", 8192, 256, 512, 8, 6, 32, 256),
-    ("gpt_l", 32000, 1024, 2048, 16, 24, 8, 48),
+# Depth drift of a bf16 decoder, measured on the CPU alone with `python -m oracle.drift_floor`
+# (the checker against itself, float instead of double accumulation and nothing else changed;
+# d2048 h16 V32000, 48 tokens): worst element / elementwise bound = 1.9-2.0 at 6 layers and
+# 2.8-3.9 at 24 layers, rel-inf 1.0 % / 1.6-1.8 %, rel-rms 0.9 % / 1.6 %. No tensor-core kernel can
+# sit below that floor, so at depth the elementwise bound is asserted as floor x 1.5 and the two
+# norm-wise figures against the 2e-2 tolerance itself.
+DEPTH_WORST_CAP = {6: 2.0 * 1.5, 24: 3.9 * 1.5}
+
+
+@pytest.mark.parametrize("name,V,T,d,H,L,B,prefixes", [
+    ("gpt_s", 8192, 256, 512, 8, 6, 32, (256, 256)),
+    ("gpt_l", 32000, 1024, 2048, 16, 24, 8, (264, 48)),
 ])
-def test_full_config_prefix_parity_math_mode(name, V, T, d, H, L, B, prefix):
-    """Full-size config on the GPU (true Q.K^T) vs the checker on a token prefix of two sequences."""
+def test_full_config_prefix_parity_math_mode(name, V, T, d, H, L, B, prefixes):
+    """Full-size config on the GPU (true Q.K^T) vs the checker on a token prefix of two sequences;
+    the long prefix of the 24-layer model spans three 128-key tiles of the fused attention kernel."""
     import munet_b200 as mb
     from munet_b200.inference import Engine, gpt_decoder_config, gpt_param_names
     seed = 4 if name == "gpt_s" else 5
@@ -54,20 +64,19 @@ def test_full_config_prefix_parity_math_mode(name, V, T, d, H, L, B, prefix):
     assert logits.shape == (B, T, V) and np.isfinite(oracle.from_bf16(logits[:, ::max(1, T // 8)])).all()
     # device argmax == first-max argmax of the device logits (bit-exact index rule)
     assert np.array_equal(am, oracle.port().argmax(logits, BF16))
-    for b in (0, B - 1):
+    for b, prefix in zip((0, B - 1), prefixes):
         sub_ps = list(ps)
         sub_ps[1] = ps[1][:prefix]  # positional table rows 0..prefix-1
         want = oracle.port().gpt_forward(ids[b:b + 1, :prefix], sub_ps, V, d, H, L, BF16, kmode=oracle.K_MATH)
         got = logits[b:b + 1, :prefix]
-        # Deep bf16 stacks: two valid evaluation orders of the same bf16 pipeline (fp32 vs double
-        # accumulation, online vs two-pass softmax) drift apart by rounding noise that grows with
-        # depth. Criteria at full size: max error within 2e-2 of the largest logit, RMS error within
-        # 2e-2 of the RMS logit, and no element further than 5x the elementwise small-shape bound
-        # (measured: 2.2x at 6 layers, 3.7x at 24 layers).
+        # Deep bf16 stacks: two valid evaluation orders of the same bf16 pipeline drift apart by
+        # rounding noise that grows with depth (see DEPTH_WORST_CAP). Criteria at full size: max
+        # error within 2e-2 of the largest logit, RMS error within 2e-2 of the RMS logit, and no
+        # element further than the measured floor x 1.5 from the elementwise bound.
         ok, worst, rel = close(got, want, BF16, rtol=2e-2)
         g, w_ = oracle.from_bf16(got).astype(np.float64), oracle.from_bf16(want).astype(np.float64)
         rel_rms = float(np.sqrt(np.mean((g - w_) ** 2)) / np.sqrt(np.mean(w_ ** 2)))
-        assert rel <= 2e-2 and rel_rms <= 2e-2 and worst <= 5.0, \
+        assert rel <= 2e-2 and rel_rms <= 2e-2 and worst <= DEPTH_WORST_CAP[L], \
             f"{name} seq {b}: worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}"
         agree = float((oracle.port().argmax(got, BF16) == oracle.port().argmax(want, BF16)).mean())
         assert agree >= 0.9, f"{name} seq {b}: argmax agreement {agree}"
@@ -105,5 +114,34 @@ def test_gpt_s_literal_mode_full_batch_geometry():
     # same full-size criteria as above (measured: worst element 1.6x the small-shape bound)
     assert rel <= 2e-2 and rel_rms <= 2e-2 and worst <= 5.0, \
         f"worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}"
+    eng.close()
+    ctx.close()
+
+
+def test_gpt_l_literal_mode_headline_geometry():
+    """The benchmark's own mode at the benchmark's own geometry: literal K addressing with 16 heads
+    of 128, d_model 2048, 1024 positions (eight key tiles per row) and the 32000-wide head. The
+    checker needs the whole batch (a literal score reads K rows of every head and sequence), so
+    depth is cut to one layer and the batch to two sequences; every kernel runs at the config's
+    per-layer shape. One layer deep, the elementwise 2e-2 bound itself is asserted."""
+    import munet_b200 as mb
+    from munet_b200.inference import Engine, gpt_decoder_config, gpt_param_names
+    V, T, d, H, L, B = 32000, 1024, 2048, 16, 1, 2
+    rng = np.random.default_rng(1005)
+    ps = decoder_weights(rng, V, T, d, L)
+    ids = np.random.default_rng(2005).integers(0, V, (B, T)).astype(np.int32)
+    want = oracle.port().gpt_forward(ids, ps, V, d, H, L, BF16, kmode=oracle.K_LITERAL)
+    ctx = mb.Context(0)
+    eng = Engine(ctx=ctx, compute_dtype=BF16, kmode=mb.K_LITERAL, argmax=True)
+    eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)), tensor_dtype=BF16)
+    eng.compile((B, T), I32)
+    got, am = eng.run(ids)
+    ok, worst, rel = close(got, want, BF16, rtol=2e-2)
+    g, w_ = oracle.from_bf16(got).astype(np.float64), oracle.from_bf16(want).astype(np.float64)
+    rel_rms = float(np.sqrt(np.mean((g - w_) ** 2)) / np.sqrt(np.mean(w_ ** 2)))
+    assert ok, f"worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}"
+    assert np.array_equal(am, oracle.port().argmax(got, BF16))
+    agree = float((am == oracle.port().argmax(want, BF16)).mean())
+    assert agree >= 0.9, f"argmax agreement {agree}"
     eng.close()
     ctx.close()

@@ -194,3 +194,15 @@ def test_data_movement_is_what_numpy_does(dtype):
     else:  # the reference's CPU backend has no bfloat16 concat (explicit_unsupported)
         with pytest.raises(RuntimeError, match="does not support feature 'concat'"):
             oracle.ref().concat(xs, dtype)
+
+
+def test_float32_to_bfloat16_conversion_rule():
+    """Tensor::to(BFloat16) of the reference (src/tensor.cpp:249-284, src/types.hpp:311-317) against
+    the checker's to_bf16 on ties (round to even), values next to ties, denormals, infinities and
+    random data: the rule the engine applies when float32 tensors are loaded for bfloat16 compute."""
+    special = np.array([1.00390625, 1.01171875, -1.00390625, 1.00390631, 1.00390619, 3.0e-39, -3.0e-39,
+                        0.0, -0.0, np.inf, -np.inf, 65280.0, 3.3895314e38, 1e-45], np.float32)
+    x = np.concatenate([special, np.random.default_rng(3).standard_normal(4096).astype(np.float32) * 7])
+    same(oracle.to_bf16(x), oracle.ref().convert(x, F32, BF16))
+    back = oracle.ref().convert(oracle.to_bf16(x), BF16, F32)
+    same(back, oracle.from_bf16(oracle.to_bf16(x)))
