@@ -1,15 +1,22 @@
 #!/usr/bin/env python
 """Forward-inference throughput of the GPT-style decoder config
-(24 layers, d_model 2048, 16 heads, vocab 32000, seq 1024, batch 64 per GPU, bf16)
+(24 layers, d_model 2048, 16 heads, vocab 32000, seq 1024, batch 64, bf16)
 through the munet_b200 compiled executor — tokens/s, roofline fraction of the
 dominant kernel, and the reference CPU path timed on the same host.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --kernel-case linear 16384 2048 2048 --act gelu      (one kernel, one shape)
+    python bench.py --configs-only                                        (the four smaller workloads)
 
-One process per GPU (launched under torch.distributed.run for N > 1). The batch is
-sharded over ranks with no data-path collective: every rank holds a full weight
-replica and runs its own 64 sequences ("weak" scaling; whole-job value = all
-ranks' tokens / max-over-ranks device time). Prints ONE JSON line on rank 0.
+One process per GPU (launched under torch.distributed.run for N > 1). The batch of 64 sequences
+is sharded over the ranks — rank r of R runs sequences [r*64/R, (r+1)*64/R), the independent
+inputs of the reference's Engine::run_batch (src/inference.hpp:618-627) — with a full weight
+replica per GPU and no data-path collective: "strong" scaling; whole-job value = 64*1024 tokens /
+max-over-ranks device time. Sub-records of the same JSON line carry the other variants:
+  weak     (N > 1) 64 sequences on EVERY rank, global batch 64*N
+  tp2      (N = 2) one replica split Megatron-style over both GPUs, NCCL all-reduce
+  configs  (N = 1) MLP, linear sweep, CNN and the 6-layer decoder, each with its roofline fraction
+Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
@@ -27,12 +34,28 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 CONFIGS = {
-    # BASELINE config 5: the one the headline metric is quoted on
+    # the 24-layer decoder: the workload the headline metric is quoted on
     "gpt_l": dict(n_layers=24, d_model=2048, n_heads=16, vocab=32000, seq=1024, batch=64),
-    # BASELINE config 4 (parity-test size; selectable for quick runs)
+    # the 6-layer decoder (quick runs)
     "gpt_s": dict(n_layers=6, d_model=512, n_heads=8, vocab=8192, seq=256, batch=32),
 }
 METRIC = "tokens/s, GPT-style decoder forward (24L d2048 16h, seq 1024, bf16)"
+
+# Nominal B200 figures, stated beside the measured ones: HBM3e 8 TB/s (the ~8 TB/s the spec of
+# this work names; the HGX part is 7.7), dense bf16 2250 TFLOP/s, dense TF32 1100 TFLOP/s.
+NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0, "tf32_tflops": 1100.0}
+
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the bf16 GEMM at
+# M = 16384 rows, per (K, N, residual) of the 24-layer decoder: ncu captures summarised in
+# profiles/gemm_bf16_tcgen05_M16384_N2048_K2048_gelu.md. A and C traffic grows in proportion to
+# M and B is small, so a launch at M rows is charged M/16384 of these.
+GEMM_TRAFFIC_AT_M16384 = {
+    (2048, 6144, False): 97.6e6 + 165.4e6,     # fused q/k/v projection
+    (2048, 2048, True): 75.6e6 + 32.5e6 + 67.1e6,   # out_proj (+ residual read, counted algorithmically)
+    (2048, 8192, False): 127.1e6 + 238.4e6,    # fc1 + GELU
+    (8192, 2048, True): 492.6e6 + 60.1e6 + 67.1e6,  # fc2 (+ residual read)
+    (2048, 32000, False): 685.5e6 + 1026.2e6,  # LM head, column panels
+}
 
 
 def peaks():
@@ -101,6 +124,9 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons)}
 
 
+# ----------------------------------------------------------------------------------------------
+# reference arm / CPU baseline
+# ----------------------------------------------------------------------------------------------
 def cpu_reference_sample(cfg, steps=1, warmup=0):
     """Times the reference's own CPU implementation (oracle/_ref, the unmodified MuNet CPU core;
     the C restatement when that library is absent) on a bounded sample of the workload and
@@ -160,7 +186,7 @@ def run_reference(args, cfg):
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * base["seconds"] / max(1, args.steps), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(cfg, args.gpus),
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
@@ -170,40 +196,28 @@ def run_reference(args, cfg):
     print(json.dumps(line))
 
 
-def workload_config(cfg, n_gpus, tp=1):
+def workload_config(cfg, n_gpus):
+    per = cfg["batch"] / n_gpus
     return {
         "workload": (f"GPT decoder forward: {cfg['n_layers']}L d{cfg['d_model']} h{cfg['n_heads']} "
-                     f"vocab {cfg['vocab']} seq {cfg['seq']} batch {cfg['batch']}/GPU, pre-LN, "
+                     f"vocab {cfg['vocab']} seq {cfg['seq']} batch {cfg['batch']}, pre-LN, "
                      "causal, 4x GELU MLP, weights N(0,0.02), uniform random ids"),
-        "global_batch": cfg["batch"] * (n_gpus if tp == 1 else 1), "seq_len": cfg["seq"],
-        "parallelism": (f"batch-sharded x{n_gpus}, full replica per GPU, no collective" if tp == 1 else
-                        f"tensor-parallel x{tp} (Megatron column/row split, NCCL all-reduce), one replica"),
-        "attention_k_addressing": ("literal (reference semantics)" if tp == 1 else
-                                   "math (true Q.K^T; literal addressing cannot be head-sharded)"),
-        "l2": "no flush needed: per-step working set (2.7 GB weights + >6 GB activations) >> 126 MB L2",
+        "global_batch": cfg["batch"], "seq_len": cfg["seq"],
+        "parallelism": (f"batch of {cfg['batch']} sharded x{n_gpus} ({per:g} sequences per GPU), "
+                        "full replica per GPU, no collective"),
+        "attention_k_addressing": "literal (reference semantics)",
+        "l2": "no flush needed: per-step working set (2.7 GB weights + activations) >> 126 MB L2",
         "e2e_result": "argmax token ids [batch, seq] int32 read back to the host",
     }
 
 
-def run_ours(args, cfg):
-    import torch
-    import torch.distributed as dist
-    import munet_b200 as mb
-    from munet_b200.inference import Engine, gpt_decoder_config, gpt_param_shapes
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
-    L, d, H, V, T, B = (cfg[k] for k in ("n_layers", "d_model", "n_heads", "vocab", "seq", "batch"))
-    dev = torch.device("cuda", local)
+# ----------------------------------------------------------------------------------------------
+# helpers shared by the timed legs
+# ----------------------------------------------------------------------------------------------
+def decoder_tensors(torch, dev, V, T, d, L, seed=1005):
+    from munet_b200.inference import gpt_param_shapes
     gen = torch.Generator(device=dev)
-    gen.manual_seed(1005)  # identical replica on every rank
+    gen.manual_seed(seed)  # identical replica on every rank
 
     def w(*shape):
         return (torch.randn(*shape, device=dev, generator=gen, dtype=torch.float32) * 0.02).bfloat16()
@@ -216,56 +230,59 @@ def run_ours(args, cfg):
             tensors[name] = torch.zeros(*shape, device=dev).bfloat16()
         else:
             tensors[name] = w(*shape)
+    return tensors
 
-    ctx = mb.Context(local)
-    tp = args.tp
-    comm = None
-    if tp > 1:
-        # tensor-parallel variant: all ranks form ONE model replica and run the SAME batch; heads,
-        # MLP columns and the vocabulary are split over ranks, partial sums meet in an NCCL
-        # all-reduce. Needs true Q.K^T: literal K addressing reads across heads and cannot be head-sharded.
-        if world != tp:
-            raise SystemExit("--tp N runs one tensor-parallel group: launch exactly N ranks")
-        comm = mb.Comm.from_torch_distributed(ctx)
-    eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_MATH if tp > 1 else mb.K_LITERAL,
-                 argmax=tp == 1, comm=comm, tp_overlap=bool(args.tp_overlap))
-    eng.load(gpt_decoder_config(V, T, d, H, L), tensors)
-    eng.compile((B, T), mb.I32)
-    del tensors
-    torch.cuda.empty_cache()
-    stats = eng.stats()
 
-    # one seeded global batch of B*world sequences; every rank owns a contiguous shard of it
+def summarize_profile(prof):
+    by_kind = {}
+    for p in prof:
+        k = by_kind.setdefault(p["kind"], {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "n": 0})
+        k["ms"] += p["ms"]
+        k["flops"] += p["flops"]
+        k["bytes"] += p["bytes"]
+        k["n"] += 1
+    return by_kind
+
+
+def gemm_traffic(prof):
+    """(measured-profile DRAM bytes, algorithmic bytes, launches) summed over the GEMMs of one
+    forward; None when a shape has no capture behind it."""
+    total, algo, n = 0.0, 0.0, 0
+    for p in prof:
+        if p["kind"] not in ("linear", "qkv_linear"):
+            continue
+        M, K, N = p["mkn"]
+        key = (K, N, p["residual"])
+        if key not in GEMM_TRAFFIC_AT_M16384:
+            return None
+        total += GEMM_TRAFFIC_AT_M16384[key] * M / 16384.0
+        algo += p["bytes"]
+        n += 1
+    return (total, algo, n) if n else None
+
+
+def run_ours(args, cfg):
+    import torch
+    import torch.distributed as dist
+    import munet_b200 as mb
+    from munet_b200.inference import Engine, gpt_decoder_config
     from munet_b200.sharding import max_over_ranks, shard_bounds
-    ids_gen = torch.Generator(device="cpu")
-    ids_gen.manual_seed(2005)
-    lo, hi = shard_bounds(B * world, rank, world) if tp == 1 else (0, B)
-    ids_host = torch.randint(0, V, (B * world, T), generator=ids_gen, dtype=torch.int32)[lo:hi]
-    ids_host = ids_host.contiguous().pin_memory()
-    ids_dev = ids_host.to(dev)
-    am_host = torch.empty((B, T), dtype=torch.int32).pin_memory()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    L, d, H, V, T, B = (cfg[k] for k in ("n_layers", "d_model", "n_heads", "vocab", "seq", "batch"))
+    dev = torch.device("cuda", local)
+    pk = peaks()
     stream = torch.cuda.current_stream()
     lib = mb.lib()
-
-    def step_device():
-        rc = lib.mu_engine_run(eng._h, ids_dev.data_ptr(), 0, None, 0, None, 0, stream.cuda_stream)
-        if rc:
-            raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
-
-    Vl = V // tp
-    last_host = torch.empty((B, Vl), dtype=torch.bfloat16).pin_memory() if tp > 1 else None
-
-    def step_e2e():
-        rc = lib.mu_engine_run(eng._h, ids_host.data_ptr(), 1, None, 0,
-                               am_host.data_ptr() if tp == 1 else None, 1, stream.cuda_stream)
-        if rc:
-            raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
-        if tp > 1:  # result = next-token logits (this rank's vocabulary slab) of every sequence
-            base = eng.output_ptr
-            for b in range(B):
-                lib.mu_copy(ctx._h, last_host.data_ptr() + b * Vl * 2,
-                            base + ((b * T + T - 1) * Vl) * 2, Vl * 2, 2, stream.cuda_stream)
-            ctx.check(stream)
+    ctx = mb.Context(local)
 
     def barrier():
         torch.cuda.synchronize()
@@ -283,7 +300,46 @@ def run_ours(args, cfg):
         barrier()
         return max_over_ranks(e0.elapsed_time(e1), device=dev)
 
-    for _ in range(max(args.warmup, 3)):
+    tensors = decoder_tensors(torch, dev, V, T, d, L)
+    # one engine, one weight slab; the batch extent is a wildcard of the shape contract so that
+    # the strong shard (64/N sequences) and the weak batch (64) are two plans over the same weights
+    eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_LITERAL, argmax=True)
+    eng.load(gpt_decoder_config(V, T, d, H, L), tensors)
+    lo, hi = shard_bounds(B, rank, world)
+    Bl = hi - lo
+    if Bl == 0:
+        raise SystemExit(f"batch {B} cannot be sharded over {world} ranks")
+    eng.compile((Bl, T), mb.I32, expected_input_shape=(-1, T))
+    del tensors
+    torch.cuda.empty_cache()
+    stats = eng.stats()
+
+    # one seeded global batch; every rank owns a contiguous shard of it
+    ids_gen = torch.Generator(device="cpu")
+    ids_gen.manual_seed(2005)
+    ids_all = torch.randint(0, V, (B * world, T), generator=ids_gen, dtype=torch.int32)
+
+    def make_steps(ids_rows):
+        ids_host = ids_rows.contiguous().pin_memory()
+        ids_dev = ids_host.to(dev)
+        am_host = torch.empty(tuple(ids_rows.shape), dtype=torch.int32).pin_memory()
+
+        def step_device():
+            rc = lib.mu_engine_run(eng._h, ids_dev.data_ptr(), 0, None, 0, None, 0, stream.cuda_stream)
+            if rc:
+                raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
+
+        def step_e2e():
+            rc = lib.mu_engine_run(eng._h, ids_host.data_ptr(), 1, None, 0, am_host.data_ptr(), 1,
+                                   stream.cuda_stream)
+            if rc:
+                raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
+        return step_device, step_e2e, (ids_host, ids_dev, am_host)
+
+    # ---- headline: the batch of 64 split over the ranks (strong scaling) ----
+    step_device, step_e2e, keep = make_steps(ids_all[lo:hi])
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         step_device()
     ctx.check()
     sampler = ClockSampler(local)
@@ -295,63 +351,111 @@ def run_ours(args, cfg):
         step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
     ctx.check()
-
-    tokens_step = B * T * (world if tp == 1 else 1)
+    tokens_step = B * T
     value = tokens_step * args.steps / (ms_total / 1e3)
     e2e_value = tokens_step * args.steps / (ms_e2e / 1e3)
 
     # dominant kernel: the tcgen05 GEMM behind every linear. Timed live with CUDA events
     # around each op of an eager forward on the same stream and buffers.
     prof = eng.profile(reps=2)
-    pk = peaks()
-    by_kind = {}
-    for p in prof:
-        k = by_kind.setdefault(p["kind"], {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "n": 0})
-        k["ms"] += p["ms"]
-        k["flops"] += p["flops"]
-        k["bytes"] += p["bytes"]
-        k["n"] += 1
+    by_kind = summarize_profile(prof)
+    n_gemm = by_kind.get("linear", {"n": 0})["n"] + by_kind.get("qkv_linear", {"n": 0})["n"]
     gemm_ms = by_kind.get("linear", {"ms": 0})["ms"] + by_kind.get("qkv_linear", {"ms": 0})["ms"]
     gemm_fl = by_kind.get("linear", {"flops": 0})["flops"] + by_kind.get("qkv_linear", {"flops": 0})["flops"]
     achieved = gemm_fl / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
+    traffic = gemm_traffic(prof)
+    att = by_kind.get("attention")
     roofline = {
         "bound": "tensor", "kernel": "gemm_bf16_tcgen05_kernel (all Linear layers of one forward)",
         "achieved": achieved, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
         "frac": achieved / pk["bf16_tflops_sustained"], "peak_source": pk["source"] + " (sustained)",
-        # DRAM bytes per launch, averaged over the 97 GEMM launches of one forward of the
-        # default config: ncu captures (dram__bytes_read.sum + dram__bytes_write.sum) of each model
-        # shape at a quarter of the rows, scaled by 4; algorithmic: 1.135e9.
-        "traffic": 1.347e9 if (cfg["d_model"], cfg["n_layers"], cfg["batch"], tp) == (2048, 24, 64, 1) else None,
-        "traffic_unit": "bytes/launch (ncu dram read+write, offline capture)",
-        "launches_per_step": by_kind.get("linear", {"n": 0})["n"] + by_kind.get("qkv_linear", {"n": 0})["n"],
-        "avg_launch_ms": gemm_ms / max(1, by_kind.get("linear", {"n": 0})["n"] + by_kind.get("qkv_linear", {"n": 0})["n"]),
+        "frac_of_measured_burst": achieved / pk["bf16_tflops"],
+        "frac_of_nominal": achieved / NOMINAL["bf16_tflops"],
+        "traffic": traffic[0] / traffic[2] if traffic else None,
+        "traffic_algorithmic": traffic[1] / traffic[2] if traffic else None,
+        "traffic_ratio": traffic[0] / traffic[1] if traffic else None,
+        "traffic_unit": ("bytes/launch: ncu dram read+write per model shape at M=16384 "
+                         "(profiles/gemm_bf16_tcgen05_M16384_N2048_K2048_gelu.md), scaled to this "
+                         "launch's rows and averaged over the GEMM launches of one forward"),
+        "launches_per_step": n_gemm, "avg_launch_ms": gemm_ms / max(1, n_gemm),
         "per_kind_ms": {k: round(v["ms"], 3) for k, v in by_kind.items()},
+        "attention": ({"achieved_tflops_causal_useful": att["flops"] / (att["ms"] / 1e3) / 1e12,
+                       "frac_of_measured_sustained": att["flops"] / (att["ms"] / 1e3) / 1e12 / pk["bf16_tflops_sustained"],
+                       "frac_of_nominal": att["flops"] / (att["ms"] / 1e3) / 1e12 / NOMINAL["bf16_tflops"]}
+                      if att and att["ms"] > 0 else None),
         "hbm_bound_ops": {
-            k: {"achieved_gbs": v["bytes"] / (v["ms"] / 1e3) / 1e9, "frac_of_measured_hbm":
-                v["bytes"] / (v["ms"] / 1e3) / 1e9 / pk["hbm_gbs"]}
+            k: {"achieved_gbs": v["bytes"] / (v["ms"] / 1e3) / 1e9,
+                "frac_of_measured_hbm": v["bytes"] / (v["ms"] / 1e3) / 1e9 / pk["hbm_gbs"],
+                "frac_of_nominal_hbm": v["bytes"] / (v["ms"] / 1e3) / 1e9 / NOMINAL["hbm_gbs"]}
             for k, v in by_kind.items() if k in ("layer_norm", "embed", "argmax") and v["ms"] > 0},
     }
+    per_rank = None
+    if world > 1:  # every rank's own per-kind times: where a strong-scaled shard loses time
+        mine = {"rank": rank, "sequences": Bl, "per_kind_ms": roofline["per_kind_ms"],
+                "gemm_tflops": achieved}
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, mine)
+
+    # ---- weak sub-record: 64 sequences on every rank ----
+    weak = None
+    if world > 1 and not args.no_variants:
+        wl, wh = shard_bounds(B * world, rank, world)
+        step_w, step_w_e2e, keep_w = make_steps(ids_all[wl:wh])
+        eng.select_shape((wh - wl, T))
+        for _ in range(3):
+            step_w()
+        ctx.check()
+        k = max(3, args.steps // 2)
+        ms_w = timed(step_w, k)
+        for _ in range(2):
+            step_w_e2e()
+        ms_we = timed(step_w_e2e, k)
+        ctx.check()
+        weak = {"scaling": "weak", "global_batch": B * world, "steps": k,
+                "value": B * world * T * k / (ms_w / 1e3), "ms_per_step": ms_w / k,
+                "e2e_value": B * world * T * k / (ms_we / 1e3), "unit": "tokens/s"}
+        del keep_w
+
+    eng.close()
+    del keep
+    torch.cuda.empty_cache()
+
+    # ---- tp2 sub-record: one replica over two GPUs ----
+    tp2 = None
+    if world == 2 and not args.no_variants:
+        tp2 = run_tp(torch, dist, mb, ctx, cfg, dev, stream, timed, args, pk)
+
+    configs = None
+    if world == 1 and not args.no_variants:
+        configs = run_configs(torch, mb, reps=args.config_reps, pk=pk)
 
     line = None
     if rank == 0:
         base = cpu_reference_sample(cfg) if world == 1 and not args.no_cpu_baseline else None
-        flops_step = sum(p["flops"] for p in prof) * world
+        flops_step = sum(p["flops"] for p in prof) * B / Bl
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": workload_config(cfg, world, tp), "scaling_note": "strong (one batch over tp ranks)" if tp > 1 else None,
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": B * T * 4 * world,
-                    "d2h_bytes_per_step": (B * T * 4 * world if tp == 1 else B * Vl * 2 * world), "ms_per_step": ms_e2e / args.steps},
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms_total / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(cfg, world),
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": B * T * 4,
+                    "d2h_bytes_per_step": B * T * 4, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": stats["n_launches"] * args.steps,
             "roofline": roofline, "clocks": clocks,
             "model_tflops_per_s": flops_step * args.steps / (ms_total / 1e3) / 1e12,
             "engine": stats,
         }
+        if per_rank is not None:
+            line["per_rank"] = per_rank
+        if weak is not None:
+            line["weak"] = weak
+        if tp2 is not None:
+            line["tp2"] = tp2
+        if configs is not None:
+            line["configs"] = configs
         if base is not None:
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))
-    eng.close()
     ctx.close()
     if world > 1:
         dist.barrier()
@@ -359,22 +463,350 @@ def run_ours(args, cfg):
     return line
 
 
+def run_tp(torch, dist, mb, ctx, cfg, dev, stream, timed, args, pk):
+    """The 2-way tensor-parallel variant on the full batch of 64: heads, MLP columns and the
+    vocabulary split over the two ranks, partial sums of the row-parallel layers exchanged over
+    NVLink. Needs true Q.K^T: literal K addressing reads across heads and cannot be head-sharded."""
+    from munet_b200.inference import Engine, gpt_decoder_config
+    L, d, H, V, T, B = (cfg[k] for k in ("n_layers", "d_model", "n_heads", "vocab", "seq", "batch"))
+    lib = mb.lib()
+    tensors = decoder_tensors(torch, dev, V, T, d, L)
+    comm = mb.Comm.from_torch_distributed(ctx)
+    eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_MATH, comm=comm, tp_overlap=bool(args.tp_overlap))
+    eng.load(gpt_decoder_config(V, T, d, H, L), tensors)
+    eng.compile((B, T), mb.I32)
+    del tensors
+    torch.cuda.empty_cache()
+    g = torch.Generator(device="cpu")
+    g.manual_seed(2005)
+    ids_host = torch.randint(0, V, (B, T), generator=g, dtype=torch.int32).pin_memory()
+    ids_dev = ids_host.to(dev)
+    Vl = V // 2
+    last_host = torch.empty((B, Vl), dtype=torch.bfloat16).pin_memory()
+
+    def step_device():
+        rc = lib.mu_engine_run(eng._h, ids_dev.data_ptr(), 0, None, 0, None, 0, stream.cuda_stream)
+        if rc:
+            raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
+
+    def step_e2e():  # result = next-token logits (this rank's vocabulary slab) of every sequence
+        rc = lib.mu_engine_run(eng._h, ids_host.data_ptr(), 1, None, 0, None, 0, stream.cuda_stream)
+        if rc:
+            raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
+        base = eng.output_ptr
+        for b in range(B):
+            lib.mu_copy(ctx._h, last_host.data_ptr() + b * Vl * 2, base + ((b * T + T - 1) * Vl) * 2,
+                        Vl * 2, 2, stream.cuda_stream)
+        ctx.check(stream)
+
+    for _ in range(3):
+        step_device()
+    ctx.check()
+    k = max(3, args.steps // 2)
+    ms = timed(step_device, k)
+    for _ in range(2):
+        step_e2e()
+    ms_e = timed(step_e2e, k)
+    ctx.check()
+    by_kind = summarize_profile(eng.profile(reps=2))
+    ar = by_kind.get("all_reduce")
+    rec = {
+        "parallelism": "tensor-parallel x2 (Megatron column/row split), one replica, batch 64",
+        "attention_k_addressing": "math (true Q.K^T; literal addressing cannot be head-sharded)",
+        "steps": k, "value": B * T * k / (ms / 1e3), "ms_per_step": ms / k, "unit": "tokens/s",
+        "e2e_value": B * T * k / (ms_e / 1e3),
+        "per_kind_ms": {kk: round(v["ms"], 3) for kk, v in by_kind.items()},
+        "exchange": eng.exchange_description() if hasattr(eng, "exchange_description") else None,
+        "all_reduce": ({"calls": ar["n"], "ms": ar["ms"], "bytes_per_rank": ar["bytes"],
+                        "gbs_per_direction": ar["bytes"] / (ar["ms"] / 1e3) / 1e9} if ar and ar["ms"] > 0 else None),
+        "engine": eng.stats(),
+    }
+    eng.close()
+    comm.close()
+    torch.cuda.empty_cache()
+    return rec
+
+
+# ----------------------------------------------------------------------------------------------
+# the four smaller workloads (sub-records at N = 1)
+# ----------------------------------------------------------------------------------------------
+def _time_engine(torch, mb, eng, x, reps):
+    stream = torch.cuda.current_stream()
+    lib = mb.lib()
+
+    def run():
+        rc = lib.mu_engine_run(eng._h, x.data_ptr(), 0, None, 0, None, 0, stream.cuda_stream)
+        if rc:
+            raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    eng.ctx.check()
+    return e0.elapsed_time(e1) / reps
+
+
+def run_configs(torch, mb, reps=20, pk=None, which=("mlp", "linear_sweep", "cnn", "gpt_s")):
+    """MLP fp32 B256, Y = GELU(X.W + b) for n = 1024..8192 in bf16 and fp32, the small CNN fp32 B512
+    and the 6-layer decoder bf16 B32 through the executor: device-resident seeded inputs, CUDA
+    events over `reps` graph replays after three warm-up runs. Each record states the algorithmic
+    work and the fraction of the roofline that bounds it, against the measured and the nominal peak.
+    (Inputs here are smaller than L2 for the small cases; those are latency-bound and say so.)"""
+    from munet_b200.inference import Engine, gpt_decoder_config, gpt_param_shapes
+    pk = pk or peaks()
+    out = []
+
+    def normal(rng, shape, std, dtype):
+        a = (rng.standard_normal(shape) * std).astype(np.float32)
+        t = torch.from_numpy(a).cuda()
+        return t.bfloat16() if dtype == mb.BF16 else t
+
+    def rec(name, ms, flops, bytes_, units, unit, bound, launches, note=None):
+        tf = flops / ms / 1e9
+        r = {"config": name, "ms": round(ms, 4), unit + "_per_s": units / ms * 1e3, "gflop": flops / 1e9,
+             "tflops": tf, "launches": launches, "bound": bound}
+        if bound == "tensor_bf16":
+            r["frac_of_measured"] = tf / pk["bf16_tflops"]
+            r["frac_of_nominal"] = tf / NOMINAL["bf16_tflops"]
+        elif bound == "tensor_tf32":
+            # no TF32 GEMM is measured on this pool: half the measured bf16 burst stands in for it;
+            # operands split into two TF32 parts cost three products per useful one, so 1/3 is the ceiling
+            r["frac_of_measured"] = tf / (pk["bf16_tflops"] / 2)
+            r["frac_of_nominal"] = tf / NOMINAL["tf32_tflops"]
+            r["ceiling_of_3xtf32"] = 1.0 / 3.0
+        else:  # latency: state both floors
+            hbm_us = bytes_ / pk["hbm_gbs"] / 1e3
+            r["hbm_floor_us"] = hbm_us
+            r["frac_of_measured"] = hbm_us / (ms * 1e3)
+            r["frac_of_nominal"] = bytes_ / NOMINAL["hbm_gbs"] / 1e3 / (ms * 1e3)
+        if note:
+            r["note"] = note
+        out.append(r)
+
+    if "mlp" in which:
+        rng = np.random.default_rng(1001)
+        sizes = [784, 512, 512, 10]
+        layers, tensors = [], {}
+        for i in range(3):
+            layers.append({"type": "Linear", "in_features": sizes[i], "out_features": sizes[i + 1], "bias": True})
+            tensors[f"{len(layers) - 1}.weight"] = normal(rng, (sizes[i], sizes[i + 1]), (2 / sizes[i]) ** 0.5, mb.F32)
+            tensors[f"{len(layers) - 1}.bias"] = torch.zeros(sizes[i + 1], device="cuda")
+            if i < 2:
+                layers.append({"type": "ReLU"})
+        eng = Engine(compute_dtype=mb.F32, argmax=True)
+        eng.load({"type": "Sequential", "layers": layers}, tensors).compile((256, 784))
+        x = torch.from_numpy(np.random.default_rng(2001).random((256, 784), dtype=np.float32)).cuda()
+        ms = _time_engine(torch, mb, eng, x, reps)
+        fl = 2 * 256 * (784 * 512 + 512 * 512 + 512 * 10)
+        rec("mlp fp32 B256", ms, fl, 3.49e6, 256, "samples", "latency", eng.stats()["n_launches"],
+            "bit-exact with the reference's float accumulation order (CUDA cores)")
+        eng.close()
+
+    if "linear_sweep" in which:
+        for dtype, dn in ((mb.BF16, "bf16"), (mb.F32, "fp32")):
+            for n in (1024, 2048, 4096, 8192):
+                rng = np.random.default_rng(1002 + n)
+                tensors = {"0.weight": normal(rng, (n, n), n ** -0.5, dtype),
+                           "0.bias": normal(rng, (n,), 0.02, dtype)}
+                cfg = {"type": "Sequential", "layers": [
+                    {"type": "Linear", "in_features": n, "out_features": n, "bias": True}, {"type": "GELU"}]}
+                eng = Engine(compute_dtype=dtype)
+                eng.load(cfg, tensors).compile((n, n))
+                x = normal(np.random.default_rng(2002 + n), (n, n), n ** -0.5, dtype)
+                r = reps if (dtype == mb.BF16 or n <= 4096) else max(1, reps // 4)
+                ms = _time_engine(torch, mb, eng, x, r)
+                es = 2 if dtype == mb.BF16 else 4
+                tc = dtype == mb.BF16 or 1.0 * n ** 3 >= 2 ** 31
+                rec(f"linear+gelu {dn} n={n}", ms, 2.0 * n ** 3, (3 * n * n + n) * es, n, "rows",
+                    "tensor_bf16" if dtype == mb.BF16 else ("tensor_tf32" if tc else "latency"),
+                    eng.stats()["n_launches"],
+                    None if tc else "below 2^31 multiply-adds: CUDA cores, bit-exact with the reference")
+                eng.close()
+                del eng, x, tensors
+                torch.cuda.empty_cache()
+
+    if "cnn" in which:
+        rng = np.random.default_rng(1003)
+        layers, tensors = [], {}
+        chans = [3, 64, 128, 256]
+        for i in range(3):
+            ic, oc = chans[i], chans[i + 1]
+            layers.append({"type": "Conv2d", "in_channels": ic, "out_channels": oc, "kernel_size": 3,
+                           "stride": 1, "padding": 1})
+            tensors[f"{len(layers) - 1}.weight"] = normal(rng, (oc, ic, 3, 3), (2 / (ic * 9)) ** 0.5, mb.F32)
+            tensors[f"{len(layers) - 1}.bias"] = torch.zeros(oc, device="cuda")
+            layers.append({"type": "ReLU"})
+            layers.append({"type": "MaxPool2d", "kernel_size": 2, "stride": 2, "padding": 0} if i < 2
+                          else {"type": "GlobalAvgPool2d"})
+        layers.append({"type": "Flatten"})
+        layers.append({"type": "Linear", "in_features": 256, "out_features": 10, "bias": True})
+        tensors[f"{len(layers) - 1}.weight"] = normal(rng, (256, 10), (2 / 256) ** 0.5, mb.F32)
+        tensors[f"{len(layers) - 1}.bias"] = torch.zeros(10, device="cuda")
+        eng = Engine(compute_dtype=mb.F32, argmax=True)
+        eng.load({"type": "Sequential", "layers": layers}, tensors).compile((512, 3, 32, 32))
+        x = torch.from_numpy(np.random.default_rng(2003).random((512, 3, 32, 32), dtype=np.float32)).cuda()
+        ms = _time_engine(torch, mb, eng, x, reps)
+        fl = 2.0 * 512 * (32 * 32 * 64 * 27 + 16 * 16 * 128 * 576 + 8 * 8 * 256 * 1152 + 256 * 10)
+        per_op = {}
+        for p in eng.profile(reps=2):
+            per_op.setdefault(p["kind"], []).append(round(p["ms"], 4))
+        rec("cnn fp32 B512", ms, fl, 109e6, 512, "images", "tensor_tf32", eng.stats()["n_launches"],
+            f"per-op ms {per_op}")
+        eng.close()
+
+    if "gpt_s" in which:
+        L, d, H, V, T, B = 6, 512, 8, 8192, 256, 32
+        tensors = decoder_tensors(torch, torch.device("cuda", torch.cuda.current_device()), V, T, d, L, seed=1004)
+        eng = Engine(compute_dtype=mb.BF16, argmax=True)
+        eng.load(gpt_decoder_config(V, T, d, H, L), tensors).compile((B, T), mb.I32)
+        ids = torch.randint(0, V, (B, T), dtype=torch.int32, device="cuda")
+        ms = _time_engine(torch, mb, eng, ids, reps)
+        tok = B * T
+        fl = tok * (L * (2 * 4 * d * d + 2 * 8 * d * d) + 2 * d * V) + L * B * H * 2 * T * T * (d // H)
+        rec("gpt_s bf16 B32 T256", ms, fl, 0, tok, "tokens", "tensor_bf16", eng.stats()["n_launches"],
+            "attention FLOPs counted causal-useful; 58 launches in ~1 ms: launch-latency bound")
+        eng.close()
+    return out
+
+
+# ----------------------------------------------------------------------------------------------
+# one kernel on one shape (the command the profiles/ summaries cite)
+# ----------------------------------------------------------------------------------------------
+def run_kernel_case(argv):
+    """python bench.py --kernel-case KERNEL DIMS... [options]
+        linear M K N [--act gelu] [--no-bias] [--residual]      attention B H T D [--kmode 0|1] [--non-causal]
+        layer_norm ROWS COLS    softmax ROWS COLS    argmax ROWS COLS    eltwise ROWS COLS [--act gelu] [--residual]
+        conv B iC H W oC [--relu] [--pool 2]   (fp32, 3x3, stride 1, pad 1)    linear_f32 M K N [--act gelu]
+    Random operands (torch is used for allocation and CUDA events only). Prints the mean milliseconds
+    over --reps launches after two warm-up launches, with the algorithmic TFLOP/s or GB/s."""
+    import torch
+    import munet_b200 as mb
+    ap = argparse.ArgumentParser(prog="bench.py --kernel-case")
+    ap.add_argument("kernel", choices=["linear", "linear_f32", "attention", "layer_norm", "softmax", "argmax",
+                                       "eltwise", "conv"])
+    ap.add_argument("dims", type=int, nargs="+")
+    ap.add_argument("--act", default="none")
+    ap.add_argument("--no-bias", action="store_true")
+    ap.add_argument("--residual", action="store_true")
+    ap.add_argument("--kmode", type=int, default=0)
+    ap.add_argument("--non-causal", action="store_true")
+    ap.add_argument("--relu", action="store_true")
+    ap.add_argument("--pool", type=int, default=0)
+    ap.add_argument("--reps", type=int, default=5)
+    a = ap.parse_args(argv)
+
+    def timed(fn, reps):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    ctx = mb.Context(0)
+    bf = dict(dtype=torch.bfloat16, device="cuda")
+    if a.kernel in ("linear", "linear_f32"):
+        M, K, N = a.dims
+        f32 = a.kernel == "linear_f32"
+        dt, code = (torch.float32, mb.F32) if f32 else (torch.bfloat16, mb.BF16)
+        x = torch.randn(M, K, device="cuda").to(dt)
+        w = (torch.randn(K, N, device="cuda") / K ** 0.5).to(dt)
+        y = torch.empty(M, N, dtype=dt, device="cuda")
+        bias = None if a.no_bias else torch.zeros(N, dtype=dt, device="cuda")
+        res = torch.randn(M, N, device="cuda").to(dt) if a.residual else None
+        ms = timed(lambda: ctx.linear(x, w, bias, y, M, K, N, code, act=a.act, residual=res), a.reps)
+        print(f"{a.kernel} {M}x{K}x{N} act={a.act} bias={bias is not None} residual={a.residual}: "
+              f"{ms:.4f} ms  {2 * M * K * N / ms / 1e9:.1f} TFLOP/s")
+    elif a.kernel == "attention":
+        B, H, T, D = a.dims
+        q, k, v = (torch.randn(B * H * T, D, device="cuda").bfloat16() for _ in range(3))
+        out = torch.empty(B * T, H * D, **bf)
+        nbytes = ctx.attention_workspace_bytes(B, H, T, D, mb.BF16)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+        causal = not a.non_causal
+        ms = timed(lambda: ctx.attention(q, k, v, out, B, H, T, D, causal, a.kmode, mb.BF16, ws, nbytes), a.reps)
+        fl = (2.0 if causal else 4.0) * B * H * T * T * D
+        print(f"attention B{B} H{H} T{T} D{D} kmode={a.kmode} causal={causal}: {ms:.4f} ms  "
+              f"{fl / ms / 1e9:.1f} TFLOP/s ({'causal-useful' if causal else 'full'})")
+    elif a.kernel == "conv":
+        B, iC, Hh, Ww, oC = a.dims
+        x = torch.rand(B, iC, Hh, Ww, device="cuda")
+        w = torch.randn(oC, iC, 3, 3, device="cuda") * (2.0 / (iC * 9)) ** 0.5
+        bias = torch.zeros(oC, device="cuda")
+        oh, ow = (Hh // 2, Ww // 2) if a.pool == 2 else (Hh, Ww)
+        y = torch.empty(B, oC, oh, ow, device="cuda")
+        ms = timed(lambda: ctx.conv2d(x, w, bias, y, B, iC, Hh, Ww, oC, 3, 1, 1, mb.F32, relu=a.relu, pool=a.pool),
+                   a.reps)
+        fl = 2.0 * B * oC * Hh * Ww * iC * 9
+        print(f"conv3x3 B{B} {iC}->{oC} @{Hh}x{Ww} relu={a.relu} pool={a.pool}: {ms:.4f} ms  "
+              f"{fl / ms / 1e9:.1f} TFLOP/s")
+    elif a.kernel == "argmax":
+        rows, cols = a.dims
+        x = torch.randn(rows, cols, device="cuda").bfloat16()
+        idx = torch.empty(rows, dtype=torch.int32, device="cuda")
+        ms = timed(lambda: ctx.argmax(x, idx, rows, cols, mb.BF16), a.reps)
+        print(f"argmax {rows}x{cols}: {ms:.4f} ms  {(rows * cols * 2 + rows * 4) / ms / 1e6:.0f} GB/s")
+    elif a.kernel == "eltwise":
+        rows, cols = a.dims
+        x = torch.randn(rows, cols, device="cuda").bfloat16()
+        y = torch.empty_like(x)
+        bias = torch.zeros(cols, **bf)
+        res = torch.randn(rows, cols, device="cuda").bfloat16() if a.residual else None
+        ms = timed(lambda: ctx.eltwise(x, y, rows * cols, mb.BF16, act=a.act, bias=bias, cols=cols,
+                                       residual=res), a.reps)
+        nb = (3 if a.residual else 2) * rows * cols * 2
+        print(f"eltwise {rows}x{cols} act={a.act} residual={a.residual}: {ms:.4f} ms  {nb / ms / 1e6:.0f} GB/s")
+    else:
+        rows, cols = a.dims
+        x = torch.randn(rows, cols, device="cuda").bfloat16()
+        y = torch.empty_like(x)
+        if a.kernel == "layer_norm":
+            g, b = torch.ones(cols, **bf), torch.zeros(cols, **bf)
+            ms = timed(lambda: ctx.layer_norm(x, g, b, y, rows, cols, mb.BF16), a.reps)
+        else:
+            ms = timed(lambda: ctx.softmax(x, y, rows, cols, mb.BF16), a.reps)
+        print(f"{a.kernel} {rows}x{cols}: {ms:.4f} ms  {2 * rows * cols * 2 / ms / 1e6:.0f} GB/s")
+    ctx.check()
+    ctx.close()
+
+
 def main():
+    if len(sys.argv) > 1 and sys.argv[1] == "--kernel-case":
+        run_kernel_case(sys.argv[2:])
+        return
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="gpt_l", choices=sorted(CONFIGS))
-    ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch")
+    ap.add_argument("--batch", type=int, default=None, help="override the global batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size (variant run)")
+    ap.add_argument("--no-variants", action="store_true",
+                    help="skip the weak / tp2 / configs sub-records (headline measurement only)")
+    ap.add_argument("--configs-only", action="store_true", help="print the four smaller workloads and exit")
+    ap.add_argument("--config-reps", type=int, default=20)
     ap.add_argument("--tp-overlap", type=int, default=1,
-                    help="1: all-reduce of a row chunk under the GEMM of the next (default); 0: in order")
+                    help="tp2 sub-record: 1 = exchange of a row chunk under the GEMM of the next; 0 = in order")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.batch:
         cfg["batch"] = args.batch
+    if args.configs_only:
+        import torch
+        import munet_b200 as mb
+        for r in run_configs(torch, mb, reps=args.config_reps):
+            print(json.dumps(r), flush=True)
+        return
     if args.impl == "reference":
         run_reference(args, cfg)
     else:

@@ -371,6 +371,9 @@ int mu_engine_run(mu_engine *engine, const void *input, int input_on_host, void 
  * kinds: 0 embed, 1 layer_norm, 2 linear, 3 qkv linear, 4 attention, 5 eltwise, 6 argmax. */
 int mu_engine_profile(mu_engine *engine, int reps, int capacity, int *n_ops, int *kinds, float *ms,
                       double *flops, double *bytes, void *stream);
+/* M, K, N and a residual flag (four ints per op, zeros for ops that are not linears) of the
+ * active plan's ops, in the order mu_engine_profile reports them. */
+int mu_engine_op_dims(const mu_engine *engine, int capacity, int *dims);
 void *mu_engine_output_ptr(const mu_engine *engine);
 /* Host-only: parse + validate a deploy artifact exactly as mu_engine_load does
  * (parse_and_validate_artifact, src/inference_serialization.cpp:919-1033) and

@@ -104,6 +104,7 @@ SIGNATURES = {
     "mu_engine_compile_contract": (_i, [_vp, C.POINTER(_i), _i, C.POINTER(_i), _i]),
     "mu_engine_select_shape": (_i, [_vp, C.POINTER(_i), _i]),
     "mu_engine_plan_count": (_i, [_vp]),
+    "mu_engine_op_dims": (_i, [_vp, _i, C.POINTER(_i)]),
     "mu_engine_output_shape": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "mu_engine_stats": (_i, [_vp] + [C.POINTER(_ll)] * 5),
     "mu_engine_run": (_i, [_vp, _vp, _i, _vp, _i, _vp, _i, _vp]),

@@ -1138,6 +1138,23 @@ int mu_engine_profile(mu_engine *e, int reps, int capacity, int *n_ops, int *kin
   return MU_OK;
 }
 
+// GEMM geometry of every op of the active plan, four ints per op: M, K, N and 1 when a residual
+// is added in the epilogue (zeros for ops that are not linears). Lets a caller group the timings
+// of mu_engine_profile by problem shape.
+int mu_engine_op_dims(const mu_engine *e, int capacity, int *dims) {
+  if (!e || !e->compiled || !dims) return MU_ERR_INVALID;
+  const int n = static_cast<int>(e->ops.size());
+  if (capacity < n) return MU_ERR_SIZE;
+  for (int i = 0; i < n; ++i) {
+    const Op &op = e->ops[i];
+    int *d = dims + 4 * i;
+    d[0] = d[1] = d[2] = d[3] = 0;
+    if (op.kind == OP_LINEAR) d[0] = op.M, d[1] = op.K, d[2] = op.N, d[3] = op.res >= 0 ? 1 : 0;
+    else if (op.kind == OP_QKV) d[0] = op.B * op.T, d[1] = op.K, d[2] = 3 * op.H * op.D;
+  }
+  return MU_OK;
+}
+
 int mu_engine_create(mu_ctx *ctx, mu_engine **out) {
   if (!ctx || !out) return MU_ERR_INVALID;
   mu_engine *e = new (std::nothrow) mu_engine();

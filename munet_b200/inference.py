@@ -275,11 +275,10 @@ class Engine:
             return hit
         self._estats["prepared_input_cache_misses"] += 1
         import torch
-        t = x if hasattr(x, "data_ptr") else torch.from_numpy(x)
-        self._check_contract(tuple(t.shape))
-        # the same conversion the uncached path applies (np.ascontiguousarray(x, dtype=...)):
-        # an int64 id tensor or a float64 array must not reach the engine as raw bytes
-        t = t.contiguous().to(_torch_dtype(self.input_dtype))
+        self._check_contract(tuple(x.shape))
+        # the same conversion the uncached path applies: an int64 id tensor or a float64 array
+        # must not reach the engine as raw bytes
+        t = _as_host_tensor(x, self.input_dtype)
         dev = t.to(torch.device("cuda", self.ctx.device))
         self._estats["prepared_input_cache_evictions"] += self._cache.store(
             key[0], key[1], dev, dev.numel() * dev.element_size())
@@ -328,6 +327,15 @@ class Engine:
             self._rc(self._lib.mu_engine_select_shape(self._h, (C.c_int * len(shape))(*shape), len(shape)))
         self.input_shape = tuple(shape)
         self._read_output_shape()
+
+    def select_shape(self, shape):
+        """Make the plan for ``shape`` (which must satisfy the compile-time contract) the active
+        one ahead of a run, so that building it is not part of the first run's time."""
+        if self.input_shape is None:
+            raise MuNetError(1, "Engine: select_shape() called before compile()")
+        shape = tuple(int(s) for s in shape)
+        self._check_contract(shape)
+        self._select(shape)
 
     def _read_output_shape(self):
         out = (C.c_int * 8)()
@@ -481,11 +489,9 @@ class Engine:
                                              None if am is None else am.ctypes.data, 1, _stream(stream)))
             self._ran(t0)
             return (out, am) if self.argmax else out
-        if host_in and not isinstance(x, np.ndarray):
-            x = x.numpy()
         if host_in:
-            x = np.ascontiguousarray(x, dtype=_NP[self.input_dtype])
-            xin = x.ctypes.data
+            x = _as_host_tensor(x, self.input_dtype)  # kept alive until the call returns
+            xin = x.data_ptr()
             if out is None:
                 out = np.empty(self.output_shape, _NP[self.output_dtype])
             am = np.empty(self.output_shape[:-1], np.int32) if self.argmax else None
@@ -530,7 +536,10 @@ class Engine:
         by = (C.c_double * cap)()
         self._rc(self._lib.mu_engine_profile(self._h, reps, cap, C.byref(n), kinds, ms, fl, by,
                                              _stream(stream)))
-        return [{"kind": self.OP_KINDS[kinds[i]], "ms": ms[i], "flops": fl[i], "bytes": by[i]}
+        dims = (C.c_int * (4 * cap))()
+        self._rc(self._lib.mu_engine_op_dims(self._h, cap, dims))
+        return [{"kind": self.OP_KINDS[kinds[i]], "ms": ms[i], "flops": fl[i], "bytes": by[i],
+                 "mkn": (dims[4 * i], dims[4 * i + 1], dims[4 * i + 2]), "residual": bool(dims[4 * i + 3])}
                 for i in range(n.value)]
 
     def run_batch(self, inputs, stream=None):
@@ -557,6 +566,24 @@ class Engine:
 def _torch_code(dt) -> int:
     import torch
     return {torch.float32: F32, torch.bfloat16: BF16, torch.int32: I32, torch.float16: 1}.get(dt, -1)
+
+
+def _as_host_tensor(x, code: int):
+    """A contiguous torch CPU tensor holding ``x`` in the engine's input dtype. 16-bit patterns
+    (numpy uint16, torch int16) given for a bfloat16 input are taken as bf16 bits, as everywhere
+    else in this package; any other dtype is converted by value (int64 ids -> int32, float64 ->
+    float32, ...), which is what the reference's prepare_input does with Tensor::to."""
+    import torch
+    want = _torch_dtype(code)
+    if isinstance(x, np.ndarray):
+        if code == BF16 and x.dtype == np.uint16:
+            return torch.from_numpy(np.ascontiguousarray(x).view(np.int16)).view(torch.bfloat16)
+        t = torch.from_numpy(np.ascontiguousarray(x))
+    else:
+        t = x
+    if code == BF16 and t.dtype == torch.int16:
+        return t.contiguous().view(torch.bfloat16)
+    return t.contiguous().to(want)
 
 
 def _torch_dtype(code: int):

@@ -68,9 +68,10 @@ def main():
 
     def host_input():
         x = torch.from_numpy(rng.standard_normal((a.batch, a.input_dim)).astype(np.float32))
-        return x if dtype == mb.F32 else x.bfloat16().view(torch.int16)  # bf16 bits travel as int16
+        return x if dtype == mb.F32 else x.bfloat16()
 
     eng = Engine(compute_dtype=dtype)
+    eng.set_lean_mode(_flag(a.lean_mode))
     eng.set_prepared_input_cache_entries(a.prepared_input_cache_entries)
     eng.set_prepared_input_cache_max_bytes(a.prepared_input_cache_max_bytes)
     t0 = time.perf_counter()

@@ -53,3 +53,27 @@ def test_attention_size_checks_do_not_wrap():
     assert lib.mu_attention_workspace_bytes_composed(2, 3, 40, 16, 0) == 2 * 3 * 40 * 40 * 4
     assert lib.mu_attention_workspace_bytes(2, 16, 1024, 128, 2) == 0   # fused kernel: no workspace
     assert lib.mu_attention_workspace_bytes_composed(2, 16, 1024, 128, 2) == 2 * 16 * 1024 * 1024 * 2
+
+
+def test_host_inputs_are_converted_to_the_compiled_dtype():
+    """What run() and prepare_batch() hand to the engine: values converted to the compiled input
+    dtype (torch.randint's int64 ids, float64 arrays), 16-bit patterns for a bfloat16 input taken
+    as bits."""
+    import torch
+    import oracle
+    from munet_b200.inference import _as_host_tensor
+    from munet_b200 import BF16, F32, I32
+    ids = torch.randint(0, 1000, (2, 5))
+    t = _as_host_tensor(ids, I32)
+    assert t.dtype == torch.int32 and torch.equal(t.long(), ids) and t.is_contiguous()
+    t = _as_host_tensor(np.arange(6, dtype=np.float64).reshape(2, 3) / 3, F32)
+    assert t.dtype == torch.float32 and np.allclose(t.numpy(), np.arange(6).reshape(2, 3) / 3)
+    bits = oracle.to_bf16(np.array([1.0, -2.5, 3.25], np.float32))
+    t = _as_host_tensor(bits, BF16)
+    assert t.dtype == torch.bfloat16 and t.float().tolist() == [1.0, -2.5, 3.25]
+    t = _as_host_tensor(torch.from_numpy(bits.view(np.int16)), BF16)
+    assert t.float().tolist() == [1.0, -2.5, 3.25]
+    t = _as_host_tensor(torch.tensor([1.0, -2.5]), BF16)          # float32 values -> bf16 by value
+    assert t.dtype == torch.bfloat16 and t.float().tolist() == [1.0, -2.5]
+    nc = torch.arange(12, dtype=torch.int32).reshape(3, 4).t()    # non-contiguous view
+    assert _as_host_tensor(nc, I32).is_contiguous()

@@ -313,3 +313,28 @@ def test_float32_artifact_runs_in_bfloat16(ctx, tmp_path, kmode):
         eng.compile((B, T), I32)
         assert_close(eng.run(ids), want, BF16, what=f"fp32 {source} in bf16")
         eng.close()
+
+
+def test_inference_baseline_report(tmp_path):
+    """The replay of the reference's benchmark protocol (tools/inference_baseline.cpp:348-428)
+    runs and prints a report with the reference's sections and keys."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for dtype, lean in (("float32", "0"), ("bfloat16", "1")):
+        r = subprocess.run([sys.executable, "-m", "munet_b200.inference_baseline", "--dtype", dtype,
+                            "--single-run-iters", "5", "--batch-run-iters", "2", "--warmup-runs", "1",
+                            "--preallocate-batch-inputs", "1", "--lean-mode", lean],
+                           cwd=root, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr
+        rep = json.loads(r.stdout)
+        for section in ("memory_policy", "shape_contract", "cold_load", "compile", "steady_single_run",
+                        "steady_batch_run", "memory_bytes"):
+            assert section in rep
+        assert rep["lean_mode"] == (lean == "1") and rep["dtype"] == dtype
+        assert rep["shape_contract"]["compiled_input_shape"] == [32, 256]
+        assert rep["shape_contract"]["compiled_output_shape"] == [32, 128]
+        assert rep["steady_single_run"]["avg_wall_ms"] > 0 and rep["steady_batch_run"]["avg_per_input_wall_ms"] > 0
+        assert rep["memory_bytes"]["prepared_input_cache_hits"] >= 2 * 4  # prepared inputs were reused

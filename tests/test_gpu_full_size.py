@@ -34,13 +34,19 @@ def decoder_weights(rng, V, T, d, L):
     return ps
 
 
-# Depth drift of a bf16 decoder, measured on the CPU alone with `python -m oracle.drift_floor`
-# (the checker against itself, float instead of double accumulation and nothing else changed;
-# d2048 h16 V32000, 48 tokens): worst element / elementwise bound = 1.9-2.0 at 6 layers and
-# 2.8-3.9 at 24 layers, rel-inf 1.0 % / 1.6-1.8 %, rel-rms 0.9 % / 1.6 %. No tensor-core kernel can
-# sit below that floor, so at depth the elementwise bound is asserted as floor x 1.5 and the two
-# norm-wise figures against the 2e-2 tolerance itself.
-DEPTH_WORST_CAP = {6: 2.0 * 1.5, 24: 3.9 * 1.5}
+# Depth drift of a bf16 decoder, measured on the CPU alone (`python -m oracle.drift_floor`: the
+# checker against itself with float instead of double accumulation in the contractions and
+# NOTHING else changed — what every tensor-core kernel does). Worst element / elementwise bound:
+#   1 layer  d2048, 2 x 1024 tokens, literal K   1.33      (rel-inf 0.6 %, rel-rms 0.4 %)
+#   2 layers d512 256 tokens / d2048 64 tokens   1.1-1.4   (0.7 %, 0.5-0.6 %)
+#   6 layers d512 256 tokens / d2048 48 tokens   1.8-2.0   (0.9-1.0 %, 0.8-0.9 %)
+#   24 layers d2048 48 tokens                    3.3-3.4   (1.5-1.65 %, 1.45 %)
+# The elementwise 2e-2 bound is therefore out of reach of any kernel that accumulates in float
+# from the first layer on; rounding unnormalised instead of normalised probabilities adds 0.2-0.3
+# at one or two layers and nothing measurable at 24 (3.35-3.5 with both changes). At depth the
+# tests assert the measured floor x 1.5 elementwise, and the two norm-wise figures against the
+# 2e-2 tolerance itself.
+DEPTH_WORST_CAP = {1: 1.33 * 1.5, 2: 1.36 * 1.5, 6: 2.0 * 1.5, 24: 3.4 * 1.5}
 
 
 @pytest.mark.parametrize("name,V,T,d,H,L,B,prefixes", [
@@ -78,6 +84,7 @@ def test_full_config_prefix_parity_math_mode(name, V, T, d, H, L, B, prefixes):
         rel_rms = float(np.sqrt(np.mean((g - w_) ** 2)) / np.sqrt(np.mean(w_ ** 2)))
         assert rel <= 2e-2 and rel_rms <= 2e-2 and worst <= DEPTH_WORST_CAP[L], \
             f"{name} seq {b}: worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}"
+        print(f"{name} seq {b} prefix {prefix}: worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}")
         agree = float((oracle.port().argmax(got, BF16) == oracle.port().argmax(want, BF16)).mean())
         assert agree >= 0.9, f"{name} seq {b}: argmax agreement {agree}"
     # shard invariance (math mode): sequences 0 and B-1 run alone give bit-identical logits
@@ -111,8 +118,8 @@ def test_gpt_s_literal_mode_full_batch_geometry():
     ok, worst, rel = close(got, want, BF16, rtol=2e-2)
     g, w_ = oracle.from_bf16(got).astype(np.float64), oracle.from_bf16(want).astype(np.float64)
     rel_rms = float(np.sqrt(np.mean((g - w_) ** 2)) / np.sqrt(np.mean(w_ ** 2)))
-    # same full-size criteria as above (measured: worst element 1.6x the small-shape bound)
-    assert rel <= 2e-2 and rel_rms <= 2e-2 and worst <= 5.0, \
+    # same criteria as above: norm-wise errors within 2e-2, elementwise within the 2-layer floor x 1.5
+    assert rel <= 2e-2 and rel_rms <= 2e-2 and worst <= DEPTH_WORST_CAP[L], \
         f"worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}"
     eng.close()
     ctx.close()
@@ -123,7 +130,9 @@ def test_gpt_l_literal_mode_headline_geometry():
     of 128, d_model 2048, 1024 positions (eight key tiles per row) and the 32000-wide head. The
     checker needs the whole batch (a literal score reads K rows of every head and sequence), so
     depth is cut to one layer and the batch to two sequences; every kernel runs at the config's
-    per-layer shape. One layer deep, the elementwise 2e-2 bound itself is asserted."""
+    per-layer shape. The checker with float accumulation alone is 1.33x the elementwise bound from
+    itself on exactly this input, so the elementwise figure is asserted at that floor x 1.5 and the
+    norm-wise ones at the 2e-2 tolerance."""
     import munet_b200 as mb
     from munet_b200.inference import Engine, gpt_decoder_config, gpt_param_names
     V, T, d, H, L, B = 32000, 1024, 2048, 16, 1, 2
@@ -139,7 +148,9 @@ def test_gpt_l_literal_mode_headline_geometry():
     ok, worst, rel = close(got, want, BF16, rtol=2e-2)
     g, w_ = oracle.from_bf16(got).astype(np.float64), oracle.from_bf16(want).astype(np.float64)
     rel_rms = float(np.sqrt(np.mean((g - w_) ** 2)) / np.sqrt(np.mean(w_ ** 2)))
-    assert ok, f"worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}"
+    assert rel <= 2e-2 and rel_rms <= 2e-2 and worst <= DEPTH_WORST_CAP[L], \
+        f"worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}"
+    print(f"gpt_l literal L=1 B=2: worst err/bound {worst:.3g}, rel-inf {rel:.3g}, rel-rms {rel_rms:.3g}")
     assert np.array_equal(am, oracle.port().argmax(got, BF16))
     agree = float((am == oracle.port().argmax(want, BF16)).mean())
     assert agree >= 0.9, f"argmax agreement {agree}"
