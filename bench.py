@@ -698,6 +698,7 @@ def run_kernel_case(argv):
     ap.add_argument("--relu", action="store_true")
     ap.add_argument("--pool", type=int, default=0)
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--gemm-tile", default="", help="BN,CTAS: fix the bf16 GEMM tile (e.g. 128,2); default automatic")
     a = ap.parse_args(argv)
 
     def timed(fn, reps):
@@ -713,6 +714,9 @@ def run_kernel_case(argv):
         return e0.elapsed_time(e1) / reps
 
     ctx = mb.Context(0)
+    if a.gemm_tile:
+        bn, ct = (int(v) for v in a.gemm_tile.split(","))
+        ctx.set_gemm_tile(bn, ct)
     bf = dict(dtype=torch.bfloat16, device="cuda")
     if a.kernel in ("linear", "linear_f32"):
         M, K, N = a.dims

@@ -73,6 +73,11 @@ int mu_ctx_force_simt(mu_ctx *ctx, int on);
 /* Persistent GEMM kernels launch one CTA per SM; n > 0 limits them to n SMs so that a kernel
  * running beside them (a collective on another stream) finds free SMs. 0 = all SMs. */
 int mu_ctx_set_sm_budget(mu_ctx *ctx, int n);
+/* Tuning knob: the bf16 tensor-core GEMM picks its tile (128 x 64/128/256 on one CTA, 256 x 128/256
+ * on a CTA pair) from the problem size and the SM count; bn > 0 fixes the tile width and `ctas`
+ * (1 or 2) the CTA count for every later GEMM of this context. 0, 0 restores the automatic choice.
+ * Results do not depend on the tile shape (same accumulation order per output element). */
+int mu_ctx_set_gemm_tile(mu_ctx *ctx, int bn, int ctas);
 int mu_alloc(mu_ctx *ctx, size_t bytes, void **ptr);
 int mu_free(mu_ctx *ctx, void *ptr);
 int mu_copy(mu_ctx *ctx, void *dst, const void *src, size_t bytes, int kind, void *stream);

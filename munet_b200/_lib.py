@@ -42,6 +42,7 @@ SIGNATURES = {
     "mu_ctx_num_sms": (_i, [_vp]),
     "mu_ctx_force_simt": (_i, [_vp, _i]),
     "mu_ctx_set_sm_budget": (_i, [_vp, _i]),
+    "mu_ctx_set_gemm_tile": (_i, [_vp, _i, _i]),
     "mu_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "mu_free": (_i, [_vp, _vp]),
     "mu_copy": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
@@ -191,6 +192,10 @@ class Context:
     def set_sm_budget(self, n: int):
         """Limit persistent GEMM grids to ``n`` SMs (0 = all): room for a kernel running beside them."""
         self._rc(self._lib.mu_ctx_set_sm_budget(self._h, int(n)))
+
+    def set_gemm_tile(self, bn: int = 0, ctas: int = 0):
+        """Fix the bf16 GEMM tile (width 64/128/256, 1 or 2 CTAs); 0, 0 = automatic."""
+        self._rc(self._lib.mu_ctx_set_gemm_tile(self._h, int(bn), int(ctas)))
 
     def check(self, stream=None):
         """Synchronise the stream and raise if a kernel latched a device-side error."""

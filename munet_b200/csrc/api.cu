@@ -36,6 +36,7 @@ struct mu_ctx {
   int num_sms = 0;
   int force_simt = 0;
   int sm_budget = 0; // > 0: persistent GEMM grids use at most this many SMs
+  int gemm_bn = 0, gemm_ctas = 0; // > 0: tile shape forced by mu_ctx_set_gemm_tile
   int *d_status = nullptr;
   char err[512] = {0};
 };
@@ -88,8 +89,10 @@ int run_gemm(mu_ctx *ctx, const mu::GemmOperands &op, const mu::GemmShape &sh, m
     return fail(ctx, MU_ERR_CUDA, "%s: cannot select device %d", who, ctx->device);
   if (dtype == MU_BF16 && !ctx->force_simt && sh.K > 0) {
     ep.vec_ok = epilogue_vec_ok(ep) ? 1 : 0;
+    mu::GemmShape shf = sh;
+    shf.force_bn = ctx->gemm_bn, shf.force_ctas = ctx->gemm_ctas;
     const int sms = (ctx->sm_budget > 0 && ctx->sm_budget < ctx->num_sms) ? ctx->sm_budget : ctx->num_sms;
-    int rc = mu::launch_gemm_bf16_tcgen05(op, sh, ep, ctx->d_status, sms, st);
+    int rc = mu::launch_gemm_bf16_tcgen05(op, shf, ep, ctx->d_status, sms, st);
     if (rc == 0)
       return MU_OK;
     if (rc == 2)
@@ -213,6 +216,16 @@ int mu_ctx_set_sm_budget(mu_ctx *ctx, int n) {
   if (!ctx || n < 0)
     return MU_ERR_INVALID;
   ctx->sm_budget = n;
+  return MU_OK;
+}
+int mu_ctx_set_gemm_tile(mu_ctx *ctx, int bn, int ctas) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  const bool ok = (bn == 0 && ctas == 0) || ((bn == 64 || bn == 128 || bn == 256) && (ctas == 1 || ctas == 2) &&
+                                             !(ctas == 2 && bn == 64));
+  if (!ok)
+    return fail(ctx, MU_ERR_INVALID, "gemm tile: width 64/128/256 on 1 CTA, 128/256 on 2; 0,0 = automatic");
+  ctx->gemm_bn = bn, ctx->gemm_ctas = ctas;
   return MU_OK;
 }
 int mu_ctx_force_simt(mu_ctx *ctx, int on) {

@@ -55,6 +55,8 @@ struct AttParams {
   int causal;
   float scale;   // 1/sqrt(D) as float
   int n_qtiles;
+  int chunk_heads; // heads whose K and V are worked on together (sized to stay in L2)
+  int chunk_rot;   // rotation of the CTA deal from one chunk to the next
 };
 
 template <int D, bool LITERAL>
@@ -100,29 +102,48 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(q_empty + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Persistent CTA: it walks "items" blockIdx.x, blockIdx.x + gridDim.x, ...; an item is one
-  // head with a PAIR of query tiles (p-th from the end, then p-th from the start), so that under
-  // the causal mask every item has the same number of key tiles (n_qtiles + 1) and the CTAs stay
-  // balanced. Consecutive items are the pairs of one head: CTAs running side by side share its
-  // K/V through L2. All three roles enumerate the same sequence with this helper; pipeline
-  // counters (key tiles, works) run on across works so loads and Q·K' of the next work overlap
-  // the epilogue of the current one.
-  const int n_pairs = (prm.n_qtiles + 1) / 2;
-  const long long n_items = 1ll * prm.BH * n_pairs;
+  // Persistent CTA: every role walks the same static sequence of works (one head, one tile of 128
+  // queries), produced by `next_work`. Under the causal mask a query tile qt sees qt + 1 key
+  // tiles, so works differ in size by up to n_qtiles x. Heads are taken in chunks of `chunk_heads`
+  // (their K and V stay in L2 while the chunk is worked on); inside a chunk the works are ordered
+  // by falling size — all heads' last query tile first — and dealt to the CTAs in a serpentine
+  // (pass 0: CTA 0..n-1, pass 1: n-1..0, ...), which pairs every large work with a small one;
+  // from chunk to chunk the deal is rotated so that the leftovers of a partial last pass fall on
+  // different CTAs. At 128 heads of 8 tiles that is 32 key tiles on the busiest of 148 CTAs where
+  // head-by-head pairs of (heavy, light) tiles gave 36; larger batches end within a tile of even.
+  // Pipeline counters (key tiles, works) run on across works so loads and Q.K' of the next work
+  // overlap the epilogue of the current one.
   struct Work {
     int bh, q0, nk;
   };
-  auto get_work = [&](long long item, int second, Work &wk) -> bool {
-    const int pr = static_cast<int>(item % n_pairs);
-    const int heavy = prm.n_qtiles - 1 - pr;
-    if (second && pr == heavy)
-      return false; // middle tile of an odd count: it has no partner
-    const int qt = second ? pr : heavy;
-    wk.bh = static_cast<int>(item / n_pairs);
-    wk.q0 = qt * BQ;
-    const int kv_len = prm.causal ? min(prm.T, wk.q0 + BQ) : prm.T;
-    wk.nk = (kv_len + BKV - 1) / BKV;
-    return true;
+  struct WorkIter {
+    int chunk, pass;
+  };
+  const int n_cta = static_cast<int>(gridDim.x);
+  auto next_work = [&](WorkIter &it, Work &wk) -> bool {
+    for (;;) {
+      const int h0 = it.chunk * prm.chunk_heads;
+      if (h0 >= prm.BH)
+        return false;
+      const int hb = min(prm.chunk_heads, prm.BH - h0);
+      const long long n_works = 1ll * hb * prm.n_qtiles;
+      if (1ll * it.pass * n_cta >= n_works) {
+        ++it.chunk, it.pass = 0;
+        continue;
+      }
+      const int c = static_cast<int>((blockIdx.x + 1ll * it.chunk * prm.chunk_rot) % n_cta);
+      const int slot = (it.pass & 1) ? n_cta - 1 - c : c;
+      const long long p = 1ll * it.pass * n_cta + slot;
+      ++it.pass;
+      if (p >= n_works)
+        continue; // this CTA sits out the partial last pass of the chunk
+      const int qt = prm.n_qtiles - 1 - static_cast<int>(p / hb);
+      wk.bh = h0 + static_cast<int>(p % hb);
+      wk.q0 = qt * BQ;
+      const int kv_len = prm.causal ? min(prm.T, wk.q0 + BQ) : prm.T;
+      wk.nk = (kv_len + BKV - 1) / BKV;
+      return true;
+    }
   };
 
   if (threadIdx.x == 0) {
@@ -166,11 +187,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
     if (lane == 0) {
       bool ok = true;
       uint32_t kt = 0, w = 0; // key tiles and works issued so far
-      for (long long item = blockIdx.x; item < n_items && ok; item += gridDim.x)
-        for (int second = 0; second < 2 && ok; ++second) {
-          Work wk;
-          if (!get_work(item, second, wk))
-            continue;
+      WorkIter wit = {0, 0};
+      for (Work wk; ok && next_work(wit, wk);) {
           // Q is single-buffered: the last Q·K' of the previous work must have read it
           if (!mbar_wait(q_empty, (w & 1) ^ 1)) {
             atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
@@ -259,11 +277,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         umma_commit(&v_empty[i % STAGES]);
         return true;
       };
-      for (long long item = blockIdx.x; item < n_items && ok; item += gridDim.x)
-        for (int second = 0; second < 2 && ok; ++second) {
-          Work wk;
-          if (!get_work(item, second, wk))
-            continue;
+      WorkIter wit = {0, 0};
+      for (Work wk; ok && next_work(wit, wk);) {
           if (!mbar_wait(q_full, w & 1)) {
             atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
             ok = false;
@@ -387,11 +402,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
       tc_fence_before();
     };
 
-    for (long long item = blockIdx.x; item < n_items && ok; item += gridDim.x)
-    for (int second = 0; second < 2 && ok; ++second) {
-    Work wk;
-    if (!get_work(item, second, wk))
-      continue;
+    WorkIter wit = {0, 0};
+    for (Work wk; ok && next_work(wit, wk);) {
     const int q0 = wk.q0, nk = wk.nk, bh = wk.bh;
     const int qrow = q0 + row; // position in the sequence
     // m_ref is the maximum the exponents are taken against. It follows the running maximum
@@ -670,13 +682,20 @@ int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *
   prm.T = T, prm.H = H, prm.BH = static_cast<int>(BH), prm.causal = causal;
   prm.scale = 1.0f / sqrtf(static_cast<float>(D));
   prm.n_qtiles = (T + BQ - 1) / BQ;
+  {
+    // K and V of one head are 4*T*D bytes; a chunk of heads is kept to about 64 MB, half of L2
+    const unsigned long long per_head = 4ull * uT * uD;
+    unsigned long long g = (64ull << 20) / per_head;
+    prm.chunk_heads = static_cast<int>(g < 1 ? 1 : (g > BH ? BH : g));
+    prm.chunk_rot = 53;
+  }
   // one persistent CTA per SM (the kernel's shared memory allows no more), fewer for small jobs
   int dev = 0, num_sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
       cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
     return 2;
-  const unsigned long long n_items = BH * ((prm.n_qtiles + 1) / 2);
-  dim3 grid(static_cast<unsigned>(n_items < static_cast<unsigned long long>(num_sms) ? n_items : num_sms));
+  const unsigned long long n_works = BH * prm.n_qtiles;
+  dim3 grid(static_cast<unsigned>(n_works < static_cast<unsigned long long>(num_sms) ? n_works : num_sms));
 
 #define MU_ATT_LAUNCH(D_, L_)                                                                    \
   do {                                                                                           \

@@ -42,6 +42,8 @@ struct GemmShape {
   // Tile order: panels of `panel_n` column tiles are swept over all row tiles before the next
   // panel starts, so a panel of B stays in L2 while A streams past it (0 = one panel).
   int panel_n = 0;
+  // > 0: use this tile width (64, 128, 256) and CTA count (1, 2) instead of the automatic choice
+  int force_bn = 0, force_ctas = 0;
 };
 
 // Operand addressing in elements. A is row-major [M,K]. B is row-major [K,N]

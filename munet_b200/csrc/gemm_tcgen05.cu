@@ -38,7 +38,7 @@ template <int BN, int CTAS = 1> struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = (BN / CTAS) * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = CTAS == 2 ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int STAGES = CTAS == 2 ? (BN == 256 ? 6 : 8) : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
   static constexpr int TMEM_COLS = 2 * BN;
   // epilogue staging: one [32 rows x 64 cols] bf16 box (128-byte rows) per epilogue warp
   static constexpr int OUT_BOX_BYTES = 32 * 128;
@@ -151,7 +151,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          int *status) {
   using Cfg = GemmCfg<BN, CTAS>;
   constexpr int STAGES = Cfg::STAGES;
-  static_assert(CTAS == 1 || (CTAS == 2 && BN == 256), "CTA pairs are built for 256-column tiles");
+  static_assert(CTAS == 1 || (CTAS == 2 && (BN == 256 || BN == 128)), "CTA pairs: 256 x 256 or 256 x 128 tiles");
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atoms.
   uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -648,11 +648,32 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
   const unsigned long long a_nb = s2.a_batched ? sh.batch : 1;
   const unsigned long long b_nb = s2.b_batched ? sh.batch : 1;
   const unsigned long long a_bs = s2.a_batched ? op.a_batch : 1ull * op.lda * sh.M;
-  const int BN = sh.N > 128 ? 256 : (sh.N > 64 ? 128 : 64);
-  // CTA pairs (256 x 256 tiles) for the large, tile-rich problems
+  // Tile shape: 128 x {64,128,256} on single CTAs, 256 x {128,256} on CTA pairs. The persistent
+  // grid runs ceil(tiles / slots) waves; a shape whose last wave is nearly empty loses up to a
+  // whole wave (M = 8192, N = 2048 is 3.46 waves of 256 x 256 pair tiles but 6.92 of 256 x 128),
+  // so the candidate with the smallest waves x tile area / relative tile speed wins. The speeds
+  // are measured ratios on the decoder's shapes (pairs stage a third less operand data per FLOP).
+  int BN = sh.N > 128 ? 256 : (sh.N > 64 ? 128 : 64);
+  int CT = 1;
+  if (sh.force_bn > 0) {
+    BN = sh.force_bn, CT = sh.force_ctas == 2 ? 2 : 1;
+  } else if (sh.N > 64) {
+    struct Cand { int bn, ct; double speed; };
+    const Cand cands[4] = {{256, 2, 1.00}, {128, 2, 0.93}, {256, 1, 0.91}, {128, 1, 0.82}};
+    double best = 0;
+    for (const Cand &c : cands) {
+      if (c.bn == 256 && sh.N <= 128) continue;
+      if (c.ct == 2 && (sh.M < 1024 || num_sms < 2)) continue;
+      const long long t = 1ll * ((sh.M + BM * c.ct - 1) / (BM * c.ct)) * ((sh.N + c.bn - 1) / c.bn) * sh.batch;
+      const long long slots = c.ct == 2 ? num_sms / 2 : num_sms;
+      if (c.ct == 2 && t < slots) continue; // too few pair tiles to fill the device
+      const double waves = static_cast<double>((t + slots - 1) / slots);
+      const double cost = waves * (BM * c.ct) * c.bn / c.speed / c.ct; // per-SM time units
+      if (best == 0 || cost < best) best = cost, BN = c.bn, CT = c.ct;
+    }
+  }
+  const bool pairs = CT == 2;
   const long long pair_tiles = 1ll * ((sh.M + 2 * BM - 1) / (2 * BM)) * ((sh.N + BN - 1) / BN) * sh.batch;
-  const bool pairs = BN == 256 && sh.M >= 1024 && num_sms >= 2 && pair_tiles >= num_sms / 2;
-  const int CT = pairs ? 2 : 1;
   // B wider than a third of L2 is cut into panels of about 32 MB (see decode_tile)
   {
     const double b_bytes = 2.0 * sh.K * sh.N;
@@ -700,10 +721,10 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
   } while (0)
 
   // CTA pairs: clusters of two, as many as the device can hold at once (persistent).
-#define MU_LAUNCH_PAIR(KM_)                                                                      \
+#define MU_LAUNCH_PAIR(BN_, KM_)                                                                 \
   do {                                                                                           \
-    auto kern = gemm_bf16_tcgen05_kernel<256, KM_, 2>;                                           \
-    constexpr int smem = GemmCfg<256, 2>::SMEM_BYTES;                                            \
+    auto kern = gemm_bf16_tcgen05_kernel<BN_, KM_, 2>;                                           \
+    constexpr int smem = GemmCfg<BN_, 2>::SMEM_BYTES;                                            \
     static PerDeviceOnce cluster_cache;                                                          \
     int max_clusters = cluster_cache.get();                                                      \
     cudaLaunchConfig_t cfg = {};                                                                 \
@@ -736,10 +757,17 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
   } while (0)
 
   if (pairs) {
-    if (op.b_kmajor)
-      MU_LAUNCH_PAIR(true);
-    else
-      MU_LAUNCH_PAIR(false);
+    if (BN == 256) {
+      if (op.b_kmajor)
+        MU_LAUNCH_PAIR(256, true);
+      else
+        MU_LAUNCH_PAIR(256, false);
+    } else {
+      if (op.b_kmajor)
+        MU_LAUNCH_PAIR(128, true);
+      else
+        MU_LAUNCH_PAIR(128, false);
+    }
     return cudaGetLastError() == cudaSuccess ? 0 : 2;
   }
 

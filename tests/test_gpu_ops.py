@@ -498,3 +498,28 @@ def test_kernel_timer_brackets_device_time(ctx):
         times.append(ctx.timer_last_us())
         ctx.check()
     assert 0.0 < times[0] < times[1]
+
+
+@pytest.mark.parametrize("M,K,N", [(2304, 320, 1100), (8192, 256, 2048)])
+def test_linear_bf16_every_tile_shape_gives_the_same_bits(ctx, M, K, N):
+    """The GEMM picks its tile from the problem size (128 x 64/128/256 on one CTA, 256 x 128/256 on
+    a CTA pair). Every shape sums each output element in the same order, so forcing each of them
+    must reproduce the automatic choice bit for bit — ragged edges, bias, GELU and residual
+    included — and that result must match the checker."""
+    rng = np.random.default_rng(M + N)
+    x, w = rnd(rng, (M, K), BF16), rnd(rng, (K, N), BF16, 1.0 / np.sqrt(K))
+    b, r = rnd(rng, (N,), BF16, 0.05), rnd(rng, (M, N), BF16)
+    auto = dev_linear(ctx, x, w, b, BF16, "gelu", res=r)
+    rows = [0, 127, 128, 255, 256, M // 2, M - 129, M - 1]
+    P = oracle.port()
+    assert_close(auto[rows], P.add(P.linear(x[rows], w, b, BF16, "gelu"), r[rows], BF16), BF16, what="auto tile")
+    try:
+        for bn, ctas in ((64, 1), (128, 1), (256, 1), (128, 2), (256, 2)):
+            ctx.set_gemm_tile(bn, ctas)
+            got = dev_linear(ctx, x, w, b, BF16, "gelu", res=r)
+            assert np.array_equal(got, auto), f"tile {bn} x {ctas} CTA differs from the automatic choice"
+    finally:
+        ctx.set_gemm_tile(0, 0)
+    import munet_b200 as mb
+    with pytest.raises(mb.MuNetError):
+        ctx.set_gemm_tile(64, 2)
