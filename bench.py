@@ -699,6 +699,8 @@ def run_kernel_case(argv):
     ap.add_argument("--pool", type=int, default=0)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--gemm-tile", default="", help="BN,CTAS: fix the bf16 GEMM tile (e.g. 128,2); default automatic")
+    ap.add_argument("--att-variant", type=int, default=0,
+                    help="fused attention kernel: 0 two query tiles per CTA (default), 1 one tile per CTA")
     a = ap.parse_args(argv)
 
     def timed(fn, reps):
@@ -714,6 +716,8 @@ def run_kernel_case(argv):
         return e0.elapsed_time(e1) / reps
 
     ctx = mb.Context(0)
+    if a.att_variant:
+        mb.lib().mu_debug_attention_variant(a.att_variant)
     if a.gemm_tile:
         bn, ct = (int(v) for v in a.gemm_tile.split(","))
         ctx.set_gemm_tile(bn, ct)

@@ -29,6 +29,7 @@ int launch_gemm_tf32x3(const float *, long long, const float *, long long, int, 
                        cudaStream_t);
 int launch_attention_tcgen05(const void *, const void *, const void *, void *, int, int, int, int,
                              int, int, int *, cudaStream_t);
+void set_attention_variant(int);
 } // namespace mu
 
 struct mu_ctx {
@@ -228,6 +229,9 @@ int mu_ctx_set_gemm_tile(mu_ctx *ctx, int bn, int ctas) {
   ctx->gemm_bn = bn, ctx->gemm_ctas = ctas;
   return MU_OK;
 }
+// Not part of the declared ABI: selects the fused attention kernel (0 two query tiles per CTA,
+// 1 one tile per CTA) for timing one against the other. Process-wide.
+void mu_debug_attention_variant(int v) { mu::set_attention_variant(v); }
 int mu_ctx_force_simt(mu_ctx *ctx, int on) {
   if (!ctx)
     return MU_ERR_INVALID;

@@ -181,6 +181,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;
+  // Head size 64 leaves 128 tensor-memory columns free: the probabilities go there (two buffers of
+  // 64 packed columns) and P.V takes its A operand from tensor memory instead of shared memory.
+  constexpr bool P_TMEM = (D == 64);
+  const uint32_t tmem_P = tmem_base + 384;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -271,7 +275,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         for (int k = 0; k < BKV / 16; ++k) {
           const uint64_t ad = make_smem_desc(p_addr + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
           const uint64_t bd = make_smem_desc(v_addr + (k / 4) * (DB * 8192) + (k % 4) * 2048, 8192, 1024);
-          umma_f16(tmem_O + ob * D, ad, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+          if constexpr (P_TMEM)
+            umma_f16_ts(tmem_O + ob * D, tmem_P + b * (BKV / 2) + k * 8, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+          else
+            umma_f16(tmem_O + ob * D, ad, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
         }
         umma_commit(&o_done[b]);
         umma_commit(&v_empty[i % STAGES]);
@@ -521,6 +528,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
           sum1 += p1;
           pk[k] = pack_bf16x2(p0, p1);
         }
+        if constexpr (P_TMEM) {
+          tmem_st_32x16(tmem_P + lane_sel + b * (BKV / 2) + half * (SC / 2) + c * 16, pk);
+          continue;
+        }
         // 32 columns = four 16-byte chunks of one 64-column box of the P tile
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
@@ -530,8 +541,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
               make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
         }
       }
+      if constexpr (P_TMEM)
+        tmem_st_wait();
       tc_fence_before();
-      fence_proxy_async();
+      if constexpr (!P_TMEM)
+        fence_proxy_async();
       __syncwarp();
       if (lane == 0)
         mbar_arrive(&p_full[b]);
@@ -599,6 +613,508 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
 }
 
 // ---------------------------------------------------------------------------
+// Two query tiles per CTA (the main kernel for D = 64 and 128)
+// ---------------------------------------------------------------------------
+// The kernel above keeps one query tile per CTA in flight and two threads per query row; its
+// softmax warps are a chain of dependent steps per key tile (tensor-memory load, row-maximum
+// exchange through shared memory, exponentials, probabilities to swizzled shared memory, proxy
+// fence) that the tensor pipe waits on: 24 % busy. This kernel changes the three things that
+// chain is made of:
+//   * a work is one head with TWO adjacent query tiles, A and B, which share every K and V
+//     tile; warps 2-5 run the softmax of A, warps 6-9 that of B, one thread per query row (its
+//     TMEM lane), so the row maximum and the row sum never leave the thread;
+//   * while the softmax of A runs, the tensor pipe works on B (P_B·V, Q_B·K' of the next tile)
+//     and the other way round;
+//   * the probabilities are written back to tensor memory over the score tile they came from
+//     (64 packed columns) and P·V takes its A operand from tensor memory: no shared-memory
+//     round trip, no proxy fence. MMAs of one CTA run in issue order, so Q·K' of the next key
+//     tile, issued after P·V, cannot overwrite probabilities that are still being read.
+// Tensor memory: S_A | S_B (128 columns each) | O_A | O_B (D columns each).
+// Shared memory: Q_A, Q_B, a K ring and a V ring, one output staging tile.
+template <int D> struct Att2Cfg {
+  static constexpr int Q_BYTES = BQ * D * 2; // one query tile
+  static constexpr int K_BYTES = BKV * D * 2;
+  static constexpr int V_BYTES = BKV * D * 2;
+  static constexpr int KS = D == 128 ? 2 : 4; // stages of the K ring
+  static constexpr int VS = D == 128 ? 2 : 4; // stages of the V ring
+  static constexpr int STG_BYTES = BQ * D * 2; // output staging, shared by A and B in turn
+  static constexpr int SMEM_BYTES = 2 * Q_BYTES + KS * K_BYTES + VS * V_BYTES + STG_BYTES + 1024;
+  static constexpr int TMEM_COLS = 512;
+};
+
+template <int D, bool LITERAL>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attention2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
+                          const __grid_constant__ CUtensorMap tmK,
+                          const __grid_constant__ CUtensorMap tmV,
+                          const __grid_constant__ CUtensorMap tmO, AttParams prm, int *status) {
+  using Cfg = Att2Cfg<D>;
+  constexpr int KS = Cfg::KS, VS = Cfg::VS;
+  constexpr int DB = D / 64;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw;
+  if (smem_u32(smem_raw) & 1023u) {
+    if (threadIdx.x == 0)
+      atomicCAS(status, 0, MU_DEV_BAD_INDEX);
+    return;
+  }
+  uint8_t *sQ = smem;                         // [2][Q_BYTES]
+  uint8_t *sK = sQ + 2 * Cfg::Q_BYTES;        // [KS][K_BYTES]
+  uint8_t *sV = sK + KS * Cfg::K_BYTES;       // [VS][V_BYTES]
+  uint8_t *sStg = sV + VS * Cfg::V_BYTES;     // [STG_BYTES]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(sStg + Cfg::STG_BYTES);
+  uint64_t *q_full = bars;            // [2]
+  uint64_t *q_empty = q_full + 2;     // [2]
+  uint64_t *k_full = q_empty + 2;     // [KS]
+  uint64_t *k_empty = k_full + KS;    // [KS]
+  uint64_t *v_full = k_empty + KS;    // [VS]
+  uint64_t *v_empty = v_full + VS;    // [VS]
+  uint64_t *s_full = v_empty + VS;    // [2] scores of A / B complete (and every MMA before them)
+  uint64_t *p_full = s_full + 2;      // [2] probabilities of A / B are in tensor memory
+  uint64_t *o_full = p_full + 2;      // [2] last P·V of the work has completed
+  uint64_t *o_free = o_full + 2;      // [2] the softmax warps have read O of the work
+  uint64_t *stg_done = o_free + 2;    // [1] an output tile has left the staging buffer
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(stg_done + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_cta = static_cast<int>(gridDim.x);
+  const int n_pairs = (prm.n_qtiles + 1) / 2;
+  const int nkv = (prm.T + BKV - 1) / BKV;
+
+  // A work = (head, pair of query tiles 2*pr, 2*pr+1). Same deal as above: heads in chunks that
+  // fit L2, pairs by falling size, serpentine over the CTAs, rotated from chunk to chunk.
+  struct Work {
+    int bh, qa, nk_a, nk_b; // first row of tile A, key tiles of A and of B (0: no tile B)
+  };
+  struct WorkIter {
+    int chunk, pass;
+  };
+  auto next_work = [&](WorkIter &it, Work &wk) -> bool {
+    for (;;) {
+      const int h0 = it.chunk * prm.chunk_heads;
+      if (h0 >= prm.BH)
+        return false;
+      const int hb = min(prm.chunk_heads, prm.BH - h0);
+      const long long n_works = 1ll * hb * n_pairs;
+      if (1ll * it.pass * n_cta >= n_works) {
+        ++it.chunk, it.pass = 0;
+        continue;
+      }
+      const int c = static_cast<int>((blockIdx.x + 1ll * it.chunk * prm.chunk_rot) % n_cta);
+      const int slot = (it.pass & 1) ? n_cta - 1 - c : c;
+      const long long p = 1ll * it.pass * n_cta + slot;
+      ++it.pass;
+      if (p >= n_works)
+        continue;
+      const int pr = n_pairs - 1 - static_cast<int>(p / hb);
+      wk.bh = h0 + static_cast<int>(p % hb);
+      wk.qa = 2 * pr * BQ;
+      const bool has_b = 2 * pr + 1 < prm.n_qtiles;
+      wk.nk_a = prm.causal ? min(nkv, 2 * pr + 1) : nkv;
+      wk.nk_b = has_b ? (prm.causal ? min(nkv, 2 * pr + 2) : nkv) : 0;
+      return true;
+    }
+  };
+
+  if (threadIdx.x == 0) {
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(&q_full[x], 1);
+      mbar_init(&q_empty[x], 1);
+      mbar_init(&s_full[x], 1);
+      mbar_init(&p_full[x], 4);
+      mbar_init(&o_full[x], 1);
+      mbar_init(&o_free[x], 4);
+    }
+    for (int s = 0; s < KS; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < VS; ++s) {
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    mbar_init(stg_done, 4);
+    fence_barrier_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t kt = 0, vt = 0;     // K / V tiles issued so far
+      uint32_t wq[2] = {0, 0};     // works that had a tile A / B so far
+      WorkIter wit = {0, 0};
+      for (Work wk; ok && next_work(wit, wk);) {
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (x == 1 && wk.nk_b == 0)
+            break;
+          // Q_x is single-buffered: the last Q·K' of the previous work must have read it
+          if (!mbar_wait(&q_empty[x], (wq[x] & 1) ^ 1)) {
+            atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&q_full[x], Cfg::Q_BYTES);
+#pragma unroll
+          for (int db = 0; db < DB; ++db)
+            tma_load_3d(sQ + x * Cfg::Q_BYTES + db * (BQ * 128), &tmQ, &q_full[x], db * 64,
+                        wk.qa + x * BQ, wk.bh);
+          ++wq[x];
+        }
+        const int nk = max(wk.nk_a, wk.nk_b);
+        for (int j = 0; j < nk && ok; ++j) {
+          const int k0 = j * BKV;
+          {
+            const int stage = kt % KS;
+            if (!mbar_wait(&k_empty[stage], ((kt / KS) & 1) ^ 1)) {
+              atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
+              ok = false;
+              break;
+            }
+            uint8_t *dst = sK + stage * Cfg::K_BYTES;
+            mbar_arrive_expect_tx(&k_full[stage], Cfg::K_BYTES);
+            if (LITERAL) {
+#pragma unroll
+              for (int db = 0; db < DB; ++db)
+#pragma unroll
+                for (int nb = 0; nb < 2; ++nb)
+                  tma_load_3d(dst + (db * 2 + nb) * 8192, &tmK, &k_full[stage],
+                              wk.bh * prm.T + k0 + nb * 64, db * 64, 0);
+            } else {
+#pragma unroll
+              for (int db = 0; db < DB; ++db)
+                tma_load_3d(dst + db * (BKV * 128), &tmK, &k_full[stage], db * 64, k0, wk.bh);
+            }
+            ++kt;
+          }
+          {
+            const int stage = vt % VS;
+            if (!mbar_wait(&v_empty[stage], ((vt / VS) & 1) ^ 1)) {
+              atomicCAS(status, 0, MU_DEV_TIMEOUT_PRODUCER);
+              ok = false;
+              break;
+            }
+            uint8_t *dst = sV + stage * Cfg::V_BYTES;
+            mbar_arrive_expect_tx(&v_full[stage], Cfg::V_BYTES);
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+              for (int db = 0; db < DB; ++db)
+                tma_load_3d(dst + (kb * DB + db) * 8192, &tmV, &v_full[stage], db * 64, k0 + kb * 64,
+                            wk.bh);
+            ++vt;
+          }
+        }
+      }
+      if (!ok)
+        for (int i = 0; i < 64; ++i)
+          __nanosleep(1000);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc(1u, 0u, LITERAL ? 1u : 0u, BQ, BKV);
+      constexpr uint32_t idesc_pv = make_idesc(1u, 0u, 1u, BQ, D);
+      bool ok = true;
+      uint32_t kq = 0, vq = 0;      // K / V tiles consumed so far
+      uint32_t wq[2] = {0, 0};      // works with a tile A / B so far
+      uint32_t pt[2] = {0, 0};      // probability tiles consumed so far, per query tile
+      auto fail = [&]() {
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
+        ok = false;
+      };
+      // S_x = Q_x · K'(stage)
+      auto issue_qk = [&](int x, int stage) {
+        const uint32_t q_addr = smem_u32(sQ + x * Cfg::Q_BYTES);
+        const uint32_t k_addr = smem_u32(sK + stage * Cfg::K_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t ad = make_smem_desc(q_addr + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
+          const uint64_t bd =
+              LITERAL ? make_smem_desc(k_addr + (k / 4) * (2 * 8192) + (k % 4) * 2048, 8192, 1024)
+                      : make_smem_desc(k_addr + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
+          umma_f16(tmem_S + x * BKV, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[x]);
+      };
+      // O_x (+)= P_x · V(stage), P_x in tensor memory over the first 64 columns of S_x
+      auto issue_pv = [&](int x, int stage, bool accumulate) {
+        const uint32_t v_addr = smem_u32(sV + stage * Cfg::V_BYTES);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k) {
+          const uint64_t bd = make_smem_desc(v_addr + (k / 4) * (DB * 8192) + (k % 4) * 2048, 8192, 1024);
+          umma_f16_ts(tmem_O + x * D, tmem_S + x * BKV + k * 8, bd, idesc_pv,
+                      (accumulate || k != 0) ? 1u : 0u);
+        }
+      };
+      WorkIter wit = {0, 0};
+      for (Work wk; ok && next_work(wit, wk);) {
+        const int nk_x[2] = {wk.nk_a, wk.nk_b};
+        const int nk = max(wk.nk_a, wk.nk_b);
+        for (int x = 0; x < 2 && ok; ++x)
+          if (nk_x[x] > 0 && !mbar_wait(&q_full[x], wq[x] & 1))
+            fail();
+        if (!ok)
+          break;
+        // first key tile: both score tiles
+        if (!mbar_wait(&k_full[kq % KS], (kq / KS) & 1)) {
+          fail();
+          break;
+        }
+        tc_fence_after();
+        for (int x = 0; x < 2; ++x)
+          if (nk_x[x] > 0) {
+            issue_qk(x, kq % KS);
+            if (nk_x[x] == 1)
+              umma_commit(&q_empty[x]);
+          }
+        umma_commit(&k_empty[kq % KS]);
+        ++kq;
+        for (int j = 0; j < nk && ok; ++j) {
+          const int vstage = vq % VS;
+          if (!mbar_wait(&v_full[vstage], (vq / VS) & 1)) {
+            fail();
+            break;
+          }
+          bool k_ready = false; // K of tile j+1 has been waited for
+          for (int x = 0; x < 2 && ok; ++x) {
+            if (j >= nk_x[x])
+              continue;
+            // probabilities of (x, j); the first P·V of a work overwrites O_x, which the
+            // softmax warps must have read (previous work)
+            if (!mbar_wait(&p_full[x], pt[x] & 1) ||
+                (j == 0 && !mbar_wait(&o_free[x], (wq[x] & 1) ^ 1))) {
+              fail();
+              break;
+            }
+            ++pt[x];
+            tc_fence_after();
+            issue_pv(x, vstage, j > 0);
+            if (j == nk_x[x] - 1)
+              umma_commit(&o_full[x]);
+            if (j + 1 < nk_x[x]) {
+              if (!k_ready) {
+                if (!mbar_wait(&k_full[kq % KS], (kq / KS) & 1)) {
+                  fail();
+                  break;
+                }
+                tc_fence_after();
+                k_ready = true;
+              }
+              issue_qk(x, kq % KS);
+              if (j + 1 == nk_x[x] - 1)
+                umma_commit(&q_empty[x]);
+            }
+          }
+          if (!ok)
+            break;
+          umma_commit(&v_empty[vstage]);
+          ++vq;
+          if (j + 1 < nk) {
+            umma_commit(&k_empty[kq % KS]);
+            ++kq;
+          }
+        }
+        for (int x = 0; x < 2; ++x)
+          if (nk_x[x] > 0)
+            ++wq[x];
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- softmax and output: warps 2-5 tile A, warps 6-9 tile B ----------------
+    const int x = (warp - 2) >> 2;     // which query tile of the pair
+    const int q = warp & 3;            // TMEM lane quarter this warp may access
+    const int row = q * 32 + lane;     // row inside the query tile = TMEM lane
+    const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t s_addr = tmem_S + lane_sel + x * BKV;
+    const uint32_t o_addr = tmem_O + lane_sel + x * D;
+    const float scale_b = bf16_round(prm.scale);
+    const uint32_t scale2 = (__float_as_uint(scale_b) >> 16) * 0x00010001u;
+    constexpr float L2E = 1.4426950408889634f;
+    bool ok = true;
+    uint32_t st = 0, wx = 0; // score tiles / works of this query tile so far
+    uint32_t n_epi = 0;      // output tiles that went through the staging buffer before this one
+
+    WorkIter wit = {0, 0};
+    for (Work wk; ok && next_work(wit, wk);) {
+      const int nk = x == 0 ? wk.nk_a : wk.nk_b;
+      // the staging buffer is used in the order A, B of each work
+      const uint32_t my_epi = n_epi + (x == 1 ? 1u : 0u);
+      n_epi += wk.nk_b > 0 ? 2u : 1u;
+      if (nk == 0)
+        continue;
+      const int q0 = wk.qa + x * BQ;
+      const int qrow = q0 + row;
+      float m_ref = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < nk && ok; ++j, ++st) {
+        if (!mbar_wait(&s_full[x], st & 1)) {
+          atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const int k0 = j * BKV;
+        int lim = prm.T - k0; // keys this row may see inside the tile: [0, lim)
+        if (prm.causal)
+          lim = min(lim, qrow - k0 + 1);
+        const bool need_mask = (k0 + BKV > prm.T) || (prm.causal && k0 + BKV > q0); // warp-uniform
+        // pass 1: first rounding (fp32 accumulator -> bf16 pairs kept in registers), mask, row maximum
+        uint32_t sp[BKV / 2];
+        uint32_t mxa[4] = {0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[2][32];
+          tmem_ld_32x32(s_addr + h * 64, r[0]);
+          tmem_ld_32x32(s_addr + h * 64 + 32, r[1]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int k = 0; k < 32; k += 2) {
+              uint32_t u = pack_bf16x2(__uint_as_float(r[c][k]), __uint_as_float(r[c][k + 1]));
+              if (need_mask) {
+                const int col = h * 64 + c * 32 + k;
+                if (col >= lim)
+                  u = (u & 0xFFFF0000u) | 0x0000FF80u;
+                if (col + 1 >= lim)
+                  u = (u & 0x0000FFFFu) | 0xFF800000u;
+              }
+              sp[h * 32 + c * 16 + k / 2] = u;
+              mxa[(k >> 1) & 3] = bf16x2_max(mxa[(k >> 1) & 3], u);
+            }
+        }
+        const uint32_t mx2 = bf16x2_max(bf16x2_max(mxa[0], mxa[1]), bf16x2_max(mxa[2], mxa[3]));
+        const float raw_mx = fmaxf(bf16_lo(mx2), bf16_hi(mx2));
+        const float mine = bf16_round(raw_mx * scale_b); // exactly a bf16 value (or -inf)
+        const float mx = fmaxf(m_ref, mine);
+        const float m_new = (mx == -INFINITY) ? 0.f : mx; // rows past the end of the sequence
+        if (j == 0) {
+          m_ref = m_new;
+        } else {
+          // m_ref follows the running maximum only when that has moved by more than 2^8, so O in
+          // tensor memory almost never needs rescaling. s_full of this tile was committed after
+          // the previous P·V of this query tile, so O is at rest here.
+          const bool grow = (m_new - m_ref) * L2E > 8.0f;
+          if (__any_sync(0xffffffffu, grow)) {
+            const float a = grow ? ex2_approx((m_ref - m_new) * L2E) : 1.0f;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32(o_addr + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int k = 0; k < 32; ++k)
+                r[k] = __float_as_uint(__uint_as_float(r[k]) * a);
+              tmem_st_32x32(o_addr + c * 32, r);
+            }
+            tmem_st_wait();
+            l_run *= a;
+            if (grow)
+              m_ref = m_new;
+          }
+        }
+        const float mL = m_ref * L2E;
+        // pass 2: second rounding (times the bf16 scale), probabilities -> bf16 pairs -> tensor
+        // memory over the first 64 columns of the score tile. Masked columns hold -inf: exp2 gives 0.
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const uint32_t u = bf16x2_mul(sp[c * 16 + k], scale2);
+            const float p0 = ex2_approx(fmaf(bf16_lo(u), L2E, -mL));
+            const float p1 = ex2_approx(fmaf(bf16_hi(u), L2E, -mL));
+            sum0 += p0;
+            sum1 += p1;
+            pk[k] = pack_bf16x2(p0, p1);
+          }
+          tmem_st_32x16(s_addr + c * 16, pk);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive(&p_full[x]);
+        l_run += sum0 + sum1;
+      }
+      // ---- output: O / l -> bf16 -> staging tile -> TMA store (token-major, heads merged) ----
+      if (ok && !mbar_wait(&o_full[x], wx & 1)) {
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+      // the tile staged before this one must have left the buffer
+      if (ok && my_epi > 0 && !mbar_wait(stg_done, (my_epi - 1) & 1)) {
+        atomicCAS(status, 0, MU_DEV_TIMEOUT_EPILOGUE);
+        ok = false;
+      }
+      if (ok) {
+        tc_fence_after();
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        uint8_t *orow = sStg + row * 128;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(o_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int gc = c * 4 + i; // 16-byte chunk of the row
+            const int box = gc >> 3, cc = gc & 7;
+            uint32_t ow[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              ow[k] = pack_bf16x2(__uint_as_float(r[i * 8 + 2 * k]) * inv,
+                                  __uint_as_float(r[i * 8 + 2 * k + 1]) * inv);
+            *reinterpret_cast<uint4 *>(orow + box * (BQ * 128) + ((cc ^ (lane & 7)) << 4)) =
+                make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          }
+        }
+        tc_fence_before();
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&o_free[x]); // O_x may be overwritten by the next work
+          if (q0 + q * 32 < prm.T) {
+            const int bb = wk.bh / prm.H, hh = wk.bh % prm.H;
+#pragma unroll
+            for (int db = 0; db < DB; ++db)
+              tma_store_5d(&tmO, sStg + db * (BQ * 128) + q * 32 * 128, db * 64, hh, q0 + q * 32, bb, 0);
+            bulk_commit();
+            bulk_wait_read<0>();
+          }
+          mbar_arrive(stg_done);
+        }
+        __syncwarp();
+      }
+      ++wx;
+    }
+    if (lane == 0)
+      bulk_wait<0>(); // every store of this warp has completed before the CTA exits
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1)
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -636,6 +1152,11 @@ static bool att_map(CUtensorMap *map, const void *base, int rank, const unsigned
             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+// 0: the two-query-tile kernel (default); 1: the one-tile kernel above. Set through
+// mu_debug_attention_variant for A/B timing; both give results within the same tolerance.
+static int g_attention_variant = 0;
+void set_attention_variant(int v) { g_attention_variant = v; }
 
 // Returns 0 ok, 1 shape/alignment outside this kernel's envelope, 2 launch failure.
 int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *out, int B, int H,
@@ -694,8 +1215,38 @@ int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *
   if (cudaGetDevice(&dev) != cudaSuccess ||
       cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0)
     return 2;
-  const unsigned long long n_works = BH * prm.n_qtiles;
+  const bool two_tiles = g_attention_variant != 1;
+  const unsigned long long n_works = BH * (two_tiles ? (prm.n_qtiles + 1) / 2 : prm.n_qtiles);
   dim3 grid(static_cast<unsigned>(n_works < static_cast<unsigned long long>(num_sms) ? n_works : num_sms));
+
+#define MU_ATT2_LAUNCH(D_, L_)                                                                   \
+  do {                                                                                           \
+    auto kern = attention2_tcgen05_kernel<D_, L_>;                                               \
+    static PerDeviceOnce attr_set;                                                               \
+    if (attr_set.get() < 0) {                                                                    \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
+                               Att2Cfg<D_>::SMEM_BYTES) != cudaSuccess)                          \
+        return 2;                                                                                \
+      attr_set.set(1);                                                                           \
+    }                                                                                            \
+    kern<<<grid, ATT_THREADS, Att2Cfg<D_>::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, prm, status); \
+  } while (0)
+
+  if (two_tiles) {
+    if (D == 128) {
+      if (literal)
+        MU_ATT2_LAUNCH(128, true);
+      else
+        MU_ATT2_LAUNCH(128, false);
+    } else {
+      if (literal)
+        MU_ATT2_LAUNCH(64, true);
+      else
+        MU_ATT2_LAUNCH(64, false);
+    }
+#undef MU_ATT2_LAUNCH
+    return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  }
 
 #define MU_ATT_LAUNCH(D_, L_)                                                                    \
   do {                                                                                           \

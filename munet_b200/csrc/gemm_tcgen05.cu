@@ -652,14 +652,17 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
   // grid runs ceil(tiles / slots) waves; a shape whose last wave is nearly empty loses up to a
   // whole wave (M = 8192, N = 2048 is 3.46 waves of 256 x 256 pair tiles but 6.92 of 256 x 128),
   // so the candidate with the smallest waves x tile area / relative tile speed wins. The speeds
-  // are measured ratios on the decoder's shapes (pairs stage a third less operand data per FLOP).
+  // are measured on the decoder's shapes at M = 8192 (CUDA events, idle GPU): 128-wide tiles run
+  // at two thirds of the 256-wide ones whether paired or not (the epilogue and the pipeline
+  // fill weigh twice as much per FLOP), single CTAs at 0.93 of a pair. In practice the narrow
+  // tiles only win where N <= 128 or the wide ones would leave most SMs idle.
   int BN = sh.N > 128 ? 256 : (sh.N > 64 ? 128 : 64);
   int CT = 1;
   if (sh.force_bn > 0) {
     BN = sh.force_bn, CT = sh.force_ctas == 2 ? 2 : 1;
   } else if (sh.N > 64) {
     struct Cand { int bn, ct; double speed; };
-    const Cand cands[4] = {{256, 2, 1.00}, {128, 2, 0.93}, {256, 1, 0.91}, {128, 1, 0.82}};
+    const Cand cands[4] = {{256, 2, 1.00}, {128, 2, 0.66}, {256, 1, 0.93}, {128, 1, 0.65}};
     double best = 0;
     for (const Cand &c : cands) {
       if (c.bn == 256 && sh.N <= 128) continue;
