@@ -29,6 +29,7 @@
 #include "common.h"
 #include "ptx.cuh"
 #include <cuda.h>
+#include <type_traits>
 
 namespace mu {
 
@@ -976,28 +977,37 @@ attention2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         // pass 1: first rounding (fp32 accumulator -> bf16 pairs kept in registers), mask, row maximum
         uint32_t sp[BKV / 2];
         uint32_t mxa[4] = {0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u};
+        // Two copies of the loop: only the tiles on the diagonal (and a ragged last tile) pay
+        // for the per-column comparisons.
+        auto pass1 = [&](auto masked) {
+          constexpr bool MASKED = decltype(masked)::value;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t r[2][32];
-          tmem_ld_32x32(s_addr + h * 64, r[0]);
-          tmem_ld_32x32(s_addr + h * 64 + 32, r[1]);
-          tmem_ld_wait();
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[2][32];
+            tmem_ld_32x32(s_addr + h * 64, r[0]);
+            tmem_ld_32x32(s_addr + h * 64 + 32, r[1]);
+            tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < 2; ++c)
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
-            for (int k = 0; k < 32; k += 2) {
-              uint32_t u = pack_bf16x2(__uint_as_float(r[c][k]), __uint_as_float(r[c][k + 1]));
-              if (need_mask) {
-                const int col = h * 64 + c * 32 + k;
-                if (col >= lim)
-                  u = (u & 0xFFFF0000u) | 0x0000FF80u;
-                if (col + 1 >= lim)
-                  u = (u & 0x0000FFFFu) | 0xFF800000u;
+              for (int k = 0; k < 32; k += 2) {
+                uint32_t u = pack_bf16x2(__uint_as_float(r[c][k]), __uint_as_float(r[c][k + 1]));
+                if constexpr (MASKED) {
+                  const int col = h * 64 + c * 32 + k;
+                  if (col >= lim)
+                    u = (u & 0xFFFF0000u) | 0x0000FF80u;
+                  if (col + 1 >= lim)
+                    u = (u & 0x0000FFFFu) | 0xFF800000u;
+                }
+                sp[h * 32 + c * 16 + k / 2] = u;
+                mxa[(k >> 1) & 3] = bf16x2_max(mxa[(k >> 1) & 3], u);
               }
-              sp[h * 32 + c * 16 + k / 2] = u;
-              mxa[(k >> 1) & 3] = bf16x2_max(mxa[(k >> 1) & 3], u);
-            }
-        }
+          }
+        };
+        if (need_mask)
+          pass1(std::true_type{});
+        else
+          pass1(std::false_type{});
         const uint32_t mx2 = bf16x2_max(bf16x2_max(mxa[0], mxa[1]), bf16x2_max(mxa[2], mxa[3]));
         const float raw_mx = fmaxf(bf16_lo(mx2), bf16_hi(mx2));
         const float mine = bf16_round(raw_mx * scale_b); // exactly a bf16 value (or -inf)
