@@ -1041,20 +1041,29 @@ attention2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         const float mL = m_ref * L2E;
         // pass 2: second rounding (times the bf16 scale), probabilities -> bf16 pairs -> tensor
         // memory over the first 64 columns of the score tile. Masked columns hold -inf: exp2 gives 0.
-        float sum0 = 0.f, sum1 = 0.f;
+        // the exponent arguments and the row sum run two columns per instruction (packed fp32)
+        const uint64_t l2e2 = f32x2_pack(L2E, L2E), nml2 = f32x2_pack(-mL, -mL);
+        uint64_t sum2[2] = {f32x2_pack(0.f, 0.f), f32x2_pack(0.f, 0.f)};
 #pragma unroll
         for (int c = 0; c < BKV / 32; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
             const uint32_t u = bf16x2_mul(sp[c * 16 + k], scale2);
-            const float p0 = ex2_approx(fmaf(bf16_lo(u), L2E, -mL));
-            const float p1 = ex2_approx(fmaf(bf16_hi(u), L2E, -mL));
-            sum0 += p0;
-            sum1 += p1;
+            float x0, x1;
+            f32x2_unpack(f32x2_fma(f32x2_pack(bf16_lo(u), bf16_hi(u)), l2e2, nml2), x0, x1);
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            sum2[k & 1] = f32x2_add(sum2[k & 1], f32x2_pack(p0, p1));
             pk[k] = pack_bf16x2(p0, p1);
           }
           tmem_st_32x16(s_addr + c * 16, pk);
+        }
+        float sum0, sum1;
+        {
+          float a0, a1, b0, b1;
+          f32x2_unpack(sum2[0], a0, a1);
+          f32x2_unpack(sum2[1], b0, b1);
+          sum0 = a0 + b0, sum1 = a1 + b1;
         }
         tmem_st_wait();
         tc_fence_before();
