@@ -472,9 +472,12 @@ def run_tp(torch, dist, mb, ctx, cfg, dev, stream, timed, args, pk):
     lib = mb.lib()
     tensors = decoder_tensors(torch, dev, V, T, d, L)
     comm = mb.Comm.from_torch_distributed(ctx)
-    eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_MATH, comm=comm, tp_overlap=bool(args.tp_overlap))
+    eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_MATH, comm=comm, tp_overlap=bool(args.tp_overlap),
+                 tp_exchange=args.tp_exchange)
     eng.load(gpt_decoder_config(V, T, d, H, L), tensors)
     eng.compile((B, T), mb.I32)
+    if args.tp_exchange == "peer":
+        eng.attach_peer_via_torch_distributed()
     del tensors
     torch.cuda.empty_cache()
     g = torch.Generator(device="cpu")
@@ -510,15 +513,19 @@ def run_tp(torch, dist, mb, ctx, cfg, dev, stream, timed, args, pk):
     ctx.check()
     by_kind = summarize_profile(eng.profile(reps=2))
     ar = by_kind.get("all_reduce")
+    pr = by_kind.get("peer_reduce")
     rec = {
         "parallelism": "tensor-parallel x2 (Megatron column/row split), one replica, batch 64",
         "attention_k_addressing": "math (true Q.K^T; literal addressing cannot be head-sharded)",
         "steps": k, "value": B * T * k / (ms / 1e3), "ms_per_step": ms / k, "unit": "tokens/s",
         "e2e_value": B * T * k / (ms_e / 1e3),
         "per_kind_ms": {kk: round(v["ms"], 3) for kk, v in by_kind.items()},
-        "exchange": eng.exchange_description() if hasattr(eng, "exchange_description") else None,
+        "exchange": ("peer memory: fused (mine + peer's partial over NVLink) + bias + residual kernel"
+                     if args.tp_exchange == "peer" else "NCCL all-reduce, then a bias + residual pass"),
         "all_reduce": ({"calls": ar["n"], "ms": ar["ms"], "bytes_per_rank": ar["bytes"],
                         "gbs_per_direction": ar["bytes"] / (ar["ms"] / 1e3) / 1e9} if ar and ar["ms"] > 0 else None),
+        "peer_reduce": ({"calls": pr["n"], "ms": pr["ms"], "bytes_from_peer": pr["bytes"],
+                         "nvlink_gbs": pr["bytes"] / (pr["ms"] / 1e3) / 1e9} if pr and pr["ms"] > 0 else None),
         "engine": eng.stats(),
     }
     eng.close()
@@ -803,6 +810,8 @@ def main():
                     help="skip the weak / tp2 / configs sub-records (headline measurement only)")
     ap.add_argument("--configs-only", action="store_true", help="print the four smaller workloads and exit")
     ap.add_argument("--config-reps", type=int, default=20)
+    ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
+                    help="tp2 sub-record: partial sums through peer memory (default) or NCCL all-reduce")
     ap.add_argument("--tp-overlap", type=int, default=1,
                     help="tp2 sub-record: 1 = exchange of a row chunk under the GEMM of the next; 0 = in order")
     args = ap.parse_args()

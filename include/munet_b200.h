@@ -337,7 +337,8 @@ int mu_engine_create(mu_ctx *ctx, mu_engine **out);
 void mu_engine_destroy(mu_engine *engine);
 const char *mu_engine_last_error(const mu_engine *engine);
 /* options: "kmode" (mu_kmode), "use_graph" (0/1), "argmax" (0/1: also produce int32 argmax),
- * "plan_cache_entries" (plans kept under a wildcard contract). Set them before the first compile. */
+ * "plan_cache_entries" (plans kept under a wildcard contract), "tp_size" / "tp_rank" / "tp_overlap" /
+ * "tp_exchange" (tensor parallelism, below). Set them before the first compile. */
 int mu_engine_set_option(mu_engine *engine, const char *name, int value);
 int mu_engine_load(mu_engine *engine, const char *artifact_path, int compute_dtype);
 /* shapes: all tensors' dims concatenated, ndims[i] of them per tensor */
@@ -352,6 +353,22 @@ int mu_engine_load_memory(mu_engine *engine, const char *config_json, int n_tens
  * Option "tp_overlap" (default 1) cuts the row-parallel layers into four row chunks and runs
  * the all-reduce of one chunk on a second stream under the GEMM of the next. */
 int mu_engine_set_comm(mu_engine *engine, mu_comm *comm);
+/* Option "tp_exchange" = 1 (two ranks, bfloat16): the partial sums of the row-parallel layers
+ * meet through peer memory instead of NCCL. Each rank's exchange kernel reads the other rank's
+ * partial straight over NVLink (plain peer loads; no TMA, multicast or multimem) and writes
+ * sum + bias + residual in one pass; two counters per rank, written by the peer, order the
+ * GEMMs and the reads, and every device-side wait on them is bounded (MU_ERR_TIMEOUT from
+ * mu_check / mu_engine_run when the peer never arrives). Set-up, after mu_engine_compile on both
+ * ranks: mu_engine_peer_info -> mu_ipc_export (a 64-byte handle each for the arena and the
+ * counters) -> hand the handles to the other process -> mu_ipc_open -> mu_engine_attach_peer.
+ * Attaching runs one forward and captures the graph: both ranks call it at the same time. The
+ * communicator is still required at compile (it defines rank and size). */
+size_t mu_peer_flags_bytes(void);
+int mu_ipc_export(mu_ctx *ctx, const void *device_ptr, void *handle_out, size_t capacity);
+int mu_ipc_open(mu_ctx *ctx, const void *handle, void **peer_ptr);
+int mu_ipc_close(mu_ctx *ctx, void *peer_ptr);
+int mu_engine_peer_info(const mu_engine *engine, void **arena, void **counters);
+int mu_engine_attach_peer(mu_engine *engine, void *peer_arena, void *peer_counters);
 int mu_engine_compile(mu_engine *engine, const int *input_shape, int ndim, int input_dtype);
 /* Engine::compile(example, expected_input_shape) with -1 wildcards (detail::ShapeContract,
  * src/inference.hpp:128-176; tests/test_inference.cpp:402-438): expected_shape[i] == -1 lets

@@ -105,6 +105,12 @@ SIGNATURES = {
     "mu_engine_compile_contract": (_i, [_vp, C.POINTER(_i), _i, C.POINTER(_i), _i]),
     "mu_engine_select_shape": (_i, [_vp, C.POINTER(_i), _i]),
     "mu_engine_plan_count": (_i, [_vp]),
+    "mu_peer_flags_bytes": (_sz, []),
+    "mu_ipc_export": (_i, [_vp, _vp, _vp, _sz]),
+    "mu_ipc_open": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "mu_ipc_close": (_i, [_vp, _vp]),
+    "mu_engine_peer_info": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
+    "mu_engine_attach_peer": (_i, [_vp, _vp, _vp]),
     "mu_engine_op_dims": (_i, [_vp, _i, C.POINTER(_i)]),
     "mu_engine_output_shape": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "mu_engine_stats": (_i, [_vp] + [C.POINTER(_ll)] * 5),

@@ -33,12 +33,25 @@ using mu::Json;
 using mu::NamedTensor;
 
 extern "C" int mu_ctx_simt_forced(const mu_ctx *ctx); // api.cu
+extern "C" { // peer_reduce.cu
+size_t mu_peer_flags_bytes(void);
+int mu_peer_arm(mu_ctx *, void *, unsigned, void *);
+int mu_peer_step(mu_ctx *, void *, void *);
+int mu_peer_signal(mu_ctx *, void *, void *, unsigned, unsigned, void *);
+int mu_peer_wait_done(mu_ctx *, void *, unsigned, unsigned, void *);
+int mu_peer_reduce(mu_ctx *, const void *, const void *, const void *, const void *, void *, long long, int,
+                   void *, void *, unsigned, unsigned, unsigned, void *);
+}
 
 namespace {
 
 enum OpKind {
   OP_EMBED, OP_LN, OP_LINEAR, OP_QKV, OP_ATTN, OP_ELTWISE, OP_ARGMAX, OP_CONV, OP_MAXPOOL, OP_GAP,
-  OP_ALLREDUCE, OP_BATCHNORM, OP_UPSAMPLE, OP_LEAKY, OP_RMSNORM
+  OP_ALLREDUCE, OP_BATCHNORM, OP_UPSAMPLE, OP_LEAKY, OP_RMSNORM,
+  // tensor-parallel exchange over peer memory (peer_reduce.cu): start of a forward, "the peer has
+  // read my earlier partials", "my partial is complete", the fused sum + bias + residual, and a
+  // kernel-less op that only joins the second stream back into the main one
+  OP_PEER_STEP, OP_PEER_WAIT, OP_PEER_SIGNAL, OP_PEER_REDUCE, OP_JOIN
 };
 
 struct Tensor {
@@ -64,6 +77,8 @@ struct Op {
   // the GEMM of the next); `rec_ev` is recorded after the op, `wait_ev` awaited before it.
   long long row0 = 0;
   int side = 0, wait_ev = -1, rec_ev = -1;
+  int budget = 0; // GEMM leaves a few SMs to the exchange kernel running beside it
+  int xidx = 0;   // peer exchange: number of this exchange within one forward
 };
 
 struct Weight {
@@ -223,6 +238,8 @@ struct mu_engine {
   }
   void release_compiled() {
     release_plans();
+    if (peer_flags_local) mu_free(ctx, peer_flags_local), peer_flags_local = nullptr;
+    peer_flags_remote = peer_arena = nullptr;
     if (cap_stream) cudaStreamDestroy(cap_stream), cap_stream = nullptr;
     if (side_stream) cudaStreamDestroy(side_stream), side_stream = nullptr;
     if (weight_slab) mu_free(ctx, weight_slab), weight_slab = nullptr;
@@ -365,6 +382,17 @@ struct mu_engine {
   int plan_and_allocate();
   int launch_all(cudaStream_t st);
   int n_events = 0, tp_overlap = 1, tp_comm_sms = 20;
+  // tp_exchange 1: partial sums of the row-parallel layers meet through peer memory
+  // (peer_reduce.cu) instead of NCCL; needs mu_engine_attach_peer after compile.
+  int tp_exchange = 0, peer_exchanges = 0;
+  // The peer reads this rank's partial sums straight out of the arena, so a partial must stay
+  // untouched until the peer has signalled that it is done with it — which this rank only waits
+  // for before its next row-parallel GEMM. The partial's lifetime in the buffer plan is therefore
+  // stretched to that wait (or to the end of the forward), not just to its last local reader.
+  int peer_last_partial = -1;
+  unsigned peer_ctas = 0;
+  void *peer_flags_local = nullptr, *peer_flags_remote = nullptr, *peer_arena = nullptr;
+  int capture_graph();
   std::vector<cudaEvent_t> events;
   cudaStream_t side_stream = nullptr;
   // rows [row0, ...) of a [rows, cols] tensor (nullptr stays nullptr)
@@ -435,13 +463,50 @@ int mu_engine::lower_linear(const std::string &prefix, int K, int N, bool bias, 
     } else {
       e_out = op.out;
     }
-    // Rows are cut into chunks so that the all-reduce of chunk i (second stream) runs under the
-    // GEMM of chunk i+1; the bias/residual pass of a chunk waits for its all-reduce.
+    // Rows are cut into chunks so that the exchange of chunk i (second stream) runs under the
+    // GEMM of chunk i+1; what consumes a chunk waits for its exchange.
     const int Mtot = op.M;
     int chunks = (tp_overlap && Mtot >= 4096) ? 4 : 1;
     const int rows_per = ((Mtot + chunks - 1) / chunks + 255) / 256 * 256;
     chunks = (Mtot + rows_per - 1) / rows_per;
     std::vector<int> done_ev(chunks, -1);
+    if (tp_exchange) {
+      // peer-memory exchange: GEMM chunk -> "partial complete" to the peer -> fused
+      // (mine + peer's) + bias + residual on the second stream
+      for (int c = 0; c < chunks; ++c) {
+        if (c == 0) {
+          Op w;
+          w.kind = OP_PEER_WAIT, w.xidx = peer_exchanges, w.in = peer_last_partial;
+          push(w);
+          peer_last_partial = op.out;
+        }
+        Op g = op;
+        g.row0 = 1ll * c * rows_per, g.M = std::min(rows_per, Mtot - c * rows_per);
+        g.budget = chunks > 1 ? 1 : 0;
+        push(g);
+        Op sg;
+        sg.kind = OP_PEER_SIGNAL, sg.xidx = peer_exchanges;
+        Op r;
+        r.kind = OP_PEER_REDUCE, r.in = op.out, r.b = bias_id, r.N = Nl, r.res = res_tid, r.out = e_out;
+        r.row0 = g.row0, r.n = 1ll * g.M * Nl, r.xidx = peer_exchanges;
+        if (chunks > 1) {
+          sg.rec_ev = n_events++;
+          r.side = 1, r.wait_ev = sg.rec_ev, r.rec_ev = n_events++;
+          done_ev[c] = r.rec_ev;
+        }
+        push(sg);
+        push(r);
+        ++peer_exchanges;
+      }
+      for (int c = 0; c < chunks && chunks > 1; ++c) {
+        Op j;
+        j.kind = OP_JOIN, j.wait_ev = done_ev[c], j.in = e_out; // keeps the result live across the join
+        push(j);
+      }
+      v.tid = e_out;
+      v.shape.back() = Nl;
+      return MU_OK;
+    }
     for (int c = 0; c < chunks; ++c) {
       Op g = op;
       g.row0 = 1ll * c * rows_per, g.M = std::min(rows_per, Mtot - c * rows_per);
@@ -450,6 +515,7 @@ int mu_engine::lower_linear(const std::string &prefix, int K, int N, bool bias, 
       ar.n = 1ll * g.M * Nl;
       if (chunks > 1) {
         g.rec_ev = n_events++;
+        g.budget = 1;
         ar.side = 1, ar.wait_ev = g.rec_ev, ar.rec_ev = n_events++;
         done_ev[c] = ar.rec_ev;
       }
@@ -933,7 +999,7 @@ int mu_engine::launch_all(cudaStream_t st) {
     if (op.wait_ev >= 0 && cudaStreamWaitEvent(s, events[op.wait_ev], 0) != cudaSuccess)
       return fail(MU_ERR_CUDA, "stream wait failed");
     // a chunked GEMM leaves a few SMs free: the all-reduce of the previous chunk runs beside it
-    const bool chunked_gemm = op.kind == OP_LINEAR && op.rec_ev >= 0;
+    const bool chunked_gemm = op.kind == OP_LINEAR && op.budget;
     if (chunked_gemm) mu_ctx_set_sm_budget(ctx, std::max(2, mu_ctx_num_sms(ctx) - tp_comm_sms));
     int rc = launch_op(op, s);
     if (chunked_gemm) mu_ctx_set_sm_budget(ctx, 0);
@@ -1024,6 +1090,29 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       rc = mu_upsample2d(ctx, tptr(op.in), tptr(op.out), op.B, op.iC, op.iH, op.iW, op.stride, dtype, st);
       n_launches += 1;
       break;
+    case OP_JOIN:
+      break;
+    case OP_PEER_STEP:
+    case OP_PEER_WAIT:
+    case OP_PEER_SIGNAL:
+    case OP_PEER_REDUCE: {
+      if (!peer_arena || !peer_flags_remote)
+        return fail(MU_ERR_INVALID, "Engine: the peer exchange needs mu_engine_attach_peer after compile");
+      const unsigned per = static_cast<unsigned>(peer_exchanges), idx = static_cast<unsigned>(op.xidx);
+      if (op.kind == OP_PEER_STEP) rc = mu_peer_step(ctx, peer_flags_local, st);
+      else if (op.kind == OP_PEER_WAIT) rc = mu_peer_wait_done(ctx, peer_flags_local, per, idx, st);
+      else if (op.kind == OP_PEER_SIGNAL) rc = mu_peer_signal(ctx, peer_flags_local, peer_flags_remote, per, idx, st);
+      else {
+        // both ranks planned the same arena: the peer's partial sits at the same offset in its arena
+        const char *a = static_cast<const char *>(rows(op.in, op.row0, op.N));
+        const char *a_peer = static_cast<const char *>(peer_arena) + (a - static_cast<const char *>(arena));
+        rc = mu_peer_reduce(ctx, a, a_peer, wptr(op.b), rows(op.res, op.row0, op.N), rows(op.out, op.row0, op.N),
+                            op.n, op.N, peer_flags_local, peer_flags_remote, per, idx, peer_ctas, st);
+      }
+      n_launches += 1;
+      if (rc) return fail(rc, "peer exchange launch failed");
+      break;
+    }
     default:
       rc = MU_ERR_UNSUPPORTED;
     }
@@ -1067,6 +1156,9 @@ void mu_engine::op_work(const Op &op, double *flops, double *bytes) const {
     break;
   case OP_ALLREDUCE:
     *bytes = es * op.n; // bytes each rank contributes
+    break;
+  case OP_PEER_REDUCE:
+    *bytes = es * op.n; // bytes read from the peer over NVLink
     break;
   case OP_CONV: {
     const double oH = (op.iH + 2 * op.pad - op.ksz) / op.stride + 1, oW = (op.iW + 2 * op.pad - op.ksz) / op.stride + 1;
@@ -1185,6 +1277,7 @@ int mu_engine_set_option(mu_engine *e, const char *name, int value) {
   else if (n == "tp_overlap") e->tp_overlap = value;
   else if (n == "tp_comm_sms") e->tp_comm_sms = value;
   else if (n == "plan_cache_entries") e->plan_cache_entries = value;
+  else if (n == "tp_exchange") e->tp_exchange = value;
   else return e->fail(MU_ERR_INVALID, "unknown option '%s'", name);
   return MU_OK;
 }
@@ -1250,6 +1343,20 @@ int mu_engine::build_plan(const std::vector<int> &shape, int input_dtype) {
   tensors[v.tid].external = true;
   const bool first = weight_slab == nullptr;
   used_params.clear();
+  peer_exchanges = 0;
+  if (tp_exchange && tp_size > 1) {
+    if (tp_size != 2) return fail(MU_ERR_UNSUPPORTED, "Engine: the peer-memory exchange is built for two ranks");
+    if (dtype != MU_BF16) return fail(MU_ERR_UNSUPPORTED, "Engine: the peer-memory exchange is built for bfloat16");
+    Op stp;
+    stp.kind = OP_PEER_STEP;
+    push(stp);
+    // nothing of this forward may overwrite arena bytes the peer could still be reading from the
+    // previous forward's last exchange
+    Op w;
+    w.kind = OP_PEER_WAIT, w.xidx = 0;
+    push(w);
+    peer_last_partial = -1;
+  }
   int rc = lower(config, "", v, nullptr, nullptr);
   if (rc) return rc;
   // Every serialized tensor must belong to a module of the tree, as in the reference's loader
@@ -1273,9 +1380,27 @@ int mu_engine::build_plan(const std::vector<int> &shape, int input_dtype) {
   const int last = static_cast<int>(ops.size());
   touch(out_tid, last);
   if (argmax_tid >= 0) touch(argmax_tid, last);
+  if (peer_last_partial >= 0) touch(peer_last_partial, last);
   rc = plan_and_allocate();
   if (rc) return rc;
-  if (use_graph) {
+  if (tp_exchange && tp_size > 1) {
+    // the peer's arena and counters are not known yet: mu_engine_attach_peer warms up and captures
+    rc = mu_alloc(ctx, mu_peer_flags_bytes(), &peer_flags_local);
+    if (rc) return fail(rc, "peer counter allocation failed: %s", mu_last_error(ctx));
+    if (cudaMemset(peer_flags_local, 0, mu_peer_flags_bytes()) != cudaSuccess)
+      return fail(MU_ERR_CUDA, "peer counter clear failed");
+    return MU_OK;
+  }
+  return capture_graph();
+}
+
+// Warm-up forward (sets per-kernel attributes), then capture and instantiate the graph of the
+// active plan. Under a peer exchange both ranks run this at the same time (the warm-up forward is
+// a real exchange).
+int mu_engine::capture_graph() {
+  if (!use_graph) return MU_OK;
+  int rc;
+  {
     if (!cap_stream && cudaStreamCreateWithFlags(&cap_stream, cudaStreamNonBlocking) != cudaSuccess)
       return fail(MU_ERR_CUDA, "stream creation failed");
     // warm-up launch outside capture (sets per-kernel attributes), then capture
@@ -1373,6 +1498,8 @@ int mu_engine_select_shape(mu_engine *e, const int *shape, int ndim) {
   const std::vector<int> want(shape, shape + ndim);
   ++e->use_clock;
   if (want == e->in_shape) return MU_OK;
+  if (e->peer_flags_local)
+    return e->fail(MU_ERR_UNSUPPORTED, "Engine: one plan per engine under the peer-memory exchange");
   const int in_dtype = e->in_dtype;
   e->park_active();
   for (size_t i = 0; i < e->parked.size(); ++i)
@@ -1401,6 +1528,29 @@ int mu_engine_select_shape(mu_engine *e, const int *shape, int ndim) {
 
 int mu_engine_plan_count(const mu_engine *e) {
   return (e && e->compiled) ? static_cast<int>(e->parked.size()) + 1 : 0;
+}
+
+// Peer-memory exchange (option "tp_exchange" = 1, two ranks): after compile each rank exports its
+// arena and its counters (mu_engine_peer_info + mu_ipc_export), the host hands the handles to the
+// other rank, which opens them (mu_ipc_open) and attaches the mappings here. Attaching runs the
+// warm-up forward and captures the graph, so both ranks must call it at the same time.
+int mu_engine_peer_info(const mu_engine *e, void **arena, void **counters) {
+  if (!e || !e->compiled || !e->peer_flags_local || !arena || !counters) return MU_ERR_INVALID;
+  *arena = e->arena, *counters = e->peer_flags_local;
+  return MU_OK;
+}
+
+int mu_engine_attach_peer(mu_engine *e, void *peer_arena, void *peer_counters) {
+  if (!e || !peer_arena || !peer_counters) return MU_ERR_INVALID;
+  if (!e->compiled || !e->peer_flags_local)
+    return e->fail(MU_ERR_INVALID, "Engine: attach_peer needs a compiled engine with tp_exchange = 1");
+  e->peer_arena = peer_arena, e->peer_flags_remote = peer_counters;
+  const int sms = mu_ctx_num_sms(e->ctx);
+  e->peer_ctas = static_cast<unsigned>(e->tp_overlap ? 2 * std::max(1, e->tp_comm_sms) : 2 * sms);
+  int rc = mu_peer_arm(e->ctx, e->peer_flags_local, e->peer_ctas, nullptr);
+  if (rc == MU_OK) rc = mu_check(e->ctx, nullptr);
+  if (rc) return e->fail(rc, "peer counter set-up failed: %s", mu_last_error(e->ctx));
+  return e->capture_graph();
 }
 
 int mu_engine_output_shape(const mu_engine *e, int *shape, int *ndim, int *dtype) {
@@ -1435,6 +1585,8 @@ int mu_engine_run(mu_engine *e, const void *input, int input_on_host, void *outp
   if (!e) return MU_ERR_INVALID;
   if (!e->compiled) return e->fail(MU_ERR_INVALID, "Engine: run() called before compile()");
   if (!input) return e->fail(MU_ERR_INVALID, "Engine: null input");
+  if (e->peer_flags_local && !e->peer_arena)
+    return e->fail(MU_ERR_INVALID, "Engine: the peer exchange needs mu_engine_attach_peer before run()");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc = mu_copy(e->ctx, e->input_buf, input, e->input_bytes,
                    input_on_host ? MU_COPY_H2D : MU_COPY_D2D, st);

@@ -163,7 +163,7 @@ class Engine:
 
     def __init__(self, ctx: Context | None = None, device: int = 0, compute_dtype: int = F32,
                  kmode: int = 0, use_graph: bool = True, argmax: bool = False, comm=None,
-                 tp_overlap: bool = True):
+                 tp_overlap: bool = True, tp_exchange: str = "nccl"):
         self._lib = lib()
         self.ctx = ctx or Context(device)
         self.compute_dtype = compute_dtype
@@ -182,7 +182,12 @@ class Engine:
             self._opt("tp_size", comm.world)
             self._opt("tp_rank", comm.rank)
             self._opt("tp_overlap", int(tp_overlap))
+            if tp_exchange not in ("nccl", "peer"):
+                raise ValueError("tp_exchange is 'nccl' or 'peer'")
+            self._opt("tp_exchange", int(tp_exchange == "peer"))
             self._rc(self._lib.mu_engine_set_comm(self._h, comm._h))
+        self.tp_exchange = tp_exchange if (comm is not None and comm.world > 1) else "nccl"
+        self._peer_maps = []
         self.input_shape = None
         self.output_shape = None
         # host-side bookkeeping with the reference's names (EngineStats, src/inference.hpp:43-68)
@@ -356,6 +361,9 @@ class Engine:
         if getattr(self, "_h", None):
             self._lib.mu_engine_destroy(self._h)
             self._h = None
+            for p in getattr(self, "_peer_maps", []):
+                self._lib.mu_ipc_close(self.ctx._h, p)
+            self._peer_maps = []
 
     def __del__(self):
         try:
@@ -460,6 +468,38 @@ class Engine:
         self._emit("compile_completed", self._estats["compile_ms"])
         return self
 
+    def peer_handles(self) -> list:
+        """CUDA IPC handles (64 bytes each) of this rank's arena and exchange counters, to be
+        handed to the other rank of a two-rank peer-memory exchange (tp_exchange="peer")."""
+        arena, counters = C.c_void_p(), C.c_void_p()
+        self._rc(self._lib.mu_engine_peer_info(self._h, C.byref(arena), C.byref(counters)))
+        out = []
+        for ptr in (arena, counters):
+            buf = C.create_string_buffer(64)
+            self.ctx._rc(self._lib.mu_ipc_export(self.ctx._h, ptr, buf, 64))
+            out.append(buf.raw)
+        return out
+
+    def attach_peer(self, their_handles):
+        """Map the other rank's arena and counters and attach them. Runs one forward (a real
+        exchange) and captures the graph: both ranks call this at the same time."""
+        maps = []
+        for raw in their_handles:
+            p = C.c_void_p()
+            self.ctx._rc(self._lib.mu_ipc_open(self.ctx._h, C.create_string_buffer(raw, 64), C.byref(p)))
+            maps.append(p)
+        self._peer_maps = maps
+        self._rc(self._lib.mu_engine_attach_peer(self._h, maps[0], maps[1]))
+        return self
+
+    def attach_peer_via_torch_distributed(self):
+        """peer_handles() traded over the default torch.distributed group, then attach_peer()."""
+        import torch.distributed as dist
+        everyone = [None] * dist.get_world_size()
+        dist.all_gather_object(everyone, self.peer_handles())
+        dist.barrier()
+        return self.attach_peer(everyone[1 - dist.get_rank()])
+
     def stats(self) -> dict:
         v = [C.c_longlong() for _ in range(5)]
         self._rc(self._lib.mu_engine_stats(self._h, *[C.byref(x) for x in v]))
@@ -524,7 +564,7 @@ class Engine:
 
     OP_KINDS = ["embed", "layer_norm", "linear", "qkv_linear", "attention", "eltwise", "argmax",
                 "conv2d", "max_pool2d", "global_avg_pool", "all_reduce", "batch_norm", "upsample",
-                "leaky_relu", "rms_norm"]
+                "leaky_relu", "rms_norm", "peer_step", "peer_wait", "peer_signal", "peer_reduce", "join"]
 
     def profile(self, reps: int = 1, stream=None) -> list[dict]:
         """Eager forward with CUDA events around every op: per-op ms + algorithmic work."""

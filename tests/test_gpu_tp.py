@@ -1,6 +1,6 @@
-"""GPU x2: tensor-parallel decoder forward (Megatron column/row split + NCCL all-reduce)
-against the unsharded CPU checker, and the raw all-reduce against the reference's sum
-semantic. Needs two GPUs: skipped on a single-GPU box."""
+"""GPU x2: tensor-parallel decoder forward (Megatron column/row split; partial sums exchanged by
+NCCL all-reduce or through peer memory) against the unsharded CPU checker, and the raw
+all-reduce against the reference's sum semantic. Needs two GPUs: skipped on a single-GPU box."""
 import os
 import socket
 
@@ -23,7 +23,7 @@ def _n_gpus():
         return 0
 
 
-def _worker(rank, world, port, dtype, uid_q, res_q, B=2, T=64):
+def _worker(rank, world, port, dtype, uid_q, res_q, B=2, T=64, hq=None):
     import torch
     import munet_b200 as mb
     from munet_b200.inference import Engine, gpt_decoder_config, gpt_param_names
@@ -52,14 +52,22 @@ def _worker(rank, world, port, dtype, uid_q, res_q, B=2, T=64):
     ps = gpt_params(prng, V, T, d, L, dtype, std=0.05)
     ids = prng.integers(0, V, (B, T)).astype(np.int32)
     slabs = []
-    for overlap in (True, False):  # row chunks + all-reduce on a second stream, then the plain order
-        eng = Engine(ctx=ctx, compute_dtype=dtype, comm=comm, kmode=mb.K_MATH, tp_overlap=overlap)
+    # row chunks + exchange on a second stream, then the plain order; through NCCL and (bf16)
+    # through peer memory: the two exchanges round the same way, so all four give the same bits
+    modes = [("nccl", True), ("nccl", False)] + ([("peer", True), ("peer", False)] if dtype == BF16 else [])
+    for exchange, overlap in modes:
+        eng = Engine(ctx=ctx, compute_dtype=dtype, comm=comm, kmode=mb.K_MATH, tp_overlap=overlap,
+                     tp_exchange=exchange)
         eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)), tensor_dtype=dtype)
         eng.compile((B, T), I32)
+        if exchange == "peer":
+            hq[1 - rank].put(eng.peer_handles())
+            eng.attach_peer(hq[rank].get(timeout=120))
         slabs.append(eng.run(ids))  # [B, T, V / world]: this rank's vocabulary columns
         slabs.append(eng.run(ids))  # graph replay gives the same bits
         eng.close()
-    assert np.array_equal(slabs[0], slabs[1]) and np.array_equal(slabs[0], slabs[2])
+    for s_ in slabs[1:]:
+        assert np.array_equal(slabs[0], s_)
     res_q.put((rank, red, slabs[0]))
     comm.close()
     ctx.close()
@@ -78,7 +86,8 @@ def test_tensor_parallel_decoder_and_all_reduce(dtype, B, T):
     s.close()
     mpc = mp.get_context("spawn")
     uid_q, res_q = mpc.Queue(), mpc.Queue()
-    procs = [mpc.Process(target=_worker, args=(r, world, port, dtype, uid_q, res_q, B, T)) for r in range(world)]
+    hq = [mpc.Queue(), mpc.Queue()]
+    procs = [mpc.Process(target=_worker, args=(r, world, port, dtype, uid_q, res_q, B, T, hq)) for r in range(world)]
     for p in procs:
         p.start()
     results = dict()
