@@ -472,8 +472,8 @@ def run_tp(torch, dist, mb, ctx, cfg, dev, stream, timed, args, pk):
     lib = mb.lib()
     tensors = decoder_tensors(torch, dev, V, T, d, L)
     comm = mb.Comm.from_torch_distributed(ctx)
-    eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_MATH, comm=comm, tp_overlap=bool(args.tp_overlap),
-                 tp_exchange=args.tp_exchange)
+    eng = Engine(ctx=ctx, compute_dtype=mb.BF16, kmode=mb.K_MATH, comm=comm,
+                 tp_overlap=None if args.tp_overlap < 0 else bool(args.tp_overlap), tp_exchange=args.tp_exchange)
     eng.load(gpt_decoder_config(V, T, d, H, L), tensors)
     eng.compile((B, T), mb.I32)
     if args.tp_exchange == "peer":
@@ -812,8 +812,9 @@ def main():
     ap.add_argument("--config-reps", type=int, default=20)
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
                     help="tp2 sub-record: partial sums through peer memory (default) or NCCL all-reduce")
-    ap.add_argument("--tp-overlap", type=int, default=1,
-                    help="tp2 sub-record: 1 = exchange of a row chunk under the GEMM of the next; 0 = in order")
+    ap.add_argument("--tp-overlap", type=int, default=-1,
+                    help="tp2 sub-record: 1 = exchange of a row chunk under the GEMM of the next; 0 = in order; "
+                         "-1 = the exchange's own default")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.batch:

@@ -1546,7 +1546,8 @@ int mu_engine_attach_peer(mu_engine *e, void *peer_arena, void *peer_counters) {
     return e->fail(MU_ERR_INVALID, "Engine: attach_peer needs a compiled engine with tp_exchange = 1");
   e->peer_arena = peer_arena, e->peer_flags_remote = peer_counters;
   const int sms = mu_ctx_num_sms(e->ctx);
-  e->peer_ctas = static_cast<unsigned>(e->tp_overlap ? 2 * std::max(1, e->tp_comm_sms) : 2 * sms);
+  // four CTAs of 512 threads per SM: with eight loads each in flight, 20 SMs keep ~5 MB on the wire
+  e->peer_ctas = static_cast<unsigned>(4 * (e->tp_overlap ? std::max(1, e->tp_comm_sms) : sms));
   int rc = mu_peer_arm(e->ctx, e->peer_flags_local, e->peer_ctas, nullptr);
   if (rc == MU_OK) rc = mu_check(e->ctx, nullptr);
   if (rc) return e->fail(rc, "peer counter set-up failed: %s", mu_last_error(e->ctx));

@@ -89,10 +89,10 @@ peer_reduce_kernel(const uint4 *__restrict__ a, const uint4 *__restrict__ a_peer
   }
   __syncthreads();
   if (go) {
-    // Four independent 16-byte peer loads per thread are in flight before the first one is used
+    // Eight independent 16-byte peer loads per thread are in flight before the first one is used
     // (an NVLink round trip is a few microseconds). ld.cv: never served from a line this SM
     // cached during an earlier exchange at the same address.
-    constexpr int U = 4;
+    constexpr int U = 8;
     const long long stride = 1ll * gridDim.x * blockDim.x;
     for (long long i0 = 1ll * blockIdx.x * blockDim.x + threadIdx.x; i0 < n_vec; i0 += stride * U) {
       uint4 vp[U], va[U], vr[U];
