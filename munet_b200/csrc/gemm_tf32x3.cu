@@ -51,6 +51,17 @@ struct T3Args {
   const float *bias;
 };
 
+// Implicit-GEMM convolution (CONV = true): the A operand is never materialised. Row m of the
+// im2col matrix is output pixel m of an NHWC image, column kk = (kh*k + kw)*iC + c; a k-block of 32
+// columns is one filter tap and 32 input channels, i.e. a [bn, bh, W, 32] box of the NHWC input
+// shifted by (kh - pad, kw - pad) — one 4-D TMA load, zero fill outside the image doing the padding.
+// A 128-row tile is bn whole images (small images) or bh full rows of one image.
+struct T3Conv {
+  int icb;  // iC / 32: k-blocks per filter tap
+  int k, pad;
+  int H, bh, bn; // tile = bn images x bh rows x W columns = 128 pixels
+};
+
 // ---- pass 1: operand split ---------------------------------------------------------------
 __device__ __forceinline__ float to_tf32(float x) {
   uint32_t u;
@@ -128,12 +139,12 @@ __device__ __forceinline__ void t3_tma_store_2d(const void *tmap, const void *sr
                : "memory");
 }
 
-template <int T3_BN>
+template <int T3_BN, bool CONV>
 __global__ void __launch_bounds__(T3_THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                    const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
-                   T3Args g, int *status) {
+                   T3Args g, T3Conv cv, int *status) {
   constexpr int T3_STAGES = T3Cfg<T3_BN>::STAGES, T3_STAGE_BYTES = T3Cfg<T3_BN>::STAGE_BYTES;
   constexpr int T3_B_BYTES = T3Cfg<T3_BN>::B_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -193,8 +204,22 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_consta
           }
           uint8_t *s = smem + stage * T3_STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], T3_STAGE_BYTES);
-          t3_tma_load_2d(s, &tmAh, &full_bar[stage], kb * T3_BK, mt * T3_BM);
-          t3_tma_load_2d(s + T3_A_BYTES, &tmAl, &full_bar[stage], kb * T3_BK, mt * T3_BM);
+          if constexpr (CONV) {
+            const int tap = kb / cv.icb, c0 = (kb % cv.icb) * T3_BK;
+            const int kh = tap / cv.k, kw = tap % cv.k;
+            int n0, h0;
+            if (cv.bn > 1) {
+              n0 = mt * cv.bn, h0 = 0;
+            } else {
+              const int per_image = cv.H / cv.bh;
+              n0 = mt / per_image, h0 = (mt % per_image) * cv.bh;
+            }
+            tma_load_4d(s, &tmAh, &full_bar[stage], c0, kw - cv.pad, h0 + kh - cv.pad, n0);
+            tma_load_4d(s + T3_A_BYTES, &tmAl, &full_bar[stage], c0, kw - cv.pad, h0 + kh - cv.pad, n0);
+          } else {
+            t3_tma_load_2d(s, &tmAh, &full_bar[stage], kb * T3_BK, mt * T3_BM);
+            t3_tma_load_2d(s + T3_A_BYTES, &tmAl, &full_bar[stage], kb * T3_BK, mt * T3_BM);
+          }
           t3_tma_load_2d(s + 2 * T3_A_BYTES, &tmBh, &full_bar[stage], kb * T3_BK, nt * T3_BN);
           t3_tma_load_2d(s + 2 * T3_A_BYTES + T3_B_BYTES, &tmBl, &full_bar[stage], kb * T3_BK, nt * T3_BN);
           if (++stage == T3_STAGES) {
@@ -399,14 +424,14 @@ size_t gemm_tf32x3_scratch_bytes(int M, int N, int K) {
   return 2 * up(static_cast<size_t>(M) * K * 4) + 2 * up(static_cast<size_t>(N) * K * 4);
 }
 
-template <int BN>
+template <int BN, bool CONV = false>
 static int t3_launch(const CUtensorMap &tmAh, const CUtensorMap &tmAl, const float *bh, const float *bl,
                      const CUtensorMap &tmC, const CUtensorMap &tmR, const T3Args &g, int *status, int num_sms,
-                     cudaStream_t st) {
+                     cudaStream_t st, T3Conv cv = T3Conv()) {
   CUtensorMap tmBh, tmBl;
   if (!t3_map(&tmBh, bh, g.K, g.N, g.K, BN) || !t3_map(&tmBl, bl, g.K, g.N, g.K, BN))
     return 2;
-  auto kern = gemm_tf32x3_kernel<BN>;
+  auto kern = gemm_tf32x3_kernel<BN, CONV>;
   static PerDeviceOnce attr_set;
   if (attr_set.get() < 0) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T3Cfg<BN>::SMEM) != cudaSuccess)
@@ -415,8 +440,69 @@ static int t3_launch(const CUtensorMap &tmAh, const CUtensorMap &tmAl, const flo
   }
   const long long tiles = 1ll * ((g.M + T3_BM - 1) / T3_BM) * ((g.N + BN - 1) / BN);
   const unsigned grid = static_cast<unsigned>(tiles < num_sms ? tiles : num_sms);
-  kern<<<grid, T3_THREADS, T3Cfg<BN>::SMEM, st>>>(tmAh, tmAl, tmBh, tmBl, tmC, tmR, g, status);
+  kern<<<grid, T3_THREADS, T3Cfg<BN>::SMEM, st>>>(tmAh, tmAl, tmBh, tmBl, tmC, tmR, g, cv, status);
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+// NHWC fp32 image tensor [B, H, W, C] as a 4-D map, box [bn, bh, W, 32 channels], 128-byte swizzle:
+// in shared memory the box is 128 rows of 128 bytes, the K-major A tile the MMA descriptors expect.
+static bool t3_map_nhwc(CUtensorMap *m, const void *base, int B, int H, int W, int C, int bh, int bn) {
+  T3EncodeFn fn = t3_encode_fn();
+  if (!fn)
+    return false;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(W), static_cast<cuuint64_t>(H),
+                        static_cast<cuuint64_t>(B)};
+  cuuint64_t strides[3] = {4ull * C, 4ull * C * W, 4ull * C * W * H};
+  cuuint32_t box[4] = {32, static_cast<cuuint32_t>(W), static_cast<cuuint32_t>(bh), static_cast<cuuint32_t>(bn)};
+  cuuint32_t es[4] = {1, 1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void *>(base), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Convolution (stride 1, "same" padding: output H x W = input H x W) as an implicit GEMM on inputs
+// that are already split: xh, xl NHWC [B,H,W,iC]; wh, wl [oC][k][k][iC] (K-major, K = k*k*iC);
+// c [B*H*W, oC] (NHWC output), bias + optional ReLU fused. Returns 0 ok, 1 when the geometry does
+// not tile into 128-pixel boxes of whole rows (the caller falls back), 2 failure.
+// Does the geometry tile into 128-pixel boxes of whole image rows?
+bool conv_tf32x3_implicit_ok(int B, int H, int W, int iC, int oC, int k, int pad) {
+  if (W <= 0 || W > 128 || 128 % W || iC % 32 || oC % 4 || 2 * pad != k - 1 || k > 15)
+    return false;
+  const int rows = 128 / W;
+  if (rows <= H ? (H % rows != 0) : (rows % H != 0 || B % (rows / H) != 0))
+    return false;
+  const long long M = 1ll * B * H * W;
+  return M <= 0x7fffffffll && M % 128 == 0;
+}
+
+int conv_tf32x3_implicit(const float *xh, const float *xl, const float *wh, const float *wl, float *c,
+                         const float *bias, int relu, int B, int H, int W, int iC, int oC, int k, int pad,
+                         int *status, int num_sms, cudaStream_t st) {
+  if (!conv_tf32x3_implicit_ok(B, H, W, iC, oC, k, pad))
+    return 1;
+  const int rows = 128 / W;
+  T3Conv cv;
+  cv.icb = iC / 32, cv.k = k, cv.pad = pad, cv.H = H;
+  if (rows <= H)
+    cv.bh = rows, cv.bn = 1;
+  else
+    cv.bh = H, cv.bn = rows / H;
+  const long long M = 1ll * B * H * W;
+  auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!al16(xh) || !al16(xl) || !al16(wh) || !al16(wl) || !al16(c))
+    return 1;
+  CUtensorMap tmAh, tmAl, tmC;
+  if (!t3_map_nhwc(&tmAh, xh, B, H, W, iC, cv.bh, cv.bn) || !t3_map_nhwc(&tmAl, xl, B, H, W, iC, cv.bh, cv.bn) ||
+      !t3_map(&tmC, c, oC, M, oC, 32))
+    return 2;
+  T3Args g;
+  g.M = static_cast<int>(M), g.N = oC, g.K = k * k * iC, g.act = relu ? ACT_RELU : ACT_NONE;
+  g.has_bias = bias != nullptr, g.has_res = 0, g.alpha = 1.0f, g.bias = bias;
+  if (oC > 128)
+    return t3_launch<256, true>(tmAh, tmAl, wh, wl, tmC, tmC, g, status, num_sms, st, cv);
+  if (oC > 64)
+    return t3_launch<128, true>(tmAh, tmAl, wh, wl, tmC, tmC, g, status, num_sms, st, cv);
+  return t3_launch<64, true>(tmAh, tmAl, wh, wl, tmC, tmC, g, status, num_sms, st, cv);
 }
 
 // The GEMM on operands that are already split: ah, al [M,K] and bh, bl [N,K], dense, K % 4 == 0.

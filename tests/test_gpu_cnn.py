@@ -143,3 +143,47 @@ def test_large_conv_on_tensor_cores_matches_direct_kernel(ctx, B, iC, H, oC, rel
     if pool:
         want = P.max_pool2d(want)
     assert_close(tensor[:1], want, F32, rtol=1e-5, what="conv vs checker")
+
+
+@pytest.mark.parametrize("B,iC,H,W,oC,k,relu,pool", [
+    (64, 32, 32, 32, 64, 5, True, 0),     # 5x5 filter, four image rows per 128-pixel box
+    (512, 128, 8, 8, 256, 3, True, 0),    # two whole images per box
+    (256, 64, 4, 32, 128, 3, False, 0),   # one image = one box (4 rows of 32)
+    (16, 32, 64, 64, 32, 3, True, 2),     # two rows per box, MaxPool folded into the layout pass
+    (66, 64, 8, 8, 64, 3, True, 0),       # 66 images in boxes of two
+    (65, 64, 8, 8, 64, 3, True, 0),       # an odd image count cannot be boxed: im2col path
+])
+def test_implicit_gemm_conv_geometries(ctx, B, iC, H, W, oC, k, relu, pool):
+    """The implicit-GEMM convolution (shifted 4-D boxes of the NHWC input as k-blocks, zero fill as
+    padding) over the ways 128 output pixels can be cut out of the images, against the direct
+    kernel (bit-exact with the reference) on every output and the CPU checker on the first and
+    last image."""
+    rng = np.random.default_rng(B + iC + H + k)
+    pad = (k - 1) // 2
+    x = rng.standard_normal((B, iC, H, W)).astype(np.float32)
+    w = (rng.standard_normal((oC, iC, k, k)) * np.sqrt(2.0 / (iC * k * k))).astype(np.float32)
+    b = (rng.standard_normal(oC) * 0.1).astype(np.float32)
+    oH, oW = (H // 2, W // 2) if pool else (H, W)
+    outs = []
+    for simt in (True, False):
+        y = empty_dev((B, oC, oH, oW), F32)
+        ctx.force_simt(simt)
+        ctx.conv2d(to_dev(x, F32), to_dev(w, F32), to_dev(b, F32), y, B, iC, H, W, oC, k, 1, pad, F32,
+                   relu=relu, pool=pool)
+        ctx.check()
+        outs.append(to_host(y))
+    ctx.force_simt(False)
+    direct, tensor = outs
+    if B * H * W * oC * iC * k * k >= 2 ** 31:
+        assert not np.array_equal(direct, tensor), "expected the tensor-core path"
+    # float32-class agreement: two summation orders of up to 1152 float products differ by a few
+    # 1e-6 relative; 3e-5 elementwise is a third of the 1e-4 tolerance of the float32 configs
+    assert_close(tensor, direct, F32, rtol=3e-5, what="implicit-GEMM conv vs direct")
+    P = oracle.port()
+    for i in (0, B - 1):
+        want = P.conv2d(x[i:i + 1], w, b, 1, pad)
+        if relu:
+            want = np.maximum(want, 0)
+        if pool:
+            want = P.max_pool2d(want)
+        assert_close(tensor[i:i + 1], want, F32, rtol=3e-5, what="implicit-GEMM conv vs checker")
