@@ -476,7 +476,7 @@ def run_tp(torch, dist, mb, ctx, cfg, dev, stream, timed, args, pk):
                  tp_overlap=None if args.tp_overlap < 0 else bool(args.tp_overlap), tp_exchange=args.tp_exchange)
     eng.load(gpt_decoder_config(V, T, d, H, L), tensors)
     eng.compile((B, T), mb.I32)
-    if args.tp_exchange == "peer":
+    if args.tp_exchange != "nccl":
         eng.attach_peer_via_torch_distributed()
     del tensors
     torch.cuda.empty_cache()
@@ -511,7 +511,15 @@ def run_tp(torch, dist, mb, ctx, cfg, dev, stream, timed, args, pk):
         step_e2e()
     ms_e = timed(step_e2e, k)
     ctx.check()
-    by_kind = summarize_profile(eng.profile(reps=2))
+    prof = eng.profile(reps=2)
+    by_kind = summarize_profile(prof)
+    by_shape = {}
+    for p_ in prof:  # time of the Linear layers by (K, N) of this rank's shard
+        if p_["kind"] == "linear":
+            key = "%dx%d" % (p_["mkn"][1], p_["mkn"][2])
+            e_ = by_shape.setdefault(key, [0, 0.0])
+            e_[0] += 1
+            e_[1] += p_["ms"]
     ar = by_kind.get("all_reduce")
     pr = by_kind.get("peer_reduce")
     rec = {
@@ -520,8 +528,11 @@ def run_tp(torch, dist, mb, ctx, cfg, dev, stream, timed, args, pk):
         "steps": k, "value": B * T * k / (ms / 1e3), "ms_per_step": ms / k, "unit": "tokens/s",
         "e2e_value": B * T * k / (ms_e / 1e3),
         "per_kind_ms": {kk: round(v["ms"], 3) for kk, v in by_kind.items()},
-        "exchange": ("peer memory: fused (mine + peer's partial over NVLink) + bias + residual kernel"
-                     if args.tp_exchange == "peer" else "NCCL all-reduce, then a bias + residual pass"),
+        "linear_ms_by_shape": {kk: {"calls": v[0], "ms_each": round(v[1] / v[0], 4)} for kk, v in by_shape.items()},
+        "exchange": {"peer": "peer memory: fused (mine + peer's partial over NVLink) + bias + residual kernel",
+                     "push": "peer memory: the row-parallel GEMM's epilogue also writes its tiles into the peer's "
+                             "arena over NVLink; (mine + received) + bias + residual kernel on local memory",
+                     "nccl": "NCCL all-reduce, then a bias + residual pass"}[args.tp_exchange],
         "all_reduce": ({"calls": ar["n"], "ms": ar["ms"], "bytes_per_rank": ar["bytes"],
                         "gbs_per_direction": ar["bytes"] / (ar["ms"] / 1e3) / 1e9} if ar and ar["ms"] > 0 else None),
         "peer_reduce": ({"calls": pr["n"], "ms": pr["ms"], "bytes_from_peer": pr["bytes"],
@@ -810,7 +821,7 @@ def main():
                     help="skip the weak / tp2 / configs sub-records (headline measurement only)")
     ap.add_argument("--configs-only", action="store_true", help="print the four smaller workloads and exit")
     ap.add_argument("--config-reps", type=int, default=20)
-    ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--tp-exchange", default="peer", choices=["peer", "push", "nccl"],
                     help="tp2 sub-record: partial sums through peer memory (default) or NCCL all-reduce")
     ap.add_argument("--tp-overlap", type=int, default=-1,
                     help="tp2 sub-record: 1 = exchange of a row chunk under the GEMM of the next; 0 = in order; "

@@ -100,6 +100,9 @@ int run_gemm(mu_ctx *ctx, const mu::GemmOperands &op, const mu::GemmShape &sh, m
       return cuda_fail(ctx, who, cudaGetLastError());
     // rc == 1: shape or alignment outside the TMA kernel's envelope
   }
+  if (ep.c_mirror)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "%s: a mirrored output needs the bfloat16 tensor-core kernel "
+                "(plain [M,N] output, N a multiple of 8, 16-byte aligned rows)", who);
   // Large float32 products: tensor cores with every operand split in two TF32 parts (float32-class
   // accuracy, not the reference's accumulation order). Below 2^31 multiply-adds the CUDA-core
   // kernel keeps the reference's result bit for bit.
@@ -378,6 +381,26 @@ int mu_linear(mu_ctx *ctx, const void *x, const void *w, const void *bias, const
   mu::GemmShape sh{M, N, K, 1};
   mu::Epilogue ep;
   ep.c = y, ep.bias = bias, ep.residual = residual, ep.act = act, ep.ldc = N, ep.round_each = 1;
+  return run_gemm(ctx, op, sh, ep, dtype, static_cast<cudaStream_t>(stream), "linear");
+}
+
+// Used by the executor, not part of the declared ABI: mu_linear whose output tiles are also
+// written to `y_mirror` (same [M,N] layout; may be a peer GPU's memory) from inside the epilogue.
+int mu_linear_mirrored(mu_ctx *ctx, const void *x, const void *w, const void *bias, const void *residual,
+                       void *y, void *y_mirror, int M, int K, int N, int act, int dtype, void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(M >= 0 && K >= 0 && N >= 0, "linear: negative dimension");
+  MU_REQUIRE(act >= MU_ACT_NONE && act <= MU_ACT_TANH, "linear: unknown activation %d", act);
+  if (M == 0 || N == 0)
+    return MU_OK;
+  MU_REQUIRE(x && w && y && y_mirror, "linear: null pointer");
+  mu::GemmOperands op;
+  op.a = x, op.lda = K, op.b = w, op.ldb = N;
+  mu::GemmShape sh{M, N, K, 1};
+  mu::Epilogue ep;
+  ep.c = y, ep.bias = bias, ep.residual = residual, ep.act = act, ep.ldc = N, ep.round_each = 1;
+  ep.c_mirror = y_mirror;
   return run_gemm(ctx, op, sh, ep, dtype, static_cast<cudaStream_t>(stream), "linear");
 }
 

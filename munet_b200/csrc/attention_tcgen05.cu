@@ -838,28 +838,49 @@ attention2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         atomicCAS(status, 0, MU_DEV_TIMEOUT_MMA);
         ok = false;
       };
+      // Operand descriptors are built once; a k-step only adds a constant to the 14-bit start
+      // address field (units of 16 bytes; shared memory is far too small for a carry out of it).
+      uint64_t q_desc[2], k_desc[KS], v_desc[VS];
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+        q_desc[x] = make_smem_desc(smem_u32(sQ + x * Cfg::Q_BYTES), 16, 1024);
+#pragma unroll
+      for (int s = 0; s < KS; ++s)
+        k_desc[s] = LITERAL ? make_smem_desc(smem_u32(sK + s * Cfg::K_BYTES), 8192, 1024)
+                            : make_smem_desc(smem_u32(sK + s * Cfg::K_BYTES), 16, 1024);
+#pragma unroll
+      for (int s = 0; s < VS; ++s)
+        v_desc[s] = make_smem_desc(smem_u32(sV + s * Cfg::V_BYTES), 8192, 1024);
+      auto pick = [](const uint64_t *d, int n, int i) { // d[i] without indexing local memory
+        uint64_t r = d[0];
+#pragma unroll
+        for (int s = 1; s < n; ++s)
+          r = (i == s) ? d[s] : r;
+        return r;
+      };
       // S_x = Q_x · K'(stage)
       auto issue_qk = [&](int x, int stage) {
-        const uint32_t q_addr = smem_u32(sQ + x * Cfg::Q_BYTES);
-        const uint32_t k_addr = smem_u32(sK + stage * Cfg::K_BYTES);
+        const uint64_t qd = x ? q_desc[1] : q_desc[0];
+        const uint64_t kd = pick(k_desc, KS, stage);
+        const uint32_t d_addr = tmem_S + x * BKV;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint64_t ad = make_smem_desc(q_addr + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024);
-          const uint64_t bd =
-              LITERAL ? make_smem_desc(k_addr + (k / 4) * (2 * 8192) + (k % 4) * 2048, 8192, 1024)
-                      : make_smem_desc(k_addr + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
-          umma_f16(tmem_S + x * BKV, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
+          const uint64_t ad = qd + static_cast<uint64_t>(((k / 4) * (BQ * 128) + (k % 4) * 32) >> 4);
+          const uint64_t bd = kd + static_cast<uint64_t>(
+                                       (LITERAL ? (k / 4) * (2 * 8192) + (k % 4) * 2048
+                                                : (k / 4) * (BKV * 128) + (k % 4) * 32) >> 4);
+          umma_f16(d_addr, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[x]);
       };
       // O_x (+)= P_x · V(stage), P_x in tensor memory over the first 64 columns of S_x
       auto issue_pv = [&](int x, int stage, bool accumulate) {
-        const uint32_t v_addr = smem_u32(sV + stage * Cfg::V_BYTES);
+        const uint64_t vd = pick(v_desc, VS, stage);
+        const uint32_t d_addr = tmem_O + x * D, a_addr = tmem_S + x * BKV;
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
-          const uint64_t bd = make_smem_desc(v_addr + (k / 4) * (DB * 8192) + (k % 4) * 2048, 8192, 1024);
-          umma_f16_ts(tmem_O + x * D, tmem_S + x * BKV + k * 8, bd, idesc_pv,
-                      (accumulate || k != 0) ? 1u : 0u);
+          const uint64_t bd = vd + static_cast<uint64_t>(((k / 4) * (DB * 8192) + (k % 4) * 2048) >> 4);
+          umma_f16_ts(d_addr, a_addr + k * 8, bd, idesc_pv, (accumulate || k != 0) ? 1u : 0u);
         }
       };
       WorkIter wit = {0, 0};

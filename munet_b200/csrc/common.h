@@ -31,6 +31,11 @@ struct Epilogue {
   int vec_ok = 0; // host-verified: 16-byte aligned rows/pointers → 128-bit stores allowed
   int tma_out = 0; // tcgen05 kernel: output (and residual) go through staged TMA boxes
   int tma_mode = 0; // coordinate scheme of the output tensor map: 0 plain, 1 merge-heads, 2 split-heads
+  // tcgen05 kernel, plain [M,N] output only: a second copy of every output tile is written here
+  // with ordinary 16-byte stores (whole 128-byte rows). The pointer may map another GPU's
+  // memory: this is how a tensor-parallel rank hands its partial sums to its peer while the
+  // GEMM is still running. Same row stride as c.
+  void *c_mirror = nullptr;
 };
 
 struct GemmShape {

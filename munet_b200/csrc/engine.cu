@@ -39,6 +39,8 @@ int mu_peer_arm(mu_ctx *, void *, unsigned, void *);
 int mu_peer_step(mu_ctx *, void *, void *);
 int mu_peer_signal(mu_ctx *, void *, void *, unsigned, unsigned, void *);
 int mu_peer_wait_done(mu_ctx *, void *, unsigned, unsigned, void *);
+int mu_linear_mirrored(mu_ctx *, const void *, const void *, const void *, const void *, void *, void *, int,
+                       int, int, int, int, void *); // api.cu
 int mu_peer_reduce(mu_ctx *, const void *, const void *, const void *, const void *, void *, long long, int,
                    void *, void *, unsigned, unsigned, unsigned, void *);
 }
@@ -79,6 +81,8 @@ struct Op {
   int side = 0, wait_ev = -1, rec_ev = -1;
   int budget = 0; // GEMM leaves a few SMs to the exchange kernel running beside it
   int xidx = 0;   // peer exchange: number of this exchange within one forward
+  int pin = -1;   // pushed exchange: the buffer of this rank that the PEER's GEMM writes (the GEMM of
+                  // this rank writes the same offset of the peer's arena)
 };
 
 struct Weight {
@@ -269,7 +273,7 @@ struct mu_engine {
   int push(const Op &op) {
     const int idx = static_cast<int>(ops.size());
     ops.push_back(op);
-    for (int t : {op.in, op.res, op.out, op.out2, op.out3, op.ws})
+    for (int t : {op.in, op.res, op.out, op.out2, op.out3, op.ws, op.pin})
       touch(t, idx);
     return idx;
   }
@@ -384,7 +388,12 @@ struct mu_engine {
   int n_events = 0, tp_overlap = 1, tp_comm_sms = 20;
   // tp_exchange 1: partial sums of the row-parallel layers meet through peer memory
   // (peer_reduce.cu) instead of NCCL; needs mu_engine_attach_peer after compile.
+  // tp_exchange 2: the same counters, but the row-parallel GEMM itself writes every output tile
+  // into the peer's memory as well (Epilogue::c_mirror), so the transfer runs under the GEMM and
+  // the reduce kernel reads local memory only. Two receive buffers, used by alternate exchanges,
+  // stay reserved for the whole plan (the peer writes them whenever it is ahead).
   int tp_exchange = 0, peer_exchanges = 0;
+  int peer_in[2] = {-1, -1};
   // The peer reads this rank's partial sums straight out of the arena, so a partial must stay
   // untouched until the peer has signalled that it is done with it — which this rank only waits
   // for before its next row-parallel GEMM. The partial's lifetime in the buffer plan is therefore
@@ -470,6 +479,35 @@ int mu_engine::lower_linear(const std::string &prefix, int K, int N, bool bias, 
     const int rows_per = ((Mtot + chunks - 1) / chunks + 255) / 256 * 256;
     chunks = (Mtot + rows_per - 1) / rows_per;
     std::vector<int> done_ev(chunks, -1);
+    if (tp_exchange == 2) {
+      const int x = peer_exchanges, slot = x & 1;
+      const size_t bytes = static_cast<size_t>(Mtot) * Nl * esize(dtype);
+      if (peer_in[slot] < 0) {
+        peer_in[slot] = new_tensor(bytes);
+        touch(peer_in[slot], 0); // reserved from the first op on
+      } else if (tensors[peer_in[slot]].bytes != bytes) {
+        return fail(MU_ERR_UNSUPPORTED, "Linear '%s': the pushed exchange needs row-parallel outputs of one size",
+                    prefix.c_str());
+      }
+      // the peer's receive buffer `slot` was last read by its reduce of exchange x - 2
+      Op w;
+      w.kind = OP_PEER_WAIT, w.xidx = std::max(0, x - 1);
+      push(w);
+      Op g = op;
+      g.pin = peer_in[slot];
+      push(g);
+      Op sg;
+      sg.kind = OP_PEER_SIGNAL, sg.xidx = x;
+      push(sg);
+      Op r;
+      r.kind = OP_PEER_REDUCE, r.in = op.out, r.pin = peer_in[slot], r.b = bias_id, r.N = Nl, r.res = res_tid;
+      r.out = e_out, r.n = 1ll * Mtot * Nl, r.xidx = x;
+      push(r);
+      ++peer_exchanges;
+      v.tid = e_out;
+      v.shape.back() = Nl;
+      return MU_OK;
+    }
     if (tp_exchange) {
       // peer-memory exchange: GEMM chunk -> "partial complete" to the peer -> fused
       // (mine + peer's) + bias + residual on the second stream
@@ -1025,6 +1063,16 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       n_launches += 1;
       break;
     case OP_LINEAR:
+      if (op.pin >= 0) {
+        if (!peer_arena)
+          return fail(MU_ERR_INVALID, "Engine: the peer exchange needs mu_engine_attach_peer after compile");
+        char *mirror = static_cast<char *>(peer_arena) +
+                       (static_cast<char *>(tptr(op.pin)) - static_cast<char *>(arena));
+        rc = mu_linear_mirrored(ctx, tptr(op.in), wptr(op.w), wptr(op.b), tptr(op.res), tptr(op.out), mirror,
+                                op.M, op.K, op.N, op.act, dtype, st);
+        n_launches += 1;
+        break;
+      }
       rc = mu_linear(ctx, rows(op.in, op.row0, op.K), wptr(op.w), wptr(op.b), rows(op.res, op.row0, op.N),
                      rows(op.out, op.row0, op.N), op.M, op.K, op.N, op.act, dtype, st);
       n_launches += 1;
@@ -1105,7 +1153,8 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       else {
         // both ranks planned the same arena: the peer's partial sits at the same offset in its arena
         const char *a = static_cast<const char *>(rows(op.in, op.row0, op.N));
-        const char *a_peer = static_cast<const char *>(peer_arena) + (a - static_cast<const char *>(arena));
+        const char *a_peer = op.pin >= 0 ? static_cast<const char *>(tptr(op.pin)) // pushed by the peer
+                                         : static_cast<const char *>(peer_arena) + (a - static_cast<const char *>(arena));
         rc = mu_peer_reduce(ctx, a, a_peer, wptr(op.b), rows(op.res, op.row0, op.N), rows(op.out, op.row0, op.N),
                             op.n, op.N, peer_flags_local, peer_flags_remote, per, idx, peer_ctas, st);
       }
@@ -1344,6 +1393,7 @@ int mu_engine::build_plan(const std::vector<int> &shape, int input_dtype) {
   const bool first = weight_slab == nullptr;
   used_params.clear();
   peer_exchanges = 0;
+  peer_in[0] = peer_in[1] = -1;
   if (tp_exchange && tp_size > 1) {
     if (tp_size != 2) return fail(MU_ERR_UNSUPPORTED, "Engine: the peer-memory exchange is built for two ranks");
     if (dtype != MU_BF16) return fail(MU_ERR_UNSUPPORTED, "Engine: the peer-memory exchange is built for bfloat16");
@@ -1381,6 +1431,7 @@ int mu_engine::build_plan(const std::vector<int> &shape, int input_dtype) {
   touch(out_tid, last);
   if (argmax_tid >= 0) touch(argmax_tid, last);
   if (peer_last_partial >= 0) touch(peer_last_partial, last);
+  for (int t : peer_in) touch(t, last);
   rc = plan_and_allocate();
   if (rc) return rc;
   if (tp_exchange && tp_size > 1) {
@@ -1543,7 +1594,7 @@ int mu_engine_peer_info(const mu_engine *e, void **arena, void **counters) {
 int mu_engine_attach_peer(mu_engine *e, void *peer_arena, void *peer_counters) {
   if (!e || !peer_arena || !peer_counters) return MU_ERR_INVALID;
   if (!e->compiled || !e->peer_flags_local)
-    return e->fail(MU_ERR_INVALID, "Engine: attach_peer needs a compiled engine with tp_exchange = 1");
+    return e->fail(MU_ERR_INVALID, "Engine: attach_peer needs a compiled engine with tp_exchange = 1 or 2");
   e->peer_arena = peer_arena, e->peer_flags_remote = peer_counters;
   const int sms = mu_ctx_num_sms(e->ctx);
   // four CTAs of 512 threads per SM: with eight loads each in flight, 20 SMs keep ~5 MB on the wire

@@ -409,6 +409,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               tma_store_5d(&tmC, buf, c0, c1, c2, c3, c4);
               bulk_commit();
             }
+            if (ep.c_mirror) {
+              // second copy of the box (plain [M,N] addressing), read back from the staging rows:
+              // eight lanes cover one 128-byte row, a warp instruction four whole rows. The next
+              // group's writes to this buffer come after a __syncwarp that follows these reads.
+              __nv_bfloat16 *mc = static_cast<__nv_bfloat16 *>(ep.c_mirror);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int idx = i * 32 + lane, r = idx >> 3, cc = idx & 7;
+                const uint4 v = *reinterpret_cast<const uint4 *>(buf + r * 128 + ((cc ^ (r & 7)) << 4));
+                const int m = m0 + r, n = n0 + cc * 8;
+                if (m < sh.M && n < sh.N)
+                  *reinterpret_cast<uint4 *>(mc + 1ll * m * ep.ldc + n) = v;
+              }
+            }
             ++gcount;
           }
         }
@@ -706,6 +720,10 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
   int mode = 0;
   ep2.tma_out = encode_out_maps(ep, sh, &tmC, &tmR, &mode) ? 1 : 0;
   ep2.tma_mode = mode;
+  // the mirrored copy exists only in the staged epilogue of a plain [M,N] output
+  if (ep.c_mirror && (!ep2.tma_out || mode != 0 || sh.batch != 1 || (sh.N % 8) ||
+                      !aligned16(ep.c_mirror)))
+    return 1;
   if (!ep2.tma_out)
     tmC = tmR = tmA; // placeholders, never dereferenced
 

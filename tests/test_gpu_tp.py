@@ -54,13 +54,14 @@ def _worker(rank, world, port, dtype, uid_q, res_q, B=2, T=64, hq=None):
     slabs = []
     # row chunks + exchange on a second stream, then the plain order; through NCCL and (bf16)
     # through peer memory: the two exchanges round the same way, so all four give the same bits
-    modes = [("nccl", True), ("nccl", False)] + ([("peer", True), ("peer", False)] if dtype == BF16 else [])
+    modes = [("nccl", True), ("nccl", False)] + ([("peer", True), ("peer", False), ("push", False)]
+                                                 if dtype == BF16 else [])
     for exchange, overlap in modes:
         eng = Engine(ctx=ctx, compute_dtype=dtype, comm=comm, kmode=mb.K_MATH, tp_overlap=overlap,
                      tp_exchange=exchange)
         eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)), tensor_dtype=dtype)
         eng.compile((B, T), I32)
-        if exchange == "peer":
+        if exchange != "nccl":
             hq[1 - rank].put(eng.peer_handles())
             eng.attach_peer(hq[rank].get(timeout=120))
         slabs.append(eng.run(ids))  # [B, T, V / world]: this rank's vocabulary columns
