@@ -532,6 +532,9 @@ def run_tp(torch, dist, mb, ctx, cfg, dev, stream, timed, args, pk):
         "exchange": {"peer": "peer memory: fused (mine + peer's partial over NVLink) + bias + residual kernel",
                      "push": "peer memory: the row-parallel GEMM's epilogue also writes its tiles into the peer's "
                              "arena over NVLink; (mine + received) + bias + residual kernel on local memory",
+                     "gather": "peer memory: the attention kernel writes its heads' output into both ranks' buffer "
+                               "(out_proj unsharded, no partial sums); the MLP's row-parallel GEMM pushes its tiles "
+                               "into the peer's arena from its epilogue; (mine + received) + bias + residual kernel",
                      "nccl": "NCCL all-reduce, then a bias + residual pass"}[args.tp_exchange],
         "all_reduce": ({"calls": ar["n"], "ms": ar["ms"], "bytes_per_rank": ar["bytes"],
                         "gbs_per_direction": ar["bytes"] / (ar["ms"] / 1e3) / 1e9} if ar and ar["ms"] > 0 else None),
@@ -821,8 +824,9 @@ def main():
                     help="skip the weak / tp2 / configs sub-records (headline measurement only)")
     ap.add_argument("--configs-only", action="store_true", help="print the four smaller workloads and exit")
     ap.add_argument("--config-reps", type=int, default=20)
-    ap.add_argument("--tp-exchange", default="peer", choices=["peer", "push", "nccl"],
-                    help="tp2 sub-record: partial sums through peer memory (default) or NCCL all-reduce")
+    ap.add_argument("--tp-exchange", default="gather", choices=["gather", "push", "peer", "nccl"],
+                    help="tp2 sub-record: how the two ranks exchange (default: attention output and MLP partial "
+                         "sums pushed into the peer's memory from inside the producing kernels)")
     ap.add_argument("--tp-overlap", type=int, default=-1,
                     help="tp2 sub-record: 1 = exchange of a row chunk under the GEMM of the next; 0 = in order; "
                          "-1 = the exchange's own default")

@@ -29,6 +29,8 @@ int launch_gemm_tf32x3(const float *, long long, const float *, long long, int, 
                        cudaStream_t);
 int launch_attention_tcgen05(const void *, const void *, const void *, void *, int, int, int, int,
                              int, int, int *, cudaStream_t);
+int launch_attention_tcgen05_ex(const void *, const void *, const void *, void *, long long, void *, int, int,
+                                int, int, int, int, int *, cudaStream_t);
 void set_attention_variant(int);
 } // namespace mu
 
@@ -487,6 +489,32 @@ size_t mu_attention_workspace_bytes(int B, int H, int T, int D, int dtype) {
     return 0;
   // composed path: one [B*H, T, T] score/probability buffer (softmax runs in place)
   return mu_attention_workspace_bytes_composed(B, H, T, D, dtype);
+}
+
+// Used by the executor, not part of the declared ABI: the fused attention kernel writing its
+// [B*T, H*D] output with row stride `out_ld` (a column slab of a wider tensor) and, from inside the
+// kernel, a second copy to `out_mirror` (same layout; may be a peer GPU's memory). bfloat16 and
+// head sizes 64 / 128 only: there is no composed path behind it.
+int mu_attention_mirrored(mu_ctx *ctx, const void *q, const void *k, const void *v, void *out, long long out_ld,
+                          void *out_mirror, int B, int H, int T, int D, int causal, int kmode, int dtype,
+                          void *stream) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  MU_REQUIRE(B > 0 && H > 0 && T > 0 && D > 0 && q && k && v && out, "attention: bad arguments");
+  MU_REQUIRE(kmode == MU_K_LITERAL || kmode == MU_K_MATH, "attention: unknown kmode %d", kmode);
+  if (dtype != MU_BF16 || ctx->force_simt)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "attention with a mirrored output needs the bfloat16 tensor-core kernel");
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "attention: cannot select device %d", ctx->device);
+  const int rc = mu::launch_attention_tcgen05_ex(q, k, v, out, out_ld, out_mirror, B, H, T, D, causal,
+                                                 kmode == MU_K_LITERAL ? 1 : 0, ctx->d_status,
+                                                 static_cast<cudaStream_t>(stream));
+  if (rc == 2)
+    return cuda_fail(ctx, "attention", cudaGetLastError());
+  if (rc)
+    return fail(ctx, MU_ERR_UNSUPPORTED, "attention with a mirrored output: head size %d, T %d or the "
+                "alignment is outside the fused kernel's envelope", D, T);
+  return MU_OK;
 }
 
 int mu_attention(mu_ctx *ctx, const void *q, const void *k, const void *v, void *out, int B, int H,

@@ -58,6 +58,12 @@ struct AttParams {
   int n_qtiles;
   int chunk_heads; // heads whose K and V are worked on together (sized to stay in L2)
   int chunk_rot;   // rotation of the CTA deal from one chunk to the next
+  // Two-query-tile kernel only: every output tile is also written, with ordinary 16-byte stores,
+  // to mirror[(b*T + t) * out_ld + h*D + d] (null = off). The pointer may map another GPU's
+  // memory: a tensor-parallel rank hands the output of its heads to its peer from inside the
+  // kernel.
+  __nv_bfloat16 *mirror;
+  long long out_ld; // row stride of the output in elements (>= H*D)
 };
 
 template <int D, bool LITERAL>
@@ -1128,16 +1134,35 @@ attention2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
         tc_fence_before();
         fence_proxy_async();
         __syncwarp();
+        const int bb = wk.bh / prm.H, hh = wk.bh % prm.H;
         if (lane == 0) {
           mbar_arrive(&o_free[x]); // O_x may be overwritten by the next work
           if (q0 + q * 32 < prm.T) {
-            const int bb = wk.bh / prm.H, hh = wk.bh % prm.H;
 #pragma unroll
             for (int db = 0; db < DB; ++db)
               tma_store_5d(&tmO, sStg + db * (BQ * 128) + q * 32 * 128, db * 64, hh, q0 + q * 32, bb, 0);
             bulk_commit();
-            bulk_wait_read<0>();
           }
+        }
+        if (prm.mirror) {
+          // second copy of this warp's 32 rows, read back from the staging tile: eight lanes
+          // cover one 128-byte row segment, a warp instruction four of them
+#pragma unroll
+          for (int db = 0; db < DB; ++db)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int idx = i * 32 + lane, r = idx >> 3, cc = idx & 7;
+              const int t = q0 + q * 32 + r;
+              const uint4 val = *reinterpret_cast<const uint4 *>(sStg + db * (BQ * 128) + (q * 32 + r) * 128 +
+                                                                 ((cc ^ (r & 7)) << 4));
+              if (t < prm.T)
+                *reinterpret_cast<uint4 *>(prm.mirror + (1ll * bb * prm.T + t) * prm.out_ld + hh * D +
+                                           db * 64 + cc * 8) = val;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          bulk_wait_read<0>();
           mbar_arrive(stg_done);
         }
         __syncwarp();
@@ -1199,17 +1224,25 @@ static int g_attention_variant = 0;
 void set_attention_variant(int v) { g_attention_variant = v; }
 
 // Returns 0 ok, 1 shape/alignment outside this kernel's envelope, 2 launch failure.
-int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *out, int B, int H,
-                             int T, int D, int causal, int literal, int *status,
-                             cudaStream_t stream) {
+// out_ld: row stride of the [B*T, H*D] output in elements (0 = dense); mirror: optional second
+// destination with the same layout (two-query-tile kernel only).
+int launch_attention_tcgen05_ex(const void *q, const void *k, const void *v, void *out, long long out_ld,
+                                void *mirror, int B, int H, int T, int D, int causal, int literal,
+                                int *status, cudaStream_t stream) {
   auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
   if ((D != 64 && D != 128) || T <= 0 || B <= 0 || H <= 0)
     return 1;
-  if (!al(q) || !al(k) || !al(v) || !al(out))
+  if (!al(q) || !al(k) || !al(v) || !al(out) || !al(mirror))
+    return 1;
+  if (out_ld == 0)
+    out_ld = 1ll * H * D;
+  if (out_ld < 1ll * H * D || (out_ld % 8))
+    return 1;
+  if (mirror && g_attention_variant == 1)
     return 1;
   if (literal && (T % 8))
     return 1; // column offset bh*T must stay 16-byte aligned
-  const unsigned long long BH = 1ull * B * H, uT = T, uD = D, Ntot = BH * uT, E = 1ull * H * D;
+  const unsigned long long BH = 1ull * B * H, uT = T, uD = D, Ntot = BH * uT;
   if (Ntot > 0x7fffffffull)
     return 1;
   CUtensorMap tmQ, tmK, tmV, tmO;
@@ -1234,7 +1267,8 @@ int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *
     // out[b][t][h][d], dimensions by ascending stride: d, h, t, b
     const unsigned long long d[5] = {uD, static_cast<unsigned long long>(H), uT,
                                      static_cast<unsigned long long>(B), 1};
-    const unsigned long long st[4] = {uD, E, uT * E, uT * E * B};
+    const unsigned long long ld = static_cast<unsigned long long>(out_ld);
+    const unsigned long long st[4] = {uD, ld, uT * ld, uT * ld * B};
     const unsigned bx[5] = {64, 1, 32, 1, 1};
     if (!att_map(&tmO, out, 5, d, st, bx))
       return 2;
@@ -1243,6 +1277,7 @@ int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *
   prm.T = T, prm.H = H, prm.BH = static_cast<int>(BH), prm.causal = causal;
   prm.scale = 1.0f / sqrtf(static_cast<float>(D));
   prm.n_qtiles = (T + BQ - 1) / BQ;
+  prm.mirror = static_cast<__nv_bfloat16 *>(mirror), prm.out_ld = out_ld;
   {
     // K and V of one head are 4*T*D bytes; a chunk of heads is kept to about 64 MB, half of L2
     const unsigned long long per_head = 4ull * uT * uD;
@@ -1314,6 +1349,12 @@ int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *
   }
 #undef MU_ATT_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : 2;
+}
+
+int launch_attention_tcgen05(const void *q, const void *k, const void *v, void *out, int B, int H,
+                             int T, int D, int causal, int literal, int *status,
+                             cudaStream_t stream) {
+  return launch_attention_tcgen05_ex(q, k, v, out, 0, nullptr, B, H, T, D, causal, literal, status, stream);
 }
 
 } // namespace mu

@@ -43,6 +43,10 @@ int mu_linear_mirrored(mu_ctx *, const void *, const void *, const void *, const
                        int, int, int, int, void *); // api.cu
 int mu_peer_reduce(mu_ctx *, const void *, const void *, const void *, const void *, void *, long long, int,
                    void *, void *, unsigned, unsigned, unsigned, void *);
+int mu_peer_wait_ready(mu_ctx *, void *, unsigned, unsigned, void *);
+int mu_peer_signal_done(mu_ctx *, void *, void *, unsigned, unsigned, void *);
+int mu_attention_mirrored(mu_ctx *, const void *, const void *, const void *, void *, long long, void *, int,
+                          int, int, int, int, int, int, void *); // api.cu
 }
 
 namespace {
@@ -53,7 +57,10 @@ enum OpKind {
   // tensor-parallel exchange over peer memory (peer_reduce.cu): start of a forward, "the peer has
   // read my earlier partials", "my partial is complete", the fused sum + bias + residual, and a
   // kernel-less op that only joins the second stream back into the main one
-  OP_PEER_STEP, OP_PEER_WAIT, OP_PEER_SIGNAL, OP_PEER_REDUCE, OP_JOIN
+  OP_PEER_STEP, OP_PEER_WAIT, OP_PEER_SIGNAL, OP_PEER_REDUCE, OP_JOIN,
+  // gathered attention (tp_exchange 3): "what the peer pushed for this exchange has arrived" and
+  // "I have consumed it" (the reduce kernel of the other exchanges says the latter itself)
+  OP_PEER_WAITRDY, OP_PEER_SIGDONE
 };
 
 struct Tensor {
@@ -392,6 +399,10 @@ struct mu_engine {
   // into the peer's memory as well (Epilogue::c_mirror), so the transfer runs under the GEMM and
   // the reduce kernel reads local memory only. Two receive buffers, used by alternate exchanges,
   // stay reserved for the whole plan (the peer writes them whenever it is ahead).
+  // tp_exchange 3: as 2, and the attention sub-block exchanges the attention OUTPUT instead of
+  // out_proj's partial sums: the attention kernel writes the columns of this rank's heads into
+  // both ranks' [tokens, E] buffer, out_proj then runs unsharded on every rank with bias and
+  // residual in its epilogue. Half the bytes cross the link and no reduce kernel follows.
   int tp_exchange = 0, peer_exchanges = 0;
   int peer_in[2] = {-1, -1};
   // The peer reads this rank's partial sums straight out of the arena, so a partial must stay
@@ -479,7 +490,7 @@ int mu_engine::lower_linear(const std::string &prefix, int K, int N, bool bias, 
     const int rows_per = ((Mtot + chunks - 1) / chunks + 255) / 256 * 256;
     chunks = (Mtot + rows_per - 1) / rows_per;
     std::vector<int> done_ev(chunks, -1);
-    if (tp_exchange == 2) {
+    if (tp_exchange >= 2) {
       const int x = peer_exchanges, slot = x & 1;
       const size_t bytes = static_cast<size_t>(Mtot) * Nl * esize(dtype);
       if (peer_in[slot] < 0) {
@@ -628,6 +639,40 @@ int mu_engine::lower_mha(const std::string &prefix, int E, int H, bool causal, i
   a.ws_bytes = mu_ctx_simt_forced(ctx) ? mu_attention_workspace_bytes_composed(B, H, T, D, dtype)
                                        : mu_attention_workspace_bytes(B, H, T, D, dtype);
   a.ws = new_tensor(a.ws_bytes);
+  if (tp && tp_exchange == 3) {
+    // gathered attention: this rank's heads are columns [tp_rank*El, +El) of a [tokens, E] buffer
+    // that exists on both ranks; the kernel writes them here and into the peer's copy
+    const int x = peer_exchanges, slot = x & 1;
+    const size_t bytes = static_cast<size_t>(B) * T * E * esize(dtype);
+    if (peer_in[slot] < 0) {
+      peer_in[slot] = new_tensor(bytes);
+      touch(peer_in[slot], 0); // reserved from the first op on
+    } else if (tensors[peer_in[slot]].bytes != bytes) {
+      return fail(MU_ERR_UNSUPPORTED, "MultiHeadAttention '%s': the gathered exchange needs buffers of one size",
+                  prefix.c_str());
+    }
+    Op w;
+    w.kind = OP_PEER_WAIT, w.xidx = std::max(0, x - 1); // the peer has consumed exchange x - 2
+    push(w);
+    a.out = peer_in[slot], a.pin = peer_in[slot];
+    a.N = E, a.K = tp_rank * El; // row stride and first column of this rank's heads
+    push(a);
+    Op sg;
+    sg.kind = OP_PEER_SIGNAL, sg.xidx = x;
+    push(sg);
+    Op wr;
+    wr.kind = OP_PEER_WAITRDY, wr.xidx = x;
+    push(wr);
+    ++peer_exchanges;
+    v.tid = peer_in[slot];
+    v.shape = {B * T, E};
+    int rc = lower_linear(prefix + "out_proj.", E, E, true, MU_ACT_NONE, res_tid, v, 0);
+    Op sd;
+    sd.kind = OP_PEER_SIGDONE, sd.xidx = x, sd.in = peer_in[slot];
+    push(sd);
+    v.shape = {B, T, E};
+    return rc;
+  }
   a.out = new_tensor(per);
   push(a);
   v.tid = a.out;
@@ -1088,6 +1133,16 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
     case OP_ATTN: {
       char *base = static_cast<char *>(tptr(op.in));
       const size_t per = static_cast<size_t>(op.B) * op.T * op.H * op.D * esize(dtype);
+      if (op.pin >= 0) {
+        if (!peer_arena)
+          return fail(MU_ERR_INVALID, "Engine: the peer exchange needs mu_engine_attach_peer after compile");
+        char *mine = static_cast<char *>(tptr(op.pin)) + static_cast<size_t>(op.K) * esize(dtype);
+        char *theirs = static_cast<char *>(peer_arena) + (mine - static_cast<char *>(arena));
+        rc = mu_attention_mirrored(ctx, base, base + per, base + 2 * per, mine, op.N, theirs, op.B, op.H, op.T,
+                                   op.D, op.causal, kmode, dtype, st);
+        n_launches += 1;
+        break;
+      }
       rc = mu_attention(ctx, base, base + per, base + 2 * per, tptr(op.out), op.B, op.H, op.T, op.D,
                         op.causal, kmode, dtype, tptr(op.ws), op.ws_bytes, st);
       n_launches += 3;
@@ -1143,6 +1198,8 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
     case OP_PEER_STEP:
     case OP_PEER_WAIT:
     case OP_PEER_SIGNAL:
+    case OP_PEER_WAITRDY:
+    case OP_PEER_SIGDONE:
     case OP_PEER_REDUCE: {
       if (!peer_arena || !peer_flags_remote)
         return fail(MU_ERR_INVALID, "Engine: the peer exchange needs mu_engine_attach_peer after compile");
@@ -1150,6 +1207,8 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       if (op.kind == OP_PEER_STEP) rc = mu_peer_step(ctx, peer_flags_local, st);
       else if (op.kind == OP_PEER_WAIT) rc = mu_peer_wait_done(ctx, peer_flags_local, per, idx, st);
       else if (op.kind == OP_PEER_SIGNAL) rc = mu_peer_signal(ctx, peer_flags_local, peer_flags_remote, per, idx, st);
+      else if (op.kind == OP_PEER_WAITRDY) rc = mu_peer_wait_ready(ctx, peer_flags_local, per, idx, st);
+      else if (op.kind == OP_PEER_SIGDONE) rc = mu_peer_signal_done(ctx, peer_flags_local, peer_flags_remote, per, idx, st);
       else {
         // both ranks planned the same arena: the peer's partial sits at the same offset in its arena
         const char *a = static_cast<const char *>(rows(op.in, op.row0, op.N));

@@ -74,6 +74,20 @@ __global__ void peer_wait_done_kernel(const PeerFlags *mine, unsigned per_step, 
     atomicCAS(status, 0, MU_DEV_TIMEOUT_OTHER);
 }
 
+// One thread, before a kernel reads what the peer pushed for exchange `index`: the peer's READY.
+__global__ void peer_wait_ready_kernel(const PeerFlags *mine, unsigned per_step, unsigned index, int *status) {
+  const unsigned long long want = (mine->step - 1) * per_step + index + 1;
+  if (!wait_at_least(&mine->ready, want))
+    atomicCAS(status, 0, MU_DEV_TIMEOUT_OTHER);
+}
+
+// One thread, after the kernel that consumed what the peer pushed for exchange `index`: the peer may
+// overwrite that receive buffer (exchanges without a reduce kernel, which otherwise writes DONE).
+__global__ void peer_signal_done_kernel(const PeerFlags *mine, PeerFlags *peer, unsigned per_step, unsigned index) {
+  __threadfence_system();
+  st_release_sys(&peer->done, (mine->step - 1) * per_step + index + 1);
+}
+
 // y = bf16(bf16(bf16(a + a_peer) + bias[col]) + residual), n elements, `cols` per row, 8 elements
 // per thread and step. bias / residual may be null. y may alias residual (in-place residual stream).
 __global__ void __launch_bounds__(512)
@@ -226,6 +240,20 @@ int mu_peer_wait_done(mu_ctx *ctx, void *flags, unsigned per_step, unsigned inde
     return MU_ERR_CUDA;
   mu::peer_wait_done_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const mu::PeerFlags *>(flags), per_step, index, mu_ctx_status_ptr(ctx));
+  return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_CUDA;
+}
+int mu_peer_wait_ready(mu_ctx *ctx, void *flags, unsigned per_step, unsigned index, void *stream) {
+  if (mu_ctx_select_device(ctx) != MU_OK)
+    return MU_ERR_CUDA;
+  mu::peer_wait_ready_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const mu::PeerFlags *>(flags), per_step, index, mu_ctx_status_ptr(ctx));
+  return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_CUDA;
+}
+int mu_peer_signal_done(mu_ctx *ctx, void *flags, void *peer_flags, unsigned per_step, unsigned index, void *stream) {
+  if (mu_ctx_select_device(ctx) != MU_OK)
+    return MU_ERR_CUDA;
+  mu::peer_signal_done_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const mu::PeerFlags *>(flags), static_cast<mu::PeerFlags *>(peer_flags), per_step, index);
   return cudaGetLastError() == cudaSuccess ? MU_OK : MU_ERR_CUDA;
 }
 // n elements of bf16 (n and cols multiples of 8, pointers 16-byte aligned); `ctas` = the grid
