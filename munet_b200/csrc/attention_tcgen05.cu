@@ -649,7 +649,9 @@ template <int D> struct Att2Cfg {
   static constexpr int TMEM_COLS = 512;
 };
 
-template <int D, bool LITERAL>
+// MIRROR: the second copy of the output (AttParams::mirror) is compiled in; a separate
+// instantiation so that the plain kernel keeps its register allocation.
+template <int D, bool LITERAL, bool MIRROR>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attention2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
                           const __grid_constant__ CUtensorMap tmK,
@@ -1144,7 +1146,7 @@ attention2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmQ,
             bulk_commit();
           }
         }
-        if (prm.mirror) {
+        if (MIRROR && prm.mirror) {
           // second copy of this warp's 32 rows, read back from the staging tile: eight lanes
           // cover one 128-byte row segment, a warp instruction four of them
 #pragma unroll
@@ -1294,9 +1296,9 @@ int launch_attention_tcgen05_ex(const void *q, const void *k, const void *v, voi
   const unsigned long long n_works = BH * (two_tiles ? (prm.n_qtiles + 1) / 2 : prm.n_qtiles);
   dim3 grid(static_cast<unsigned>(n_works < static_cast<unsigned long long>(num_sms) ? n_works : num_sms));
 
-#define MU_ATT2_LAUNCH(D_, L_)                                                                   \
+#define MU_ATT2_LAUNCH_M(D_, L_, M_)                                                             \
   do {                                                                                           \
-    auto kern = attention2_tcgen05_kernel<D_, L_>;                                               \
+    auto kern = attention2_tcgen05_kernel<D_, L_, M_>;                                           \
     static PerDeviceOnce attr_set;                                                               \
     if (attr_set.get() < 0) {                                                                    \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
@@ -1306,7 +1308,17 @@ int launch_attention_tcgen05_ex(const void *q, const void *k, const void *v, voi
     }                                                                                            \
     kern<<<grid, ATT_THREADS, Att2Cfg<D_>::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, prm, status); \
   } while (0)
+#define MU_ATT2_LAUNCH(D_, L_) MU_ATT2_LAUNCH_M(D_, L_, false)
 
+  if (two_tiles && mirror) { // tensor-parallel path: true Q·K' only (literal addressing is not sharded)
+    if (literal)
+      return 1;
+    if (D == 128)
+      MU_ATT2_LAUNCH_M(128, false, true);
+    else
+      MU_ATT2_LAUNCH_M(64, false, true);
+    return cudaGetLastError() == cudaSuccess ? 0 : 2;
+  }
   if (two_tiles) {
     if (D == 128) {
       if (literal)
@@ -1320,6 +1332,7 @@ int launch_attention_tcgen05_ex(const void *q, const void *k, const void *v, voi
         MU_ATT2_LAUNCH(64, false);
     }
 #undef MU_ATT2_LAUNCH
+#undef MU_ATT2_LAUNCH_M
     return cudaGetLastError() == cudaSuccess ? 0 : 2;
   }
 
