@@ -535,6 +535,10 @@ def run_tp(torch, dist, mb, ctx, cfg, dev, stream, timed, args, pk):
                      "gather": "peer memory: the attention kernel writes its heads' output into both ranks' buffer "
                                "(out_proj unsharded, no partial sums); the MLP's row-parallel GEMM pushes its tiles "
                                "into the peer's arena from its epilogue; (mine + received) + bias + residual kernel",
+                     "rows": "peer memory: attention output written into both ranks' buffer by the attention kernel; "
+                             "out_proj on this rank's half of the token rows, its epilogue writing them into both "
+                             "ranks' residual stream; the MLP's row-parallel GEMM pushes its tiles into the peer's "
+                             "arena; (mine + received) + bias + residual kernel",
                      "nccl": "NCCL all-reduce, then a bias + residual pass"}[args.tp_exchange],
         "all_reduce": ({"calls": ar["n"], "ms": ar["ms"], "bytes_per_rank": ar["bytes"],
                         "gbs_per_direction": ar["bytes"] / (ar["ms"] / 1e3) / 1e9} if ar and ar["ms"] > 0 else None),
@@ -824,7 +828,7 @@ def main():
                     help="skip the weak / tp2 / configs sub-records (headline measurement only)")
     ap.add_argument("--configs-only", action="store_true", help="print the four smaller workloads and exit")
     ap.add_argument("--config-reps", type=int, default=20)
-    ap.add_argument("--tp-exchange", default="gather", choices=["gather", "push", "peer", "nccl"],
+    ap.add_argument("--tp-exchange", default="rows", choices=["rows", "gather", "push", "peer", "nccl"],
                     help="tp2 sub-record: how the two ranks exchange (default: attention output and MLP partial "
                          "sums pushed into the peer's memory from inside the producing kernels)")
     ap.add_argument("--tp-overlap", type=int, default=-1,

@@ -384,7 +384,9 @@ struct mu_engine {
   int lower(const Json &node, const std::string &prefix, Val &v, const Json *next, bool *fused_next,
             const Json *next2 = nullptr, int *fused_count = nullptr);
   // par: 0 replicated, 1 column-parallel (this rank's slice of the outputs), 2 row-parallel
-  // (this rank's slice of the inputs; partial sums are all-reduced, then bias/residual)
+  // (this rank's slice of the inputs; partial sums are all-reduced, then bias/residual),
+  // 3 replicated weights, token rows split: this rank computes its half of the rows and the
+  // epilogue also writes them into the peer's copy of the output (two ranks, peer exchange)
   int lower_linear(const std::string &prefix, int K, int N, bool bias, int act, int res_tid, Val &v,
                    int par = 0);
   int lower_mha(const std::string &prefix, int E, int H, bool causal, int res_tid, Val &v,
@@ -491,6 +493,7 @@ int mu_engine::lower_linear(const std::string &prefix, int K, int N, bool bias, 
     chunks = (Mtot + rows_per - 1) / rows_per;
     std::vector<int> done_ev(chunks, -1);
     if (tp_exchange >= 2) {
+      // receive buffers are handed out by a count of their own: some exchanges use none
       const int x = peer_exchanges, slot = x & 1;
       const size_t bytes = static_cast<size_t>(Mtot) * Nl * esize(dtype);
       if (peer_in[slot] < 0) {
@@ -593,6 +596,11 @@ int mu_engine::lower_linear(const std::string &prefix, int K, int N, bool bias, 
   } else {
     op.out = new_tensor(static_cast<size_t>(op.M) * Nl * esize(dtype));
   }
+  if (par == 3 && tp_size == 2 && op.M % 2 == 0) {
+    const int half = op.M / 2;
+    op.row0 = 1ll * tp_rank * half, op.M = half;
+    op.pin = op.out; // the same rows of the peer's copy
+  }
   push(op);
   v.tid = op.out;
   v.shape.back() = Nl;
@@ -639,7 +647,7 @@ int mu_engine::lower_mha(const std::string &prefix, int E, int H, bool causal, i
   a.ws_bytes = mu_ctx_simt_forced(ctx) ? mu_attention_workspace_bytes_composed(B, H, T, D, dtype)
                                        : mu_attention_workspace_bytes(B, H, T, D, dtype);
   a.ws = new_tensor(a.ws_bytes);
-  if (tp && tp_exchange == 3) {
+  if (tp && tp_exchange >= 3) {
     // gathered attention: this rank's heads are columns [tp_rank*El, +El) of a [tokens, E] buffer
     // that exists on both ranks; the kernel writes them here and into the peer's copy
     const int x = peer_exchanges, slot = x & 1;
@@ -666,10 +674,27 @@ int mu_engine::lower_mha(const std::string &prefix, int E, int H, bool causal, i
     ++peer_exchanges;
     v.tid = peer_in[slot];
     v.shape = {B * T, E};
-    int rc = lower_linear(prefix + "out_proj.", E, E, true, MU_ACT_NONE, res_tid, v, 0);
+    const bool split_rows = tp_exchange == 4 && (B * T) % 2 == 0 && res_tid >= 0;
+    int rc = lower_linear(prefix + "out_proj.", E, E, true, MU_ACT_NONE, res_tid, v, split_rows ? 3 : 0);
     Op sd;
     sd.kind = OP_PEER_SIGDONE, sd.xidx = x, sd.in = peer_in[slot];
     push(sd);
+    if (split_rows && rc == MU_OK) {
+      // out_proj ran on this rank's half of the token rows and wrote them into both copies of
+      // the residual stream; the other half arrives from the peer. That stream is live on both
+      // ranks from the embedding to the last layer, at the same arena offset, and the peer can
+      // only write it between this rank's attention kernel (its READY) and this wait, when
+      // nothing here reads those rows.
+      const int x1 = peer_exchanges;
+      Op s1, w1, d1;
+      s1.kind = OP_PEER_SIGNAL, s1.xidx = x1, s1.in = v.tid;
+      w1.kind = OP_PEER_WAITRDY, w1.xidx = x1, w1.in = v.tid;
+      d1.kind = OP_PEER_SIGDONE, d1.xidx = x1, d1.in = v.tid;
+      push(s1);
+      push(w1);
+      push(d1);
+      ++peer_exchanges;
+    }
     v.shape = {B, T, E};
     return rc;
   }
@@ -1112,9 +1137,10 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
         if (!peer_arena)
           return fail(MU_ERR_INVALID, "Engine: the peer exchange needs mu_engine_attach_peer after compile");
         char *mirror = static_cast<char *>(peer_arena) +
-                       (static_cast<char *>(tptr(op.pin)) - static_cast<char *>(arena));
-        rc = mu_linear_mirrored(ctx, tptr(op.in), wptr(op.w), wptr(op.b), tptr(op.res), tptr(op.out), mirror,
-                                op.M, op.K, op.N, op.act, dtype, st);
+                       (static_cast<char *>(rows(op.pin, op.row0, op.N)) - static_cast<char *>(arena));
+        rc = mu_linear_mirrored(ctx, rows(op.in, op.row0, op.K), wptr(op.w), wptr(op.b),
+                                rows(op.res, op.row0, op.N), rows(op.out, op.row0, op.N), mirror, op.M, op.K,
+                                op.N, op.act, dtype, st);
         n_launches += 1;
         break;
       }

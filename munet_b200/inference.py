@@ -181,19 +181,21 @@ class Engine:
         if comm is not None and comm.world > 1:  # tensor-parallel shard of the decoder blocks
             self._opt("tp_size", comm.world)
             self._opt("tp_rank", comm.rank)
-            if tp_exchange not in ("nccl", "peer", "push", "gather"):
-                raise ValueError("tp_exchange is 'nccl', 'peer', 'push' or 'gather'")
+            if tp_exchange not in ("nccl", "peer", "push", "gather", "rows"):
+                raise ValueError("tp_exchange is 'nccl', 'peer', 'push', 'gather' or 'rows'")
             # row chunks with the exchange of one under the GEMM of the next pay off for the NCCL
             # path (measured 105.5 against 108.6 ms on the 24-layer decoder) but not for the
             # peer-memory one, whose kernel wants every SM for its NVLink loads (93.6 against 96.4)
-            if tp_overlap is None or tp_exchange in ("push", "gather"):  # the pushed exchanges are never chunked
+            if tp_overlap is None or tp_exchange in ("push", "gather", "rows"):  # the pushed exchanges are never chunked
                 tp_overlap = tp_exchange == "nccl"
             self._opt("tp_overlap", int(tp_overlap))
             # "peer": the reduce kernel loads the other rank's partial over NVLink; "push": the
             # row-parallel GEMM writes its tiles into the other rank's memory while it runs;
             # "gather": as "push" for the MLP, and the attention kernel writes its heads' output
-            # into both ranks' buffer so that out_proj runs unsharded (no partial sums to add)
-            self._opt("tp_exchange", {"nccl": 0, "peer": 1, "push": 2, "gather": 3}[tp_exchange])
+            # into both ranks' buffer so that out_proj runs unsharded (no partial sums to add);
+            # "rows": as "gather", but each rank runs out_proj on its half of the token rows only
+            # and its epilogue writes them into both ranks' residual stream
+            self._opt("tp_exchange", {"nccl": 0, "peer": 1, "push": 2, "gather": 3, "rows": 4}[tp_exchange])
             self._rc(self._lib.mu_engine_set_comm(self._h, comm._h))
         self.tp_exchange = tp_exchange if (comm is not None and comm.world > 1) else "nccl"
         self._peer_maps = []

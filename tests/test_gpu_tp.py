@@ -82,6 +82,16 @@ def _worker(rank, world, port, dtype, uid_q, res_q, B=2, T=64, hq=None):
         gathered = eng.run(ids)
         assert np.array_equal(gathered, eng.run(ids))
         eng.close()
+        # the same with out_proj on this rank's half of the token rows (mirrored into the peer's
+        # residual stream): every output row is computed by the same arithmetic, so the bits match
+        eng = Engine(ctx=ctx, compute_dtype=dtype, comm=comm, kmode=mb.K_MATH, tp_exchange="rows")
+        eng.load(gpt_decoder_config(V, T, d, H, L), dict(zip(gpt_param_names(L), ps)), tensor_dtype=dtype)
+        eng.compile((B, T), I32)
+        hq[1 - rank].put(eng.peer_handles())
+        eng.attach_peer(hq[rank].get(timeout=120))
+        assert np.array_equal(gathered, eng.run(ids))
+        assert np.array_equal(gathered, eng.run(ids))
+        eng.close()
     res_q.put((rank, red, slabs[0], gathered))
     comm.close()
     ctx.close()
