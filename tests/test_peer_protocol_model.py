@@ -1,6 +1,6 @@
 """Model check of the READY / DONE counter protocol of the peer-memory exchanges.
 
-The executor (munet_b200/csrc/engine.cu, lower_linear / lower_mha with tp_exchange 2 and 3) emits,
+The executor (munet_b200/csrc/engine.cu, lower_linear / lower_mha with tp_exchange 2 to 4) emits,
 for exchange number x of a forward, on BOTH ranks:
 
     wait  DONE  >= seq(x) - 2      the peer has consumed what last sat in receive buffer x & 1
