@@ -693,8 +693,9 @@ def run_configs(torch, mb, reps=20, pk=None, which=("mlp", "linear_sweep", "cnn"
         ms = _time_engine(torch, mb, eng, ids, reps)
         tok = B * T
         fl = tok * (L * (2 * 4 * d * d + 2 * 8 * d * d) + 2 * d * V) + L * B * H * 2 * T * T * (d // H)
-        rec("gpt_s bf16 B32 T256", ms, fl, 0, tok, "tokens", "tensor_bf16", eng.stats()["n_launches"],
-            "attention FLOPs counted causal-useful; 58 launches in ~1 ms: launch-latency bound")
+        nl = eng.stats()["n_launches"]
+        rec("gpt_s bf16 B32 T256", ms, fl, 0, tok, "tokens", "tensor_bf16", nl,
+            "attention FLOPs counted causal-useful; %d launches in ~1 ms: launch-latency bound" % nl)
         eng.close()
     return out
 

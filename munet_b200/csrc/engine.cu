@@ -1171,7 +1171,7 @@ int mu_engine::launch_op(const Op &op, cudaStream_t st) {
       }
       rc = mu_attention(ctx, base, base + per, base + 2 * per, tptr(op.out), op.B, op.H, op.T, op.D,
                         op.causal, kmode, dtype, tptr(op.ws), op.ws_bytes, st);
-      n_launches += 3;
+      n_launches += op.ws_bytes ? 3 : 1; // composed path: scores, softmax, context; fused: one kernel
       break;
     }
     case OP_ELTWISE:
