@@ -563,17 +563,27 @@ def _time_engine(torch, mb, eng, x, reps):
         rc = lib.mu_engine_run(eng._h, x.data_ptr(), 0, None, 0, None, 0, stream.cuda_stream)
         if rc:
             raise mb.MuNetError(rc, lib.mu_engine_last_error(eng._h).decode())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(n):
+        e0.record()
+        for _ in range(n):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
     for _ in range(3):
         run()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        run()
-    e1.record()
-    torch.cuda.synchronize()
+    # Sub-millisecond workloads: a GPU that has just idled (the CPU baseline runs before this)
+    # needs tens of milliseconds of work to come back to its running clock, so warm up for
+    # about 30 ms and time at least that long.
+    est = max(timed(5), 1e-3)
+    n = int(min(2000, max(reps, 30.0 / est)))
+    timed(n)
+    ms = timed(n)
     eng.ctx.check()
-    return e0.elapsed_time(e1) / reps
+    return ms
 
 
 def run_configs(torch, mb, reps=20, pk=None, which=("mlp", "linear_sweep", "cnn", "gpt_s")):
