@@ -91,6 +91,20 @@ def _worker(rank, world, port, dtype, uid_q, res_q, B=2, T=64, hq=None):
         eng.attach_peer(hq[rank].get(timeout=120))
         assert np.array_equal(gathered, eng.run(ids))
         assert np.array_equal(gathered, eng.run(ids))
+        # soak: the ranks are pushed out of step (host sleeps, GPU work queued ahead of a forward);
+        # the counters must keep every buffer hand-over in order, so the bits never change
+        import random
+        import time
+        rng = random.Random(100 + rank)
+        junk = torch.empty(16 << 20, device="cuda")
+        for _ in range(60):
+            r = rng.random()
+            if r < 0.25:
+                time.sleep(rng.random() * 0.003)
+            elif r < 0.5:
+                for _ in range(rng.randint(1, 6)):
+                    junk.mul_(1.0001)
+            assert np.array_equal(gathered, eng.run(ids))
         eng.close()
     res_q.put((rank, red, slabs[0], gathered))
     comm.close()
