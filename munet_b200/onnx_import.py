@@ -15,8 +15,9 @@ ValueInfoProto) are decoded straight from the wire format with the field numbers
 
 Operators lowered: Gemm (transA = 0, alpha = beta = 1), MatMul with a constant right-hand side,
 Conv (2-D, one group, unit dilation, square kernel / stride, symmetric padding), MaxPool (2-D,
-square, symmetric), Relu, LeakyRelu, Sigmoid, Tanh, Gelu, Flatten (axis 1), GlobalAveragePool;
-Identity passes through; Constant nodes feed later nodes.
+square, symmetric), Relu, LeakyRelu, Sigmoid, Tanh, Gelu, Flatten (axis 1), GlobalAveragePool, and
+(beyond the reference's list) BatchNormalization in its inference form; Identity passes through;
+Constant nodes feed later nodes.
 """
 from __future__ import annotations
 
@@ -243,6 +244,7 @@ _LOWERED = {
     "Gemm": "nn.Linear", "MatMul": "nn.Linear", "Conv": "nn.Conv2d", "MaxPool": "nn.MaxPool2d",
     "Relu": "nn.ReLU", "LeakyRelu": "nn.LeakyReLU", "Sigmoid": "nn.Sigmoid", "Tanh": "nn.Tanh",
     "Gelu": "nn.GELU", "Flatten": "nn.Flatten", "GlobalAveragePool": "nn.GlobalAvgPool2d",
+    "BatchNormalization": "nn.BatchNorm2d",
 }
 _PASS_THROUGH = {"Identity": "pass_through", "Constant": "constant"}
 
@@ -348,6 +350,15 @@ def _lower(model: dict):
             precondition(st[0] == st[1] and pd[0] == pd[2] and pd[1] == pd[3] and pd[0] == pd[1],
                          "square stride, symmetric padding")
             emit({"type": "MaxPool2d", "kernel_size": int(ks[0]), "stride": int(st[0]), "padding": int(pd[0])})
+        elif op == "BatchNormalization":
+            # inference form: y = (x - mean) / sqrt(var + eps) * scale + B over the channel axis
+            ins = [consts.get(n) for n in node["input"][1:5]] if len(node["input"]) >= 5 else []
+            precondition(len(ins) == 4 and all(t is not None and t.ndim == 1 and t.size == ins[0].size for t in ins),
+                         "constant scale, B, mean and var of one length")
+            precondition(attrs.get("training_mode", 0) == 0, "inference mode")
+            emit({"type": "BatchNorm2d", "num_features": int(ins[0].size),
+                  "eps": float(attrs.get("epsilon", 1e-5)), "momentum": float(attrs.get("momentum", 0.9))},
+                 weight=ins[0], bias=ins[1], running_mean=ins[2], running_var=ins[3])
         elif op == "LeakyRelu":
             emit({"type": "LeakyReLU", "negative_slope": float(attrs.get("alpha", 0.01))})
         elif op == "Flatten":

@@ -79,6 +79,41 @@ def test_conv_without_bias_gets_the_zero_bias_the_module_needs():
         oi.compile_onnx(lopsided)
 
 
+def _conv_bn_relu():
+    rng = np.random.default_rng(8)
+    w = (rng.standard_normal((3, 2, 3, 3)) * 0.4).astype(np.float32)
+    scale, shift, mean = (rng.standard_normal(3).astype(np.float32) for _ in range(3))
+    var = (rng.random(3) + 0.5).astype(np.float32)
+    data = ox.model([ox.node("Conv", ["x", "w"], ["c"], kernel_shape=[3, 3], pads=[1, 1, 1, 1]),
+                     ox.node("BatchNormalization", ["c", "s", "b", "m", "v"], ["n"], epsilon=1e-3),
+                     ox.node("Relu", ["n"], ["y"])],
+                    [ox.value_info("x", [2, 2, 6, 6])], [ox.value_info("y", [2, 3, 6, 6])],
+                    [ox.tensor("w", w), ox.tensor("s", scale), ox.tensor("b", shift), ox.tensor("m", mean),
+                     ox.tensor("v", var)])
+    x = rng.standard_normal((2, 2, 6, 6)).astype(np.float32)
+    xp = np.pad(x, ((0, 0), (0, 0), (1, 1), (1, 1))).astype(np.float64)
+    conv = np.zeros((2, 3, 6, 6))
+    for kh in range(3):
+        for kw in range(3):
+            conv += np.einsum("bihw,oi->bohw", xp[:, :, kh:kh + 6, kw:kw + 6], w[:, :, kh, kw])
+    c = lambda t: t[None, :, None, None].astype(np.float64)
+    want = np.maximum((conv - c(mean)) / np.sqrt(c(var) + 1e-3) * c(scale) + c(shift), 0.0)
+    return data, x, want
+
+
+def test_batch_normalization_lowers_to_batchnorm2d(tmp_path):
+    data, x, want = _conv_bn_relu()
+    cfg, tensors = oi.compile_onnx(data)
+    assert [l["type"] for l in cfg["layers"]] == ["Conv2d", "BatchNorm2d", "ReLU"]
+    assert cfg["layers"][1]["num_features"] == 3 and abs(cfg["layers"][1]["eps"] - 1e-3) < 1e-9
+    assert sorted(k for k in tensors if k.startswith("1.")) == ["1.bias", "1.running_mean", "1.running_var",
+                                                                "1.weight"]
+    if oracle.have_ref():  # the reference's own engine agrees with the formula
+        path = str(tmp_path / "conv_bn_relu.npz")
+        oi.compile_onnx(data, output_path=path)
+        assert np.allclose(oracle.ref().engine_run_npz(path, x), want, rtol=1e-4, atol=1e-5)
+
+
 def test_unsupported_ops_are_reported_like_the_reference():
     data = ox.model([ox.node("Relu", ["x"], ["a"]), ox.node("NonMaxSuppression", ["a"], ["b"]),
                      ox.node("Loop", ["b"], ["y"])],
@@ -178,4 +213,10 @@ def test_imported_models_run_on_the_b200_engine():
     pooled = conv.reshape(3, 4, 4, 2, 4, 2).max(axis=(3, 5))
     want = pooled.reshape(3, -1) @ fw
     assert np.allclose(got, want, rtol=1e-4, atol=1e-4)
+    eng.close()
+    data, xin, want = _conv_bn_relu()
+    eng = Engine(compute_dtype=mb.F32)
+    eng.load(*oi.compile_onnx(data))
+    eng.compile(xin.shape)
+    assert np.allclose(np.asarray(eng.run(xin)), want, rtol=1e-4, atol=1e-5)
     eng.close()
