@@ -108,6 +108,10 @@ peer_reduce_kernel(const uint4 *__restrict__ a, const uint4 *__restrict__ a_peer
     // cached during an earlier exchange at the same address.
     constexpr int U = 8;
     const long long stride = 1ll * gridDim.x * blockDim.x;
+    // column (in 16-byte vectors) of element i0 + u * stride, kept by addition: one 64-bit
+    // modulo per thread instead of one per vector
+    const int cstep = static_cast<int>(stride % cols_vec);
+    int c0 = static_cast<int>((1ll * blockIdx.x * blockDim.x + threadIdx.x) % cols_vec);
     for (long long i0 = 1ll * blockIdx.x * blockDim.x + threadIdx.x; i0 < n_vec; i0 += stride * U) {
       uint4 vp[U], va[U], vr[U];
 #pragma unroll
@@ -127,11 +131,15 @@ peer_reduce_kernel(const uint4 *__restrict__ a, const uint4 *__restrict__ a_peer
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long i = i0 + u * stride;
+        const int col = c0;
+        c0 += cstep;
+        if (c0 >= cols_vec)
+          c0 -= cols_vec;
         if (i >= n_vec)
           break;
         uint4 vb = make_uint4(0, 0, 0, 0);
         if (bias)
-          vb = __ldg(bias + (i % cols_vec));
+          vb = __ldg(bias + col);
         const uint32_t wa[4] = {va[u].x, va[u].y, va[u].z, va[u].w}, wp[4] = {vp[u].x, vp[u].y, vp[u].z, vp[u].w};
         const uint32_t wb[4] = {vb.x, vb.y, vb.z, vb.w}, wr[4] = {vr[u].x, vr[u].y, vr[u].z, vr[u].w};
         uint32_t wo[4];
