@@ -45,16 +45,27 @@ METRIC = "tokens/s, GPT-style decoder forward (24L d2048 16h, seq 1024, bf16)"
 # this work names; the HGX part is 7.7), dense bf16 2250 TFLOP/s, dense TF32 1100 TFLOP/s.
 NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0, "tf32_tflops": 1100.0}
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the bf16 GEMM at
-# M = 16384 rows, per (K, N, residual) of the 24-layer decoder: ncu captures summarised in
-# profiles/gemm_bf16_tcgen05_M16384_N2048_K2048_gelu.md. A and C traffic grows in proportion to
-# M and B is small, so a launch at M rows is charged M/16384 of these.
-GEMM_TRAFFIC_AT_M16384 = {
-    (2048, 6144, False): 97.6e6 + 165.4e6,     # fused q/k/v projection
-    (2048, 2048, True): 75.6e6 + 32.5e6 + 67.1e6,   # out_proj (+ residual read, counted algorithmically)
-    (2048, 8192, False): 127.1e6 + 238.4e6,    # fc1 + GELU
-    (8192, 2048, True): 492.6e6 + 60.1e6 + 67.1e6,  # fc2 (+ residual read)
-    (2048, 32000, False): 685.5e6 + 1026.2e6,  # LM head, column panels
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the bf16 GEMM per
+# (K, N, residual) of the 24-layer decoder, from one-pass ncu captures summarised in
+# profiles/gemm_bf16_tcgen05_M16384_N2048_K2048_gelu.md, at two row counts: M = 65536 (the batch-64
+# forward) and M = 16384. Re-fetches of the weights grow with the number of tile waves, so traffic
+# per row is not the same at the two sizes; a launch at M rows is charged M / M_table of the table
+# nearer to it.
+GEMM_TRAFFIC = {
+    65536: {
+        (2048, 6144, False): 321.8e6 + 771.7e6,    # fused q/k/v projection
+        (2048, 2048, True): 545.7e6 + 245.3e6,     # out_proj (residual read included)
+        (2048, 8192, False): 458.8e6 + 1046.5e6,   # fc1 + GELU
+        (8192, 2048, True): 2076.6e6 + 260.6e6,    # fc2 (residual read included; L2 hints on)
+        (2048, 32000, False): 3886.7e6 + 4174.7e6,  # LM head, column panels
+    },
+    16384: {
+        (2048, 6144, False): 97.6e6 + 165.4e6,
+        (2048, 2048, True): 75.6e6 + 32.5e6 + 67.1e6,   # residual read added algorithmically
+        (2048, 8192, False): 127.1e6 + 238.4e6,
+        (8192, 2048, True): 492.6e6 + 60.1e6 + 67.1e6,
+        (2048, 32000, False): 685.5e6 + 1026.2e6,
+    },
 }
 
 
@@ -253,9 +264,10 @@ def gemm_traffic(prof):
             continue
         M, K, N = p["mkn"]
         key = (K, N, p["residual"])
-        if key not in GEMM_TRAFFIC_AT_M16384:
+        m_table = 65536 if M > 32768 else 16384
+        if key not in GEMM_TRAFFIC[m_table]:
             return None
-        total += GEMM_TRAFFIC_AT_M16384[key] * M / 16384.0
+        total += GEMM_TRAFFIC[m_table][key] * M / float(m_table)
         algo += p["bytes"]
         n += 1
     return (total, algo, n) if n else None
@@ -374,9 +386,9 @@ def run_ours(args, cfg):
         "traffic": traffic[0] / traffic[2] if traffic else None,
         "traffic_algorithmic": traffic[1] / traffic[2] if traffic else None,
         "traffic_ratio": traffic[0] / traffic[1] if traffic else None,
-        "traffic_unit": ("bytes/launch: ncu dram read+write per model shape at M=16384 "
-                         "(profiles/gemm_bf16_tcgen05_M16384_N2048_K2048_gelu.md), scaled to this "
-                         "launch's rows and averaged over the GEMM launches of one forward"),
+        "traffic_unit": ("bytes/launch: ncu dram read+write per model shape at M=65536 or M=16384, "
+                         "whichever is nearer (profiles/gemm_bf16_tcgen05_M16384_N2048_K2048_gelu.md), "
+                         "scaled to this launch's rows and averaged over the GEMM launches of one forward"),
         "launches_per_step": n_gemm, "avg_launch_ms": gemm_ms / max(1, n_gemm),
         "per_kind_ms": {k: round(v["ms"], 3) for k, v in by_kind.items()},
         "attention": ({"achieved_tflops_causal_useful": att["flops"] / (att["ms"] / 1e3) / 1e12,
@@ -737,6 +749,9 @@ def run_kernel_case(argv):
     ap.add_argument("--gemm-tile", default="", help="BN,CTAS: fix the bf16 GEMM tile (e.g. 128,2); default automatic")
     ap.add_argument("--att-variant", type=int, default=0,
                     help="fused attention kernel: 0 two query tiles per CTA (default), 1 one tile per CTA")
+    ap.add_argument("--b-hint", type=int, default=-1,
+                    help="linear: L2 hints of the GEMM: 0 none, 1 evict_last on weight tiles, 2 that and evict_first on "
+                         "the residual / output streams; default: the launcher decides")
     a = ap.parse_args(argv)
 
     def timed(fn, reps):
@@ -754,6 +769,8 @@ def run_kernel_case(argv):
     ctx = mb.Context(0)
     if a.att_variant:
         mb.lib().mu_debug_attention_variant(a.att_variant)
+    if a.b_hint >= 0:
+        mb.lib().mu_debug_gemm_b_hint(a.b_hint)
     if a.gemm_tile:
         bn, ct = (int(v) for v in a.gemm_tile.split(","))
         ctx.set_gemm_tile(bn, ct)

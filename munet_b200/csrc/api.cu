@@ -32,6 +32,7 @@ int launch_attention_tcgen05(const void *, const void *, const void *, void *, i
 int launch_attention_tcgen05_ex(const void *, const void *, const void *, void *, long long, void *, int, int,
                                 int, int, int, int, int *, cudaStream_t);
 void set_attention_variant(int);
+void set_gemm_b_hint(int);
 } // namespace mu
 
 struct mu_ctx {
@@ -237,6 +238,10 @@ int mu_ctx_set_gemm_tile(mu_ctx *ctx, int bn, int ctas) {
 // Not part of the declared ABI: selects the fused attention kernel (0 two query tiles per CTA,
 // 1 one tile per CTA) for timing one against the other. Process-wide.
 void mu_debug_attention_variant(int v) { mu::set_attention_variant(v); }
+// Not part of the declared ABI: L2 hints of the tensor-core GEMM: 0 none, 1 evict_last on the B tiles,
+// 2 that and evict_first on the residual and output streams; -1 leaves the choice to the launcher.
+// Process-wide, for timing one against the other.
+void mu_debug_gemm_b_hint(int v) { mu::set_gemm_b_hint(v); }
 int mu_ctx_force_simt(mu_ctx *ctx, int on) {
   if (!ctx)
     return MU_ERR_INVALID;

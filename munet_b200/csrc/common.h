@@ -49,6 +49,10 @@ struct GemmShape {
   int panel_n = 0;
   // > 0: use this tile width (64, 128, 256) and CTA count (1, 2) instead of the automatic choice
   int force_bn = 0, force_ctas = 0;
+  // tcgen05 kernel: 1 = B tiles are loaded with the L2 evict_last priority (B is re-used by every wave
+  // of tiles while A, the residual and the output stream past it); 2 = that, and the residual loads and
+  // output stores carry evict_first
+  int b_evict_last = 0;
 };
 
 // Operand addressing in elements. A is row-major [M,K]. B is row-major [K,N]

@@ -216,6 +216,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t b_policy = sh.b_evict_last ? l2_policy_evict_last() : 0ull;
       for (long long tile = tile0; tile < total_tiles && ok; tile += tile_step) {
         int nt, mt, bt;
         decode_tile(tile, tiles_m, tiles_n, panel, bt, mt, nt);
@@ -236,9 +237,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             tma_load_3d_g<CTAS>(sb, &tmB, &full_bar[stage], kb * BK, nt * BN + rank * (BN / CTAS), btb);
           } else {
             const int c0 = nt * BN + rank * (BN / CTAS) + bt * sh.b_col_per_batch;
+            if (sh.b_evict_last) {
 #pragma unroll
-            for (int j = 0; j < BN / CTAS / 64; ++j)
-              tma_load_3d_g<CTAS>(sb + j * 8192, &tmB, &full_bar[stage], c0 + j * 64, kb * BK, btb);
+              for (int j = 0; j < BN / CTAS / 64; ++j)
+                tma_load_3d_g_hint<CTAS>(sb + j * 8192, &tmB, &full_bar[stage], c0 + j * 64, kb * BK, btb,
+                                         b_policy);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / CTAS / 64; ++j)
+                tma_load_3d_g<CTAS>(sb + j * 8192, &tmB, &full_bar[stage], c0 + j * 64, kb * BK, btb);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -312,6 +320,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const bool split = ep.split_T > 0;
     const int HD = ep.split_H * ep.split_D;
     int it = 0;
+    const uint64_t stream_policy = sh.b_evict_last > 1 ? l2_policy_evict_first() : 0ull;
     int gcount = 0; // staged 64-column groups issued by this warp (phase of its residual barrier)
     bool ok = true;
     auto release_accumulator = [&](int b) {
@@ -362,7 +371,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               bulk_wait_read<0>(); // the previous store from this buffer has finished reading it
               if (has_res) {
                 mbar_arrive_expect_tx(&res_bar[warp - 2], Cfg::OUT_BOX_BYTES);
-                tma_load_5d(buf, &tmR, &res_bar[warp - 2], c0, c1, c2, c3, c4);
+                if (sh.b_evict_last > 1)
+                  tma_load_5d_hint(buf, &tmR, &res_bar[warp - 2], c0, c1, c2, c3, c4, stream_policy);
+                else
+                  tma_load_5d(buf, &tmR, &res_bar[warp - 2], c0, c1, c2, c3, c4);
               }
             }
             __syncwarp();
@@ -406,7 +418,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             fence_proxy_async(); // generic-proxy writes → visible to the TMA store
             __syncwarp();
             if (lane == 0) {
-              tma_store_5d(&tmC, buf, c0, c1, c2, c3, c4);
+              if (sh.b_evict_last > 1)
+                tma_store_5d_hint(&tmC, buf, c0, c1, c2, c3, c4, stream_policy);
+              else
+                tma_store_5d(&tmC, buf, c0, c1, c2, c3, c4);
               bulk_commit();
             }
             if (ep.c_mirror) {
@@ -642,6 +657,11 @@ static bool encode_out_maps(const Epilogue &ep, const GemmShape &sh, CUtensorMap
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// -1: the launcher decides about the L2 hints; 0 none, 1 evict_last on B tiles, 2 that and evict_first on
+// the residual and output streams (A/B timing).
+static int g_b_hint = -1;
+void set_gemm_b_hint(int v) { g_b_hint = v; }
+
 // Returns 0 ok, 1 shape/alignment not supported by this kernel, 2 launch/encode failure.
 int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const Epilogue &ep,
                              int *status, int num_sms, cudaStream_t stream) {
@@ -698,6 +718,16 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
     s2.panel_n = b_bytes > 48e6 ? static_cast<int>(32e6 / tile_bytes) : 0;
     if (b_bytes > 48e6 && s2.panel_n < 1)
       s2.panel_n = 1;
+  }
+  // L2 priorities. With a long K (fc2: K = 8192) every wave of tiles streams tens of MB of A past a B
+  // that all of them share, and LRU drops B between waves: B tiles then ask for evict_last and the
+  // single-use residual and output streams for evict_first. Measured at M = 65536, K = 8192, N = 2048:
+  // DRAM reads 2610 -> 2077 MB, 1.498 -> 1.491 ms. With K = 2048 (fc1, the LM head) the same hints
+  // save less traffic and cost 0.3-1 % time, so they stay off there.
+  {
+    const double b_bytes = 2.0 * sh.K * sh.N;
+    const bool wanted = sh.K >= 4096 && sh.M >= 4096 && b_bytes >= 8e6 && b_bytes <= 64e6 && !op.b_kmajor;
+    s2.b_evict_last = g_b_hint >= 0 ? g_b_hint : (wanted ? 2 : 0);
   }
   CUtensorMap tmA, tmB;
   if (!encode_map3(&tmA, op.a, sh.K, sh.M, a_nb, op.lda, a_bs, BK, BM))

@@ -133,6 +133,27 @@ __device__ __forceinline__ void tma_store_5d(const void *tmap, const void *smem_
                "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
                : "memory");
 }
+// The 5-D load / store with an L2 eviction-priority hint (single-use streams: evict_first).
+__device__ __forceinline__ void tma_load_5d_hint(void *smem_dst, const void *tmap, uint64_t *bar, int c0,
+                                                 int c1, int c2, int c3, int c4, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+               " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;" ::"r"(smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+               "r"(c3), "r"(c4), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_5d_hint(const void *tmap, const void *smem_src, int c0, int c1,
+                                                  int c2, int c3, int c4, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group.L2::cache_hint"
+               " [%0, {%2, %3, %4, %5, %6}], [%1], %7;" ::"l"(reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -275,6 +296,28 @@ __device__ __forceinline__ void tma_load_3d_g(void *smem_dst, const void *tmap, 
                  "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0),
                  "r"(c1), "r"(c2)
                  : "memory");
+}
+// The same load with an L2 eviction-priority hint (policy from l2_policy_evict_last()).
+template <int G>
+__device__ __forceinline__ void tma_load_3d_g_hint(void *smem_dst, const void *tmap, uint64_t *bar, int c0,
+                                                   int c1, int c2, uint64_t policy) {
+  if constexpr (G == 1)
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+                 " [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(smem_u32(smem_dst)),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+                 "l"(policy)
+                 : "memory");
+  else
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 ".L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(smem_u32(smem_dst)),
+                 "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0),
+                 "r"(c1), "r"(c2), "l"(policy)
+                 : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
 }
 // 32 lanes × 32 consecutive fp32 columns: thread i of the warp gets lane
 // (base_lane + i), registers r[0..31] = columns col..col+31.
