@@ -57,7 +57,7 @@ GEMM_TRAFFIC = {
         (2048, 2048, True): 545.7e6 + 245.3e6,     # out_proj (residual read included)
         (2048, 8192, False): 458.8e6 + 1046.5e6,   # fc1 + GELU
         (8192, 2048, True): 2076.6e6 + 260.6e6,    # fc2 (residual read included; L2 hints on)
-        (2048, 32000, False): 3886.7e6 + 4174.7e6,  # LM head, column panels
+        (2048, 32000, False): 3125.8e6 + 4166.5e6,  # LM head, column panels of 24 MB
     },
     16384: {
         (2048, 6144, False): 97.6e6 + 165.4e6,
