@@ -48,15 +48,15 @@ NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0, "tf32_tflops": 1100.0}
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the bf16 GEMM per
 # (K, N, residual) of the 24-layer decoder, from one-pass ncu captures summarised in
 # profiles/gemm_bf16_tcgen05_M16384_N2048_K2048_gelu.md, at two row counts: M = 65536 (the batch-64
-# forward) and M = 16384. Re-fetches of the weights grow with the number of tile waves, so traffic
+# forward, with the 40 MB L2 set-aside that bench.py turns on by default) and M = 16384. Re-fetches of the weights grow with the number of tile waves, so traffic
 # per row is not the same at the two sizes; a launch at M rows is charged M / M_table of the table
 # nearer to it.
 GEMM_TRAFFIC = {
     65536: {
         (2048, 6144, False): 321.8e6 + 771.7e6,    # fused q/k/v projection
         (2048, 2048, True): 545.7e6 + 245.3e6,     # out_proj (residual read included)
-        (2048, 8192, False): 458.8e6 + 1046.5e6,   # fc1 + GELU
-        (8192, 2048, True): 2076.6e6 + 260.6e6,    # fc2 (residual read included; L2 hints on)
+        (2048, 8192, False): 304.4e6 + 1040.9e6,   # fc1 + GELU (40 MB L2 set-aside, weights evict_last)
+        (8192, 2048, True): 1497.8e6 + 261.7e6,    # fc2 (residual read included; same)
         (2048, 32000, False): 3125.8e6 + 4166.5e6,  # LM head, column panels of 24 MB
     },
     16384: {
@@ -255,7 +255,11 @@ def summarize_profile(prof):
     return by_kind
 
 
-def gemm_traffic(prof):
+# the two shapes the set-aside changes, without it (evict_last on fc2's weights only)
+GEMM_TRAFFIC_NO_SET_ASIDE = {(2048, 8192, False): 458.8e6 + 1046.5e6, (8192, 2048, True): 2076.6e6 + 260.6e6}
+
+
+def gemm_traffic(prof, set_aside=True):
     """(measured-profile DRAM bytes, algorithmic bytes, launches) summed over the GEMMs of one
     forward; None when a shape has no capture behind it."""
     total, algo, n = 0.0, 0.0, 0
@@ -267,7 +271,10 @@ def gemm_traffic(prof):
         m_table = 65536 if M > 32768 else 16384
         if key not in GEMM_TRAFFIC[m_table]:
             return None
-        total += GEMM_TRAFFIC[m_table][key] * M / float(m_table)
+        per_launch = GEMM_TRAFFIC[m_table][key]
+        if m_table == 65536 and not set_aside:
+            per_launch = GEMM_TRAFFIC_NO_SET_ASIDE.get(key, per_launch)
+        total += per_launch * M / float(m_table)
         algo += p["bytes"]
         n += 1
     return (total, algo, n) if n else None
@@ -295,6 +302,8 @@ def run_ours(args, cfg):
     stream = torch.cuda.current_stream()
     lib = mb.lib()
     ctx = mb.Context(local)
+    if getattr(args, "l2_set_aside_mb", 0) > 0:
+        ctx.set_l2_set_aside(args.l2_set_aside_mb << 20)
 
     def barrier():
         torch.cuda.synchronize()
@@ -375,7 +384,7 @@ def run_ours(args, cfg):
     gemm_ms = by_kind.get("linear", {"ms": 0})["ms"] + by_kind.get("qkv_linear", {"ms": 0})["ms"]
     gemm_fl = by_kind.get("linear", {"flops": 0})["flops"] + by_kind.get("qkv_linear", {"flops": 0})["flops"]
     achieved = gemm_fl / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
-    traffic = gemm_traffic(prof)
+    traffic = gemm_traffic(prof, set_aside=args.l2_set_aside_mb > 0)
     att = by_kind.get("attention")
     roofline = {
         "bound": "tensor", "kernel": "gemm_bf16_tcgen05_kernel (all Linear layers of one forward)",
@@ -439,6 +448,9 @@ def run_ours(args, cfg):
 
     configs = None
     if world == 1 and not args.no_variants:
+        # the smaller workloads run with the whole L2: the set-aside is sized for the decoder's
+        # 33.5 MB weight matrices and only takes cache away from them
+        ctx.set_l2_set_aside(0)
         configs = run_configs(torch, mb, reps=args.config_reps, pk=pk)
 
     line = None
@@ -449,7 +461,11 @@ def run_ours(args, cfg):
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": warm, "ms_per_step": ms_total / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": workload_config(cfg, world),
+            "data": "synthetic",
+            "config": dict(workload_config(cfg, world),
+                           l2_set_aside=(f"{args.l2_set_aside_mb} MB of L2 reserved for the GEMMs' weight tiles "
+                                         "(mu_ctx_set_l2_set_aside; a limit of this process's CUDA context)"
+                                         if args.l2_set_aside_mb > 0 else "off")),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": B * T * 4,
                     "d2h_bytes_per_step": B * T * 4, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": stats["n_launches"] * args.steps,
@@ -749,6 +765,8 @@ def run_kernel_case(argv):
     ap.add_argument("--gemm-tile", default="", help="BN,CTAS: fix the bf16 GEMM tile (e.g. 128,2); default automatic")
     ap.add_argument("--att-variant", type=int, default=0,
                     help="fused attention kernel: 0 two query tiles per CTA (default), 1 one tile per CTA")
+    ap.add_argument("--persist-mb", type=int, default=0,
+                    help="linear: L2 set-aside (MB) for evict_last lines, this process's context only")
     ap.add_argument("--b-hint", type=int, default=-1,
                     help="linear: L2 hints of the GEMM: 0 none, 1 evict_last on weight tiles, 2 that and evict_first on "
                          "the residual / output streams; default: the launcher decides")
@@ -771,6 +789,8 @@ def run_kernel_case(argv):
         mb.lib().mu_debug_attention_variant(a.att_variant)
     if a.b_hint >= 0:
         mb.lib().mu_debug_gemm_b_hint(a.b_hint)
+    if a.persist_mb > 0:
+        ctx.set_l2_set_aside(a.persist_mb << 20)
     if a.gemm_tile:
         bn, ct = (int(v) for v in a.gemm_tile.split(","))
         ctx.set_gemm_tile(bn, ct)
@@ -856,6 +876,9 @@ def main():
                     help="skip the weak / tp2 / configs sub-records (headline measurement only)")
     ap.add_argument("--configs-only", action="store_true", help="print the four smaller workloads and exit")
     ap.add_argument("--config-reps", type=int, default=20)
+    ap.add_argument("--l2-set-aside-mb", type=int, default=40,
+                    help="L2 set aside for the weight tiles of the GEMMs (mu_ctx_set_l2_set_aside: a limit of "
+                         "this process's CUDA context only); 0 = off")
     ap.add_argument("--tp-exchange", default="rows", choices=["rows", "gather", "push", "peer", "nccl"],
                     help="tp2 sub-record: how the two ranks exchange (default: attention output and MLP partial "
                          "sums pushed into the peer's memory from inside the producing kernels)")

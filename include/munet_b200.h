@@ -78,6 +78,16 @@ int mu_ctx_set_sm_budget(mu_ctx *ctx, int n);
  * (1 or 2) the CTA count for every later GEMM of this context. 0, 0 restores the automatic choice.
  * Results do not depend on the tile shape (same accumulation order per output element). */
 int mu_ctx_set_gemm_tile(mu_ctx *ctx, int bn, int ctas);
+/* L2 set-aside for weights. `bytes` of the L2 of the context's device are reserved for cache lines
+ * loaded with the evict_last priority (cudaLimitPersistingL2CacheSize of the calling process's CUDA
+ * context: it ends with the process and changes nothing on the GPU for anyone else); the bf16
+ * tensor-core GEMM then keeps a weight matrix that fits (fc1 / fc2 of the decoder: 33.5 MB) in L2
+ * while activations and outputs stream past it, instead of re-fetching part of it for every wave
+ * of tiles. Measured on the 24-layer decoder at 65 536 tokens with 40 MB: DRAM traffic of the GEMMs
+ * 1.18 -> 1.03 of the algorithmic bytes, step time unchanged (the GEMMs gain what LayerNorm loses
+ * to the smaller remaining L2). 0 turns it off (the default: the limit is process-wide, so the
+ * application decides). Results do not change. */
+int mu_ctx_set_l2_set_aside(mu_ctx *ctx, size_t bytes);
 int mu_alloc(mu_ctx *ctx, size_t bytes, void **ptr);
 int mu_free(mu_ctx *ctx, void *ptr);
 int mu_copy(mu_ctx *ctx, void *dst, const void *src, size_t bytes, int kind, void *stream);

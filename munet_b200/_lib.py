@@ -43,6 +43,7 @@ SIGNATURES = {
     "mu_ctx_force_simt": (_i, [_vp, _i]),
     "mu_ctx_set_sm_budget": (_i, [_vp, _i]),
     "mu_ctx_set_gemm_tile": (_i, [_vp, _i, _i]),
+    "mu_ctx_set_l2_set_aside": (_i, [_vp, _sz]),
     "mu_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "mu_free": (_i, [_vp, _vp]),
     "mu_copy": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
@@ -202,6 +203,11 @@ class Context:
     def set_gemm_tile(self, bn: int = 0, ctas: int = 0):
         """Fix the bf16 GEMM tile (width 64/128/256, 1 or 2 CTAs); 0, 0 = automatic."""
         self._rc(self._lib.mu_ctx_set_gemm_tile(self._h, int(bn), int(ctas)))
+
+    def set_l2_set_aside(self, nbytes: int):
+        """Reserve ``nbytes`` of L2 for the GEMMs' weight tiles (a limit of this process's CUDA
+        context; 0 = off)."""
+        self._rc(self._lib.mu_ctx_set_l2_set_aside(self._h, int(nbytes)))
 
     def check(self, stream=None):
         """Synchronise the stream and raise if a kernel latched a device-side error."""

@@ -33,6 +33,7 @@ int launch_attention_tcgen05_ex(const void *, const void *, const void *, void *
                                 int, int, int, int, int *, cudaStream_t);
 void set_attention_variant(int);
 void set_gemm_b_hint(int);
+void set_gemm_l2_set_aside(double);
 } // namespace mu
 
 struct mu_ctx {
@@ -242,6 +243,17 @@ void mu_debug_attention_variant(int v) { mu::set_attention_variant(v); }
 // 2 that and evict_first on the residual and output streams; -1 leaves the choice to the launcher.
 // Process-wide, for timing one against the other.
 void mu_debug_gemm_b_hint(int v) { mu::set_gemm_b_hint(v); }
+int mu_ctx_set_l2_set_aside(mu_ctx *ctx, size_t bytes) {
+  if (!ctx)
+    return MU_ERR_INVALID;
+  if (!set_device(ctx))
+    return fail(ctx, MU_ERR_CUDA, "l2 set-aside: cannot select device %d", ctx->device);
+  const cudaError_t e = cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, bytes);
+  if (e != cudaSuccess)
+    return cuda_fail(ctx, "l2 set-aside", e);
+  mu::set_gemm_l2_set_aside(static_cast<double>(bytes));
+  return MU_OK;
+}
 int mu_ctx_force_simt(mu_ctx *ctx, int on) {
   if (!ctx)
     return MU_ERR_INVALID;

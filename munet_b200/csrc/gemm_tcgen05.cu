@@ -661,6 +661,10 @@ static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 // the residual and output streams (A/B timing).
 static int g_b_hint = -1;
 void set_gemm_b_hint(int v) { g_b_hint = v; }
+// Bytes of L2 this process has set aside for evict_last lines (0: none). With a set-aside the hints
+// hold a whole weight matrix of that size in L2 and more shapes profit.
+static double g_l2_set_aside = 0;
+void set_gemm_l2_set_aside(double bytes) { g_l2_set_aside = bytes; }
 
 // Returns 0 ok, 1 shape/alignment not supported by this kernel, 2 launch/encode failure.
 int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const Epilogue &ep,
@@ -728,7 +732,9 @@ int launch_gemm_bf16_tcgen05(const GemmOperands &op, const GemmShape &sh, const 
   // save less traffic and cost 0.3-1 % time, so they stay off there.
   {
     const double b_bytes = 2.0 * sh.K * sh.N;
-    const bool wanted = sh.K >= 4096 && sh.M >= 4096 && b_bytes >= 8e6 && b_bytes <= 64e6 && !op.b_kmajor;
+    const bool long_k = sh.K >= 4096 && b_bytes >= 8e6 && b_bytes <= 64e6;
+    const bool wide_n = g_l2_set_aside > 0 && sh.N >= 8192 && b_bytes >= 8e6 && b_bytes <= g_l2_set_aside;
+    const bool wanted = sh.M >= 4096 && !op.b_kmajor && (long_k || wide_n);
     s2.b_evict_last = g_b_hint >= 0 ? g_b_hint : (wanted ? 2 : 0);
   }
   CUtensorMap tmA, tmB;

@@ -83,6 +83,24 @@ def test_linear_bf16_under_an_sm_budget(ctx, budget):
         assert np.array_equal(full, limited)
 
 
+def test_linear_bf16_l2_set_aside_changes_no_bits(ctx):
+    """mu_ctx_set_l2_set_aside reserves L2 for the weight tiles and switches the loads of long-K and
+    wide-N shapes to the evict_last / evict_first priorities: cache behaviour only, same results."""
+    rng = np.random.default_rng(41)
+    shapes = ((4096, 4096, 1024, "none", True), (4096, 1024, 8192, "gelu", False), (512, 4096, 1024, "none", False))
+    base = []
+    for M, K, N, act, res in shapes:
+        x, w, b = rnd(rng, (M, K), BF16), rnd(rng, (K, N), BF16, 1.0 / np.sqrt(K)), rnd(rng, (N,), BF16, 0.05)
+        r = rnd(rng, (M, N), BF16) if res else None
+        base.append((x, w, b, r, act, dev_linear(ctx, x, w, b, BF16, act, res=r)))
+    ctx.set_l2_set_aside(32 << 20)
+    try:
+        for x, w, b, r, act, want in base:
+            assert np.array_equal(dev_linear(ctx, x, w, b, BF16, act, res=r), want)
+    finally:
+        ctx.set_l2_set_aside(0)
+
+
 def test_linear_bf16_wide_weights_use_column_panels(ctx):
     """A weight matrix wider than the L2 budget (here 49 MB) is swept in panels of column tiles,
     the last one narrower. Every output tile must still be produced exactly once: compared with
